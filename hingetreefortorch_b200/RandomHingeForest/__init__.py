@@ -1,0 +1,12 @@
+"""nn.Module layer of the hinge tree drop-in (same exported names as the reference package)."""
+from ._RandomHingeForest import (  # noqa: F401
+    RandomHingeForest, RandomHingeFern, RandomHingeTrie,
+    SparseRandomHingeForest, SparseRandomHingeFern,
+    RandomHingeForestFusedLinear, RandomHingeFernFusedLinear,
+    SparseRandomHingeForestFusedLinear, SparseRandomHingeFernFusedLinear,
+    RandomHingeForestFusion, RandomHingeFernFusion,
+    RandomHingeForestFusionFusedLinear, RandomHingeFernFusionFusedLinear,
+)
+from ._HingeTreeConv import (  # noqa: F401
+    HingeTreeConv1d, HingeTreeConv2d, HingeTreeConv3d, HingeFernConv1d, HingeFernConv2d, HingeFernConv3d,
+)

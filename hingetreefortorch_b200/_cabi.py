@@ -1,0 +1,138 @@
+"""ctypes binding of the C ABI in include/hingetree_b200.h.
+
+This is the thinnest possible caller of the library: it passes raw device pointers of torch
+tensors and the current CUDA stream.  The parity tests and the benchmark go through it so
+that they exercise exactly the symbols a foreign binding would.  torch is used for device
+memory and streams only.
+"""
+import ctypes
+import os
+
+from . import _build
+
+HT_KIND = {"tree": 0, "fern": 1}
+HT_DETERMINISTIC = 1
+HT_FLAG_ORDINAL_RANGE = 1
+
+# every symbol include/hingetree_b200.h declares (checked by the CPU test-suite)
+SYMBOLS = [
+    "ht_version", "ht_status_string", "ht_last_cuda_error", "ht_forest_workspace_bytes",
+    "ht_forest_forward_f32", "ht_forest_leafmap_f32", "ht_forest_marginmap_f32",
+    "ht_forest_reachability_f32", "ht_forest_backward_f32",
+]
+
+
+class ForestProblem(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_int32), ("depth", ctypes.c_int32), ("B", ctypes.c_int64), ("C", ctypes.c_int64),
+                ("K", ctypes.c_int64), ("T", ctypes.c_int64), ("M", ctypes.c_int64), ("flags", ctypes.c_uint32),
+                ("reserved", ctypes.c_uint32)]
+
+
+class HingeTreeError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__("hingetree_b200 status %d: %s" % (status, message))
+        self.status = status
+
+
+_lib = None
+
+
+def library():
+    """Load libhingetree_b200.so from the source tree.  Fails loudly when it was not built."""
+    global _lib
+    if _lib is None:
+        path = _build.library_path()
+        if not os.path.exists(path):
+            raise ImportError("%s is missing: build it with `python -m hingetreefortorch_b200._build` "
+                              "(there is no fallback path)" % path)
+        lib = ctypes.CDLL(path)
+        lib.ht_status_string.restype = ctypes.c_char_p
+        lib.ht_status_string.argtypes = [ctypes.c_int]
+        lib.ht_forest_workspace_bytes.restype = ctypes.c_size_t
+        lib.ht_forest_workspace_bytes.argtypes = [ctypes.POINTER(ForestProblem)]
+        _lib = lib
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise HingeTreeError(rc, library().ht_status_string(rc).decode())
+
+
+def _ptr(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(t):
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def forest_problem(kind, x, w, deterministic=False):
+    import math
+    L = w.shape[1]
+    depth = L.bit_length() - 1
+    if L <= 0 or (1 << depth) != L:
+        raise ValueError("leaf count %d is not a power of two" % L)
+    return ForestProblem(HT_KIND[kind], depth, x.shape[0], x.shape[1], math.prod(x.shape[2:]), w.shape[0],
+                         math.prod(w.shape[2:]), HT_DETERMINISTIC if deterministic else 0, 0)
+
+
+class Forest:
+    """Scratch memory and status word for repeated calls on one problem shape."""
+
+    def __init__(self, kind, x, w, deterministic=False):
+        import torch
+        self.kind = kind
+        self.problem = forest_problem(kind, x, w, deterministic)
+        nbytes = library().ht_forest_workspace_bytes(ctypes.byref(self.problem))
+        self.workspace = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=x.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=x.device)
+        self.out_shape = tuple(x.shape[:1]) + tuple(w.shape[:1]) + tuple(x.shape[2:]) + tuple(w.shape[2:])
+        self.map_shape = tuple(x.shape[:1]) + tuple(w.shape[:1]) + tuple(x.shape[2:])
+
+    def _tail(self, x):
+        return (_ptr(self.workspace), ctypes.c_size_t(self.workspace.numel()), _ptr(self.status), _stream(x))
+
+    def forward(self, x, thr, ord_, w, out=None):
+        import torch
+        if out is None:
+            out = torch.empty(self.out_shape, dtype=torch.float32, device=x.device)
+        _check(library().ht_forest_forward_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(w),
+                                               _ptr(out), *self._tail(x)))
+        return out
+
+    def leafmap(self, x, thr, ord_):
+        import torch
+        leaf = torch.empty(self.map_shape, dtype=torch.int64, device=x.device)
+        _check(library().ht_forest_leafmap_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(leaf),
+                                               *self._tail(x)))
+        return leaf
+
+    def marginmap(self, x, thr, ord_):
+        import torch
+        margin = torch.empty(self.map_shape, dtype=torch.float32, device=x.device)
+        mord = torch.empty(self.map_shape, dtype=torch.int64, device=x.device)
+        _check(library().ht_forest_marginmap_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_),
+                                                 _ptr(margin), _ptr(mord), *self._tail(x)))
+        return margin, mord
+
+    def reachability(self, x, thr, ord_):
+        import torch
+        counts = torch.empty((self.problem.T, 1 << self.problem.depth), dtype=torch.int64, device=x.device)
+        _check(library().ht_forest_reachability_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_),
+                                                    _ptr(counts), *self._tail(x)))
+        return counts
+
+    def backward(self, x, thr, ord_, w, g, need=(True, True, True), outs=None):
+        import torch
+        if outs is None:
+            outs = (torch.empty_like(x) if need[0] else None, torch.empty_like(thr) if need[1] else None,
+                    torch.empty_like(w) if need[2] else None)
+        _check(library().ht_forest_backward_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(w),
+                                                _ptr(g), _ptr(outs[0]), _ptr(outs[1]), _ptr(outs[2]), *self._tail(x)))
+        return outs
+
+    def ordinal_flags(self):
+        """Reads the device status word (blocks until the stream has drained)."""
+        return int(self.status.item())

@@ -1,0 +1,52 @@
+// Helpers shared by the translation units of the `hingetree_cpp` torch extension.
+#pragma once
+
+#include <torch/extension.h>
+
+#include <string>
+#include <vector>
+
+#include "hingetree_b200.h"
+
+namespace htx {
+
+[[noreturn]] void bad_argument(const std::string &what);  // std::invalid_argument -> ValueError
+[[noreturn]] void bad_runtime(const std::string &what);   // std::runtime_error -> RuntimeError
+void raise_status(int rc, const char *op);
+
+ht_stream_t current_stream(const torch::Tensor &t);
+int64_t inner_count(const torch::Tensor &t, int64_t from);
+int depth_of(int64_t leaves);
+int64_t threshold_count(int kind, int depth);
+void require_cuda(const torch::Tensor &t);
+void require_float32(const torch::Tensor &t);
+torch::Tensor make_workspace(size_t bytes, const torch::Tensor &like);
+void set_ordinal_check(const std::string &mode);
+
+// Owns the device status word of one call and turns a flagged ordinal into the reference's
+// RuntimeError.  word() is null when this ordinals tensor is already known to be valid.
+class OrdinalGuard {
+ public:
+  OrdinalGuard(const torch::Tensor &ord, int64_t channels);
+  uint32_t *word();
+  void finish();
+
+ private:
+  torch::Tensor ord_, word_;
+  int64_t channels_;
+  bool check_;
+};
+
+// Argument checks and shape bookkeeping of the plain forest operators.
+struct ForestCall {
+  ForestCall(int kind, const torch::Tensor &x, const torch::Tensor &thr, const torch::Tensor &ord,
+             const torch::Tensor &w, const torch::Tensor *g);
+  ht_forest_problem problem;
+  std::vector<int64_t> out_sizes;  // [B, T, inner data dims..., inner weight dims...]
+  std::vector<int64_t> map_sizes;  // [B, T, inner data dims...]
+};
+
+// Registers the convolution, fused-linear, fusion, sparse, trie and contract/expand operators.
+void bind_more_ops(pybind11::module_ &m);
+
+}  // namespace htx

@@ -1,0 +1,106 @@
+// Shared device code of the sm_100a hinge tree library: the traversal, feature lookups,
+// launch helpers and argument checks used by every kernel file.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "hingetree_b200.h"
+
+namespace ht {
+
+constexpr int TREE = HT_KIND_TREE;
+constexpr int FERN = HT_KIND_FERN;
+
+// Per-thread record of the last failed CUDA runtime call (ht_last_cuda_error()).
+extern thread_local int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return HT_ERR_CUDA;
+}
+
+#define HT_CUDA_TRY(expr)                                   \
+  do {                                                      \
+    cudaError_t _e = (expr);                                \
+    if (_e != cudaSuccess) return ::ht::cuda_fail(_e);      \
+  } while (0)
+
+// Checks the launch that was just issued (never synchronises).
+#define HT_CHECK_LAUNCH() HT_CUDA_TRY(cudaPeekAtLastError())
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+__host__ __device__ inline int64_t threshold_count(int kind, int depth) {
+  return kind == FERN ? (int64_t)depth : (((int64_t)1) << depth) - 1;
+}
+
+// Result of one traversal: leaf key (bit l = decision at depth l, LSB = root), signed margin
+// of the decision with the smallest |margin| (first one wins ties) and its vertex index.
+struct Path {
+  uint32_t key;
+  float margin;
+  uint32_t vertex;
+};
+
+// Feature of one (sample, position): x[i, c, k] with the (i, k) part folded into `base`.
+struct PlainFeature {
+  const float *__restrict__ base;
+  int64_t stride;  // K
+  __device__ __forceinline__ float operator()(int c) const { return __ldg(base + (int64_t)c * stride); }
+};
+
+// Image + per-sample vector lookup: features below the image channel count come from the
+// image, the rest from the vector (reference semantics: HingeTreeCommon.cuh:81-107, 156-184).
+struct FusionFeature {
+  const float *__restrict__ img;
+  int64_t stride;
+  const float *__restrict__ vec;
+  int img_channels;
+  __device__ __forceinline__ float operator()(int c) const {
+    return c < img_channels ? __ldg(img + (int64_t)c * stride) : __ldg(vec + (c - img_channels));
+  }
+};
+
+// The traversal.  One plain fp32 subtract per level; `m > 0` sends NaN and 0 to the left;
+// strict `<` keeps the shallowest minimum.  Level 0 seeds the minimum, which is what the
+// reference's initialisation from vertex 0 amounts to (also for NaN margins).
+template <int KIND, typename OrdT, typename Feature>
+__device__ __forceinline__ Path traverse(const Feature &feat, const float *__restrict__ thr,
+                                         const OrdT *__restrict__ ord, int depth) {
+  Path p;
+  p.key = 0;
+  p.vertex = 0;
+  p.margin = 0.0f;
+  uint32_t v = 0;
+  for (int l = 0; l < depth; ++l) {
+    const uint32_t at = (KIND == FERN) ? (uint32_t)l : v;
+    const float m = feat((int)ord[at]) - thr[at];
+    const uint32_t bit = (m > 0.0f) ? 1u : 0u;
+    if (l == 0 || fabsf(m) < fabsf(p.margin)) {
+      p.margin = m;
+      p.vertex = at;
+    }
+    p.key |= bit << l;
+    v = 2 * v + 1 + bit;
+  }
+  return p;
+}
+
+__device__ __forceinline__ float sign_of(float m) { return (float)((0.0f < m) - (m < 0.0f)); }
+
+// Common argument screening for the forest entry points.
+inline int check_forest_problem(const ht_forest_problem *p) {
+  if (p == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  if (p->kind != TREE && p->kind != FERN) return HT_ERR_INVALID_ARGUMENT;
+  if (p->depth < 1 || p->depth > 31) return HT_ERR_DEPTH;
+  if (p->B < 0 || p->C < 1 || p->K < 0 || p->T < 0 || p->M < 0) return HT_ERR_INVALID_ARGUMENT;
+  if (p->C > 0x7fffffff) return HT_ERR_UNSUPPORTED;
+  return HT_OK;
+}
+
+// Converts int64 ordinals to int32, clamping out-of-range values to 0 and flagging them.
+int pack_ordinals(const int64_t *ord, int64_t n, int64_t C, int32_t *packed, uint32_t *status_word,
+                  cudaStream_t stream);
+
+}  // namespace ht

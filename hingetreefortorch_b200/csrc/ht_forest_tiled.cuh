@@ -1,0 +1,14 @@
+// Shared-memory tile kernel for the forest forward (see ht_forest_tiled.cu).
+#pragma once
+
+#include "ht_common.cuh"
+
+namespace ht {
+
+// Runs the forward with the tile kernel when the shape qualifies; returns HT_ERR_UNSUPPORTED
+// (and launches nothing) when it does not, so that the caller can use the any-shape kernel.
+// `ord` are the compact (validated, clamped) int32 ordinals.
+int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
+                  float *out, cudaStream_t stream);
+
+}  // namespace ht

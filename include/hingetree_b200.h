@@ -1,0 +1,117 @@
+/*
+ * hingetree_b200 -- C ABI of the sm_100a hinge tree / hinge fern evaluation library.
+ *
+ * This is the boundary a binding of HingeTreeForTorch's `hingetree_cpp` extension links
+ * against: plain pointers and sizes, no torch types.  Every entry point
+ *   - works on DEVICE pointers of the current CUDA device,
+ *   - enqueues its kernels on the stream it is given and returns without synchronising,
+ *   - allocates nothing (scratch comes from the caller, sized by the *_workspace_bytes query),
+ *   - never throws: it returns HT_OK or a negative ht_status.
+ *
+ * Tensor layouts are the reference's (row-major, contiguous, fp32 data, int64 ordinals):
+ *   x   [B, C, K]     K = product of the inner data dimensions (1 for tabular input)
+ *   thr [T, N]        N = 2^depth - 1 for trees, depth for ferns
+ *   ord [T, N]        int64 feature index of each decision, in [0, C)
+ *   w   [T, L, M]     L = 2^depth leaves, M = product of the inner weight dimensions
+ *   out [B, T, K, M]
+ *
+ * Ordinal validation: the reference raises when an ordinal is outside [0, C)
+ * (hingetree_gpu.cu:445).  Here the kernels clamp such an ordinal to 0, so that no access
+ * ever leaves the input, and OR the bit HT_FLAG_ORDINAL_RANGE into the caller's device
+ * status word; the host binding reads the word and raises.  The status word is never
+ * cleared by the library.
+ */
+#ifndef HINGETREE_B200_H
+#define HINGETREE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st *ht_stream_t; /* a cudaStream_t */
+
+typedef enum ht_status {
+  HT_OK = 0,
+  HT_ERR_INVALID_ARGUMENT = -1, /* shapes / null pointers: the reference's std::invalid_argument (ValueError) */
+  HT_ERR_DEPTH = -2,            /* depth outside [1, 31] or N does not match: the reference's std::runtime_error */
+  HT_ERR_CUDA = -3,             /* a launch or runtime call failed; ht_last_cuda_error() has the code */
+  HT_ERR_WORKSPACE = -4,        /* workspace missing, misaligned or too small */
+  HT_ERR_UNSUPPORTED = -5       /* valid request that this build does not implement */
+} ht_status;
+
+/* bits OR-ed into the device status word */
+#define HT_FLAG_ORDINAL_RANGE 1u /* an ordinal was < 0 or >= C (reference: RuntimeError) */
+
+#define HT_KIND_TREE 0 /* complete binary tree: HingeTreeCommon<>  (HingeTreeCommon.h:129) */
+#define HT_KIND_FERN 1 /* oblivious fern:       HingeFernCommon<>  (HingeTreeCommon.h:42)  */
+
+/* ht_forest_problem.flags */
+#define HT_DETERMINISTIC 1u /* backward: fixed summation order equal to the reference CPU loops */
+
+typedef struct ht_forest_problem {
+  int32_t kind;   /* HT_KIND_TREE or HT_KIND_FERN */
+  int32_t depth;  /* 1..31 (HingeTreeCommon.h:51,138: uint32 leaf keys) */
+  int64_t B;      /* batch */
+  int64_t C;      /* channels (features) of x */
+  int64_t K;      /* inner data positions per sample */
+  int64_t T;      /* trees */
+  int64_t M;      /* outputs per leaf */
+  uint32_t flags;
+  uint32_t reserved;
+} ht_forest_problem;
+
+int ht_version(void);
+const char *ht_status_string(int status);
+int ht_last_cuda_error(void); /* cudaError_t of the last failed runtime call on this thread */
+
+/* Scratch bytes ht_forest_* calls need for this problem (compact ordinals and, for the
+ * backward, nothing more).  The workspace must be 256-byte aligned device memory. */
+size_t ht_forest_workspace_bytes(const ht_forest_problem *p);
+
+/* out[i,j,k,m] = |margin(i,j,k)| * w[j, leaf(i,j,k), m]
+ * Replaces hingetree_gpu_forward / ForwardKernel (hingetree_gpu.cu:416-498, 58-87) and the
+ * traversal templates it instantiates (HingeTreeCommon.cuh:60-79 fern, 133-154 tree). */
+int ht_forest_forward_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
+                          const float *w, float *out, void *workspace, size_t workspace_bytes,
+                          uint32_t *status_word, ht_stream_t stream);
+
+/* leaf[i,j,k] = leaf key (bit l = decision at depth l), int64.
+ * Replaces hingetree_gpu_leafmap / LeafMapKernel (hingetree_gpu.cu:791-860, 116-139). */
+int ht_forest_leafmap_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
+                          int64_t *leaf, void *workspace, size_t workspace_bytes, uint32_t *status_word,
+                          ht_stream_t stream);
+
+/* margin[i,j,k] = signed margin of the closest decision, margin_ord[i,j,k] = its feature index.
+ * Replaces hingetree_gpu_marginmap / MarginMapKernel (hingetree_gpu.cu:862-933, 141-166). */
+int ht_forest_marginmap_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
+                            float *margin, int64_t *margin_ord, void *workspace, size_t workspace_bytes,
+                            uint32_t *status_word, ht_stream_t stream);
+
+/* counts[j, leaf] = number of (i,k) positions reaching that leaf, int64 [T, L]; cleared here.
+ * Replaces hingetree_gpu_reachability / ReachabilityKernel (hingetree_gpu.cu:732-789, 89-114). */
+int ht_forest_reachability_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
+                               int64_t *counts, void *workspace, size_t workspace_bytes, uint32_t *status_word,
+                               ht_stream_t stream);
+
+/* Gradients of the forward with respect to x, thr and w given g = d loss / d out [B,T,K,M]:
+ *   gx  [i, ord[j,v*], k] += sign * w[j,leaf,m] * g[i,j,k,m]
+ *   gthr[j, v*]           += -sign * w[j,leaf,m] * g[i,j,k,m]
+ *   gw  [j, leaf, m]      += |margin| * g[i,j,k,m]
+ * Any of gx / gthr / gw may be NULL (not requested); the others are cleared here first.
+ * Without HT_DETERMINISTIC this replaces hingetree_gpu_backward and its three atomic kernels
+ * (hingetree_gpu.cu:619-730, 212-253, 293-325, 370-410).  With HT_DETERMINISTIC it replaces
+ * hingetree_gpu_backward_deterministic (hingetree_gpu.cu:500-617, 170-210, 257-291, 328-368):
+ * every gradient element is then summed in exactly the order of the reference CPU loops
+ * (hingetree.cpp:232-308: i, then j, then k, then m), so results are reproducible and equal
+ * to the reference CPU build bit for bit. */
+int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
+                           const float *w, const float *g, float *gx, float *gthr, float *gw,
+                           void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HINGETREE_B200_H */
