@@ -46,6 +46,26 @@ def _nvcc():
     return cand if os.path.exists(cand) else "nvcc"
 
 
+def _shared_libstdcxx():
+    """Full path of the shared libstdc++, put on link lines explicitly.
+
+    Some toolchain layouts carry a dangling libstdc++.so next to libstdc++.a, and the linker
+    then silently links the static archive into the shared object (two C++ runtimes in one
+    process: iostreams crash).  Naming the shared library first leaves the archive nothing to add.
+    """
+    try:
+        out = subprocess.run(["ldconfig", "-p"], capture_output=True, text=True).stdout
+        for line in out.splitlines():
+            if "libstdc++.so.6" in line and "x86-64" in line and "=>" in line:
+                return [line.split("=>")[1].strip()]
+    except OSError:
+        pass
+    for cand in ("/usr/lib/x86_64-linux-gnu/libstdc++.so.6", "/usr/lib64/libstdc++.so.6"):
+        if os.path.exists(cand):
+            return [cand]
+    return []
+
+
 def build_library(force=False, verbose=False):
     """Compile csrc/*.cu for sm_100a and link libhingetree_b200.so."""
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
@@ -96,7 +116,7 @@ def build_extension(force=False):
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
         objs = list(ex.map(compile_one, sources))
     if force or _newer(target, objs + [library_path()]):
-        link = [cxx, "-shared", "-o", target] + objs + ["-L" + PKG, "-lhingetree_b200", "-Wl,-rpath,$ORIGIN"]
+        link = [cxx, "-shared", "-o", target] + objs + _shared_libstdcxx() + ["-L" + PKG, "-lhingetree_b200", "-Wl,-rpath,$ORIGIN"]
         for d in ce.library_paths() + [os.path.join(cuda_home, "lib64")]:
             link += ["-L" + d, "-Wl,-rpath," + d]
         link += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart"]

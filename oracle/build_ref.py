@@ -70,6 +70,11 @@ def build(reference, jobs=8, force=False):
         objs = list(ex.map(compile_one, srcs))
     libdirs = ce.library_paths()
     link = [cxx, "-shared", "-o", target] + objs
+    # name the shared C++ runtime first, so that a static libstdc++.a is never pulled in
+    for cand in ("/usr/lib/x86_64-linux-gnu/libstdc++.so.6", "/usr/lib64/libstdc++.so.6"):
+        if os.path.exists(cand):
+            link.append(cand)
+            break
     for d in libdirs:
         link += ["-L" + d, "-Wl,-rpath," + d]
     link += ["-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python"]

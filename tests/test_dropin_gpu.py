@@ -1,0 +1,116 @@
+"""The reference-facing surface on a GPU: the `hingetree_cpp` operators, the autograd
+Functions and the nn.Modules, checked against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import random_forest_inputs
+from oracle import hinge_oracle as ho
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from hingetreefortorch_b200._ext import hingetree_cpp
+    return hingetree_cpp
+
+
+def dev(*arrays):
+    return [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in arrays]
+
+
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+def test_operators_match_oracle(ext, kind):
+    x, thr, ord_, w = random_forest_inputs(21, kind, 40, 12, (3,), 10, 4, (2,))
+    g = np.random.default_rng(0).standard_normal((40, 10, 3, 2)).astype(np.float32)
+    dx, dthr, dord, dw, dg = dev(x, thr, ord_, w, g)
+    out = getattr(ext, kind + "_forward")(dx, dthr, dord, dw)
+    assert out.shape == (40, 10, 3, 2) and np.array_equal(out.cpu().numpy(), ho.forward(kind, x, thr, ord_, w))
+    leaf, margin, mord, reach = ho.maps(kind, x, thr, ord_, w)
+    got_leaf = getattr(ext, kind + "_leafmap")(dx, dthr, dord, dw)
+    assert got_leaf.dtype == torch.int64 and np.array_equal(got_leaf.cpu().numpy(), leaf)
+    got_margin, got_mord = getattr(ext, kind + "_marginmap")(dx, dthr, dord, dw)
+    assert np.array_equal(got_margin.cpu().numpy(), margin) and np.array_equal(got_mord.cpu().numpy(), mord)
+    got_reach = getattr(ext, kind + "_reachability")(dx, dthr, dord, dw)
+    assert got_reach.dtype == torch.int64 and np.array_equal(got_reach.cpu().numpy(), reach)
+    want = ho.backward(kind, x, thr, ord_, w, g)
+    grads = getattr(ext, kind + "_backward_deterministic")(dx, True, dthr, True, dord, False, dw, True, dg)
+    assert grads[2] is None
+    for got, ref in zip((grads[0], grads[1], grads[3]), want):
+        assert np.array_equal(got.cpu().numpy(), ref)
+    grads = getattr(ext, kind + "_backward")(dx, True, dthr, False, dord, False, dw, True, dg)
+    assert grads[1] is None and grads[2] is None
+    assert np.allclose(grads[0].cpu().numpy(), want[0], rtol=1e-4, atol=1e-5)
+    assert np.allclose(grads[3].cpu().numpy(), want[2], rtol=1e-4, atol=1e-5)
+    assert getattr(ext, kind + "_backward")(dx, False, dthr, False, dord, False, dw, False, dg) == [None] * 4
+
+
+def test_error_contract_on_device(ext):
+    x, thr, ord_, w = random_forest_inputs(22, "tree", 8, 5, (), 3, 3, ())
+    dx, dthr, dord, dw = dev(x, thr, ord_, w)
+    bad = dord.clone()
+    bad[0, 0] = 5
+    with pytest.raises(RuntimeError, match="ordinal"):
+        ext.tree_forward(dx, dthr, bad, dw)
+    with pytest.raises(RuntimeError, match="ordinal"):
+        ext.tree_backward(dx, True, dthr, True, bad, False, dw, True, torch.ones(8, 3, device="cuda"))
+    with pytest.raises(ValueError, match="same device"):
+        ext.tree_forward(dx, dthr.cpu(), dord, dw)
+    with pytest.raises(RuntimeError, match="tree depth"):
+        ext.tree_forward(dx, dthr[:, :6].contiguous(), dord[:, :6].contiguous(), dw)
+    with pytest.raises(ValueError, match="outDataGrad.shape"):
+        ext.tree_backward(dx, True, dthr, True, dord, False, dw, True, torch.ones(8, 4, device="cuda"))
+    with pytest.raises(ValueError):
+        ext.tree_forward(dx.double(), dthr.double(), dord, dw.double())
+    # a valid ordinals tensor that is later corrupted in place is re-validated (version changed)
+    ext.tree_forward(dx, dthr, dord, dw)
+    dord[1, 1] = -3
+    with pytest.raises(RuntimeError, match="ordinal"):
+        ext.tree_forward(dx, dthr, dord, dw)
+
+
+@pytest.mark.parametrize("module_name,kind", [("RandomHingeForest", "tree"), ("RandomHingeFern", "fern")])
+def test_modules_forward_backward(module_name, kind):
+    from hingetreefortorch_b200 import RandomHingeForest as R
+    torch.manual_seed(0)
+    m = getattr(R, module_name)(20, 16, 5, extra_outputs=3).cuda()
+    x = torch.randn(64, 20, device="cuda", requires_grad=True)
+    y = m(x)
+    assert y.shape == (64, 16, 3)
+    y.backward(torch.ones_like(y))
+    xn, thr, ord_, w = x.detach().cpu().numpy(), m.thresholds.detach().cpu().numpy(), m.ordinals.cpu().numpy(), m.weights.detach().cpu().numpy()
+    assert np.array_equal(y.detach().cpu().numpy(), ho.forward(kind, xn, thr, ord_, w))
+    gx, gthr, gw = ho.backward(kind, xn, thr, ord_, w, np.ones(y.shape, np.float32))
+    assert np.allclose(x.grad.cpu().numpy(), gx, rtol=1e-4, atol=1e-5)
+    assert np.allclose(m.thresholds.grad.cpu().numpy(), gthr, rtol=1e-4, atol=1e-4)
+    assert np.allclose(m.weights.grad.cpu().numpy(), gw, rtol=1e-4, atol=1e-4)
+    assert m.ordinals.grad is None
+    # deterministic mode selects the fixed-order backward: bit-exact against the oracle
+    prev = torch.are_deterministic_algorithms_enabled()
+    torch.use_deterministic_algorithms(True)
+    try:
+        for p in (x, m.thresholds, m.weights):
+            p.grad = None
+        m(x).backward(torch.ones_like(y))
+    finally:
+        torch.use_deterministic_algorithms(prev)
+    assert np.array_equal(x.grad.cpu().numpy(), gx)
+    assert np.array_equal(m.thresholds.grad.cpu().numpy(), gthr)
+    assert np.array_equal(m.weights.grad.cpu().numpy(), gw)
+    # analysis helpers
+    leaf = m.leafmap(x.detach())
+    assert leaf.shape == (64, 16) and m.reachability(x.detach()).sum() == 64 * 16
+    assert m.pathmap(x.detach()).shape == (64, 16, 5)
+
+
+def test_kernels_run_on_the_current_stream(ext):
+    x, thr, ord_, w = random_forest_inputs(23, "tree", 512, 64, (), 32, 6, ())
+    dx, dthr, dord, dw = dev(x, thr, ord_, w)
+    ext.tree_forward(dx, dthr, dord, dw)  # validates the ordinals once
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        out = ext.tree_forward(dx, dthr, dord, dw)
+    side.synchronize()
+    assert np.array_equal(out.cpu().numpy(), ho.forward("tree", x, thr, ord_, w))

@@ -1,0 +1,179 @@
+"""Parity of the CUDA path with the CPU oracle, called through the C ABI (ctypes), on the
+golden vectors of the reference and on seeded synthetic inputs.
+
+Bars: forward, leaf map, margin map and reachability are bit-exact.  The default backward
+matches within rtol 1e-5 of the per-element term magnitude (its summation order is free);
+the deterministic backward is bit-exact against the oracle, whose loops are the reference
+CPU loops, and identical from run to run.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import forest_case, forest_case_ids, random_forest_inputs
+from oracle import hinge_oracle as ho
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cabi():
+    from hingetreefortorch_b200 import _cabi
+    _cabi.library()
+    return _cabi
+
+
+def dev(*arrays):
+    return [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in arrays]
+
+
+def equal(t, a):
+    return np.array_equal(t.cpu().numpy(), a, equal_nan=True)
+
+
+def grad_close(t, ref, scale):
+    """|t - ref| <= 1e-5 * scale, scale = sum of |terms| that went into each element."""
+    got = t.cpu().numpy().astype(np.float64)
+    return np.all(np.abs(got - ref.astype(np.float64)) <= 1e-5 * scale + 1e-30)
+
+
+def check_case(cabi, kind, x, thr, ord_, w, g, expect=None):
+    if expect is None:
+        leaf, margin, mord, reach = ho.maps(kind, x, thr, ord_, w)
+        gx, gthr, gw = ho.backward(kind, x, thr, ord_, w, g)
+        expect = dict(out=ho.forward(kind, x, thr, ord_, w), leaf=leaf, margin=margin, margin_ord=mord, reach=reach,
+                      gx=gx, gthr=gthr, gw=gw)
+    dx, dthr, dord, dw, dg = dev(x, thr, ord_, w, g)
+    f = cabi.Forest(kind, dx, dw)
+    assert equal(f.forward(dx, dthr, dord, dw), expect["out"])
+    assert equal(f.leafmap(dx, dthr, dord), expect["leaf"])
+    margin, mord = f.marginmap(dx, dthr, dord)
+    assert equal(margin, expect["margin"]) and equal(mord, expect["margin_ord"])
+    assert equal(f.reachability(dx, dthr, dord), expect["reach"])
+    assert f.ordinal_flags() == 0
+
+    # magnitude of what was summed into each gradient element (for the tolerance)
+    ax, athr, aw = ho.backward(kind, x, thr, ord_, np.abs(w), np.abs(g))
+    athr = np.abs(athr)
+    gx, gthr, gw = f.backward(dx, dthr, dord, dw, dg)
+    finite = np.isfinite(expect["gx"]).all() and np.isfinite(expect["gthr"]).all() and np.isfinite(expect["gw"]).all()
+    if finite:
+        assert grad_close(gx, expect["gx"], np.abs(ax))
+        assert grad_close(gthr, expect["gthr"], athr)
+        assert grad_close(gw, expect["gw"], aw)
+
+    fd = cabi.Forest(kind, dx, dw, deterministic=True)
+    first = fd.backward(dx, dthr, dord, dw, dg)
+    for t, name in zip(first, ("gx", "gthr", "gw")):
+        assert equal(t, expect[name]), name
+    second = fd.backward(dx, dthr, dord, dw, dg)
+    for a, b in zip(first, second):
+        assert torch.equal(a, b) or (torch.isnan(a) == torch.isnan(b)).all()
+
+
+@pytest.mark.parametrize("idx", forest_case_ids())
+def test_golden_vectors_of_the_reference(cabi, golden_forest, idx):
+    c = forest_case(golden_forest, idx)
+    check_case(cabi, c["kind"], c["x"], c["thr"], c["ord"], c["w"], c["g"], expect=c)
+
+
+SHAPES = [
+    # B, C, inner, T, depth, extra
+    (1, 1, (), 1, 1, ()),
+    (31, 9, (), 7, 2, ()),
+    (32, 128, (), 8, 8, ()),
+    (33, 256, (), 9, 5, (1,)),
+    (100, 1000, (), 100, 7, (1,)),
+    (257, 128, (), 65, 8, ()),
+    (64, 16, (), 33, 10, (10,)),
+    (5, 3, (17,), 6, 3, (2,)),
+    (2, 7, (8, 8), 5, 4, (2, 2)),
+    (3, 5, (3,), 4, 12, ()),
+]
+
+
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+@pytest.mark.parametrize("shape", SHAPES, ids=[str(s) for s in SHAPES])
+def test_synthetic_shapes(cabi, kind, shape):
+    B, C, inner, T, depth, extra = shape
+    x, thr, ord_, w = random_forest_inputs(2 * SHAPES.index(shape) + (kind == "fern"), kind, B, C, inner, T, depth, extra)
+    g = np.random.default_rng(1).standard_normal((B, T) + inner + extra).astype(np.float32)
+    check_case(cabi, kind, x, thr, ord_, w, g)
+
+
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+def test_ties_zero_margins_and_hot_ordinals(cabi, kind):
+    # quantised values give exact ties and exact zeros; all ordinals on two features makes every
+    # sample of a tree hit the same gradient elements
+    x, thr, ord_, w = random_forest_inputs(5, kind, 200, 6, (), 12, 6, (3,), quantise=True)
+    ord_ = ord_ % 2
+    g = np.random.default_rng(2).standard_normal((200, 12, 3)).astype(np.float32)
+    check_case(cabi, kind, x, thr, ord_, w, g)
+
+
+def test_fern_depth_20(cabi):
+    x, thr, ord_, w = random_forest_inputs(9, "fern", 50, 40, (), 2, 20, ())
+    g = np.ones((50, 2), np.float32)
+    check_case(cabi, "fern", x, thr, ord_, w, g)
+
+
+def test_empty_batch_and_no_trees(cabi):
+    for (B, T) in [(0, 4), (3, 0)]:
+        x, thr, ord_, w = random_forest_inputs(1, "tree", B, 5, (), T, 3, ())
+        dx, dthr, dord, dw = dev(x, thr, ord_, w)
+        f = cabi.Forest("tree", dx, dw)
+        assert tuple(f.forward(dx, dthr, dord, dw).shape) == (B, T)
+        gx, gthr, gw = f.backward(dx, dthr, dord, dw, torch.zeros(B, T, device="cuda"))
+        assert float(gx.abs().sum()) == 0 and float(gthr.abs().sum()) == 0 and float(gw.abs().sum()) == 0
+
+
+def test_out_of_range_ordinals_are_flagged_and_never_dereferenced(cabi):
+    x, thr, ord_, w = random_forest_inputs(3, "tree", 16, 8, (), 4, 3, ())
+    bad = ord_.copy()
+    bad[1, 2] = 8
+    bad[2, 0] = -1
+    dx, dthr, dord, dw = dev(x, thr, bad, w)
+    f = cabi.Forest("tree", dx, dw)
+    out = f.forward(dx, dthr, dord, dw)
+    assert f.ordinal_flags() & cabi.HT_FLAG_ORDINAL_RANGE
+    # the offending ordinals were read as 0: same result as the clamped parameters
+    clamped = bad.copy()
+    clamped[1, 2] = 0
+    clamped[2, 0] = 0
+    assert equal(out, ho.forward("tree", x, thr, clamped, w))
+
+
+def test_workspace_is_checked(cabi):
+    import ctypes
+    x, thr, ord_, w = random_forest_inputs(3, "tree", 4, 8, (), 4, 3, ())
+    dx, dthr, dord, dw = dev(x, thr, ord_, w)
+    f = cabi.Forest("tree", dx, dw)
+    out = torch.empty(4, 4, device="cuda")
+    lib = cabi.library()
+    args = (ctypes.byref(f.problem), cabi._ptr(dx), cabi._ptr(dthr), cabi._ptr(dord), cabi._ptr(dw), cabi._ptr(out))
+    rc = lib.ht_forest_forward_f32(*args, cabi._ptr(f.workspace), ctypes.c_size_t(8), cabi._ptr(f.status), None)
+    assert rc == -4
+    rc = lib.ht_forest_forward_f32(*args, ctypes.c_void_p(f.workspace.data_ptr() + 4), ctypes.c_size_t(1 << 20),
+                                   cabi._ptr(f.status), None)
+    assert rc == -4
+
+
+def test_large_batch_properties(cabi):
+    """At a size the oracle cannot finish quickly: a random slice is bit-exact, shards concatenate to
+    the whole (the multi-GPU decomposition), and reachability sums to the number of positions."""
+    B, C, T, depth = 65536, 128, 256, 8
+    x, thr, ord_, w = random_forest_inputs(11, "tree", B, C, (), T, depth, ())
+    dx, dthr, dord, dw = dev(x, thr, ord_, w)
+    f = cabi.Forest("tree", dx, dw)
+    out = f.forward(dx, dthr, dord, dw)
+    rows = np.random.default_rng(0).choice(B, 64, replace=False)
+    assert np.array_equal(out[torch.from_numpy(rows).cuda()].cpu().numpy(), ho.forward("tree", x[rows], thr, ord_, w))
+    halves = []
+    for part in (dx[: B // 2].contiguous(), dx[B // 2:].contiguous()):
+        halves.append(cabi.Forest("tree", part, dw).forward(part, dthr, dord, dw))
+    assert torch.equal(torch.cat(halves), out)
+    reach = f.reachability(dx, dthr, dord)
+    assert reach.sum(dim=1).eq(B).all()
+    leaf = f.leafmap(dx, dthr, dord)
+    counts = torch.zeros_like(reach).scatter_add_(1, leaf.t().contiguous(), torch.ones(T, B, dtype=torch.int64, device="cuda"))
+    assert torch.equal(counts, reach)

@@ -1,0 +1,100 @@
+"""Host-side logic of the drop-in that needs no GPU: the torch extension loads, exposes the
+reference's operator names, screens arguments with the reference's exception types, and the
+threshold-hygiene utilities reproduce the reference on the golden vectors."""
+import numpy as np
+import pytest
+import torch
+
+from hingetreefortorch_b200._ext import hingetree_cpp
+from hingetreefortorch_b200 import HingeTree as F, RandomHingeForest as R
+
+REFERENCE_OPERATORS = """
+tree_forward tree_backward tree_backward_deterministic sparse_tree_backward tree_check_thresholds tree_fix_thresholds
+tree_reachability tree_leafmap tree_marginmap tree_speedtest tree_init_medians tree_init_greedy
+fern_forward fern_backward fern_backward_deterministic sparse_fern_backward fern_check_thresholds fern_fix_thresholds
+fern_reachability fern_leafmap fern_marginmap fern_speedtest fern_init_medians
+tree_conv1d_forward tree_conv2d_forward tree_conv3d_forward tree_conv1d_backward tree_conv2d_backward tree_conv3d_backward
+fern_conv1d_forward fern_conv2d_forward fern_conv3d_forward fern_conv1d_backward fern_conv2d_backward fern_conv3d_backward
+trie_forward trie_backward trie_init_medians
+tree_fused_linear_forward tree_fused_linear_backward sparse_tree_fused_linear_backward
+fern_fused_linear_forward fern_fused_linear_backward sparse_fern_fused_linear_backward
+tree_fusion_forward tree_fusion_backward fern_fusion_forward fern_fusion_backward
+tree_fusion_fused_linear_forward tree_fusion_fused_linear_backward
+fern_fusion_fused_linear_forward fern_fusion_fused_linear_backward contract expand
+""".split()
+
+
+def test_extension_exposes_the_reference_operator_names():
+    assert len(REFERENCE_OPERATORS) == 54
+    for name in REFERENCE_OPERATORS:
+        assert callable(getattr(hingetree_cpp, name)), name
+
+
+def test_threshold_hygiene_matches_reference(golden_forest):
+    g = golden_forest
+    thr = torch.from_numpy(g["hygiene_thr_before"].copy())
+    ord_ = torch.from_numpy(g["hygiene_ord"])
+    w = torch.zeros(thr.shape[0], thr.shape[1] + 1)
+    assert hingetree_cpp.tree_check_thresholds(thr, ord_, w) == g["hygiene_check_before"].tolist()
+    assert hingetree_cpp.tree_fix_thresholds(thr, ord_, w) == g["hygiene_changed"].tolist()
+    assert np.array_equal(thr.numpy(), g["hygiene_thr_after"])
+    assert hingetree_cpp.tree_check_thresholds(thr, ord_, w) == g["hygiene_check_after"].tolist()
+    assert all(g["hygiene_check_after"].tolist())
+    # ferns: nothing to check, nothing to fix
+    thr_f, ord_f, w_f = torch.randn(3, 4), torch.randint(0, 5, (3, 4)), torch.randn(3, 16)
+    assert hingetree_cpp.fern_check_thresholds(thr_f, ord_f, w_f) == [True] * 3
+    assert hingetree_cpp.fern_fix_thresholds(thr_f, ord_f, w_f) == [False] * 3
+
+
+def test_argument_screening_uses_the_reference_exception_types():
+    x, thr, ord_, w = torch.randn(4, 5), torch.randn(3, 7), torch.randint(0, 5, (3, 7)), torch.randn(3, 8)
+    with pytest.raises(ValueError):  # dtype mismatch
+        hingetree_cpp.tree_forward(x.double(), thr, ord_, w)
+    with pytest.raises(ValueError):  # ordinals must be int64
+        hingetree_cpp.tree_forward(x, thr, ord_.int(), w)
+    with pytest.raises(ValueError):  # not contiguous
+        hingetree_cpp.tree_forward(x.t().contiguous().t(), thr, ord_, w)
+    with pytest.raises(RuntimeError, match="CUDA devices only"):  # no CPU evaluation path
+        hingetree_cpp.tree_forward(x, thr, ord_, w)
+    with pytest.raises(RuntimeError, match="inOrdinals never has a gradient"):
+        hingetree_cpp.tree_backward(x, True, thr, True, ord_, True, w, True, torch.randn(4, 3))
+    with pytest.raises(ValueError):
+        hingetree_cpp.tree_check_thresholds(thr, ord_.int(), w)
+    with pytest.raises(RuntimeError):  # 7 thresholds do not fit 16 leaves
+        hingetree_cpp.tree_check_thresholds(thr, ord_, torch.randn(3, 16))
+
+
+def test_modules_construct_like_the_reference():
+    torch.manual_seed(3)
+    m = R.RandomHingeForest(10, 4, 3, extra_outputs=1)
+    assert m.weights.shape == (4, 8, 1) and m.thresholds.shape == (4, 7) and m.ordinals.dtype == torch.long
+    assert not m.ordinals.requires_grad and all(m.check_thresholds())
+    assert list(m.state_dict().keys()) == ["weights", "thresholds", "ordinals"]
+    assert R.RandomHingeFern(10, 4, 5, extra_outputs=[2, 3]).weights.shape == (4, 32, 2, 3)
+    seq = R.RandomHingeForest(12700, 100, 7, init_type="sequential")
+    assert torch.equal(seq.ordinals, torch.arange(12700).view(100, 127))
+    fl = R.RandomHingeForestFusedLinear(10, 6, 3, 4, bias=False)
+    assert fl.linear_weights.shape == (3, 6) and not fl.linear_bias.requires_grad
+    fu = R.RandomHingeFernFusion(5, 3, 6, 4)
+    assert fu.ordinals.shape == (6, 4) and int(fu.ordinals.max()) < 8
+    conv = R.HingeTreeConv2d(3, 4, 2, 3, padding=1, extra_outputs=5)
+    assert conv.thresholds.shape == (4, 3, 3) and conv.weights.shape == (4, 3, 4, 5) and int(conv.ordinals.max()) < 9
+    with pytest.raises(RuntimeError):
+        R.RandomHingeForest(10, 4, 3, init_type="nope")
+    # checkpoints that store the ordinals as float32 load and are cast back to long
+    state = {k: v.clone() for k, v in m.state_dict().items()}
+    state["ordinals"] = state["ordinals"].float()
+    m2 = R.RandomHingeForest(10, 4, 3, extra_outputs=1)
+    m2.ordinals = torch.nn.Parameter(m2.ordinals.float(), requires_grad=False)
+    m2.load_state_dict(state)
+    assert m2.ordinals.dtype == torch.long and torch.equal(m2.ordinals, m.ordinals)
+
+
+def test_function_layer_names():
+    for name in ["HingeTree", "HingeFern", "SparseHingeTree", "SparseHingeFern", "HingeTreeFusedLinear",
+                 "HingeFernFusedLinear", "SparseHingeTreeFusedLinear", "SparseHingeFernFusedLinear", "HingeTreeFusion",
+                 "HingeFernFusion", "HingeTreeFusionFusedLinear", "HingeFernFusionFusedLinear", "HingeTreeConv1d",
+                 "HingeTreeConv2d", "HingeTreeConv3d", "HingeFernConv1d", "HingeFernConv2d", "HingeFernConv3d",
+                 "HingeTrie", "contract", "expand", "Contract", "Expand"]:
+        assert hasattr(F, name), name
+    assert issubclass(F.SparseHingeTree, F.HingeTree) and issubclass(F.HingeTreeFusedLinear, F.HingeTree)
