@@ -238,7 +238,7 @@ def our_arm(a, wl):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    B = wl["B"]
+    B = a.rows or wl["B"]
     thr, ord_, w = [t.to(device) for t in make_params(wl)]
     x_host = make_x(wl, B, rank)
     x = x_host.to(device)
@@ -287,6 +287,13 @@ def our_arm(a, wl):
     elapsed_ms = float(t.item())
     evals = B * wl["T"]
     value = evals * world * a.steps / (elapsed_ms * 1e-3)
+
+    if a.kernel_only:
+        if rank == 0:
+            print(json.dumps({"kernel_only": True, "rows": B, "ms_per_step": elapsed_ms / a.steps, "value": value}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- end to end through the reference-facing operator, host buffers in and out -----------
     fwd_op = getattr(hingetree_cpp, wl["kind"] + "_forward")
@@ -352,7 +359,7 @@ def our_arm(a, wl):
             "value": value, "unit": "tree-evals/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": elapsed_ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl["name"], "rows_per_gpu": B, "l2": "inputs and outputs exceed L2 (126 MB)"
+            "config": {"workload": wl["name"] + ("" if B == wl["B"] else " (rows overridden)"), "rows_per_gpu": B, "l2": "inputs and outputs exceed L2 (126 MB)"
                        if bytes_per_launch > 4 * 126e6 else "working set fits L2",
                        "parallelism": "batch-sharded x%d, replicated parameters" % world},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -378,6 +385,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--rows", type=int, default=0, help="rows per GPU instead of the workload's (profiler captures)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="time the device-resident step only (profiler captures): no end-to-end and no CPU leg")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3) if a.impl == "ours" else a.warmup
     wl = WORKLOADS[a.workload]

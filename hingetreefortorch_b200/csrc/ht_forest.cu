@@ -234,6 +234,11 @@ __global__ void __launch_bounds__(32) forest_backward_params_ordered_kernel(Fore
     for (int64_t t = lane; t < LM; t += 32) gw[j * LM + t] = w_bins[t];
 }
 
+// The workspace starts with the compact int32 ordinals; the tile kernel's records follow.
+inline size_t ordinals_bytes(const ht_forest_problem *p) {
+  return align_up((size_t)(p->T * threshold_count(p->kind, p->depth)) * sizeof(int32_t), 256);
+}
+
 inline unsigned blocks_for(int64_t n, int block) { return (unsigned)((n + block - 1) / block); }
 
 struct Prepared {
@@ -248,7 +253,11 @@ int prepare(const ht_forest_problem *p, const float *x, const float *thr, const 
             Prepared &out) {
   const int rc = check_forest_problem(p);
   if (rc != HT_OK) return rc;
-  if (x == nullptr || thr == nullptr || ord == nullptr || (need_w && w == nullptr)) return HT_ERR_INVALID_ARGUMENT;
+  // a null pointer is only acceptable for a tensor without elements
+  const int64_t decisions = p->T * threshold_count(p->kind, p->depth);
+  if ((x == nullptr && p->B * p->C * p->K > 0) || ((thr == nullptr || ord == nullptr) && decisions > 0) ||
+      (need_w && w == nullptr && p->T * p->M > 0))
+    return HT_ERR_INVALID_ARGUMENT;
   const size_t need = ht_forest_workspace_bytes(p);
   if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
     return HT_ERR_WORKSPACE;
@@ -320,8 +329,7 @@ const char *ht_status_string(int status) {
 
 size_t ht_forest_workspace_bytes(const ht_forest_problem *p) {
   if (check_forest_problem(p) != HT_OK) return 0;
-  const int64_t n = p->T * threshold_count(p->kind, p->depth);
-  return align_up((size_t)n * sizeof(int32_t), 256) + 256;
+  return ordinals_bytes(p) + forward_tiled_workspace_bytes(p) + 256;
 }
 
 int ht_forest_forward_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
@@ -330,9 +338,10 @@ int ht_forest_forward_f32(const ht_forest_problem *p, const float *x, const floa
   Prepared pr;
   const int rc = prepare(p, x, thr, ord, w, true, workspace, workspace_bytes, status_word, stream, pr);
   if (rc != HT_OK) return rc;
-  if (out == nullptr) return HT_ERR_INVALID_ARGUMENT;
   if (pr.evals * p->M == 0) return HT_OK;
-  const int trc = forward_tiled(p, x, thr, pr.args.ord, w, out, pr.stream);
+  if (out == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  const int trc = forward_tiled(p, x, thr, pr.args.ord, w, out, static_cast<unsigned char *>(workspace) + ordinals_bytes(p),
+                                status_word, pr.stream);
   if (trc != HT_ERR_UNSUPPORTED) return trc;
   return launch_any<MODE_FORWARD>(p, pr, out, nullptr);
 }
@@ -343,7 +352,7 @@ int ht_forest_leafmap_f32(const ht_forest_problem *p, const float *x, const floa
   Prepared pr;
   const int rc = prepare(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
   if (rc != HT_OK) return rc;
-  if (leaf == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  if (leaf == nullptr && pr.evals > 0) return HT_ERR_INVALID_ARGUMENT;
   return launch_any<MODE_LEAFMAP>(p, pr, nullptr, leaf);
 }
 
@@ -353,7 +362,7 @@ int ht_forest_marginmap_f32(const ht_forest_problem *p, const float *x, const fl
   Prepared pr;
   const int rc = prepare(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
   if (rc != HT_OK) return rc;
-  if (margin == nullptr || margin_ord == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  if ((margin == nullptr || margin_ord == nullptr) && pr.evals > 0) return HT_ERR_INVALID_ARGUMENT;
   return launch_any<MODE_MARGINMAP>(p, pr, margin, margin_ord);
 }
 
@@ -363,7 +372,7 @@ int ht_forest_reachability_f32(const ht_forest_problem *p, const float *x, const
   Prepared pr;
   const int rc = prepare(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
   if (rc != HT_OK) return rc;
-  if (counts == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  if (counts == nullptr && pr.args.T > 0) return HT_ERR_INVALID_ARGUMENT;
   if (pr.args.T * pr.args.L > 0)
     HT_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int64_t) * (size_t)(pr.args.T * pr.args.L), pr.stream));
   return launch_any<MODE_REACH>(p, pr, nullptr, counts);
@@ -375,7 +384,7 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
   Prepared pr;
   const int rc = prepare(p, x, thr, ord, w, true, workspace, workspace_bytes, status_word, stream, pr);
   if (rc != HT_OK) return rc;
-  if (g == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  if (g == nullptr && pr.evals * p->M > 0) return HT_ERR_INVALID_ARGUMENT;
   const ForestArgs &a = pr.args;
   if (gx != nullptr && a.B * a.C * a.K > 0)
     HT_CUDA_TRY(cudaMemsetAsync(gx, 0, sizeof(float) * (size_t)(a.B * a.C * a.K), pr.stream));

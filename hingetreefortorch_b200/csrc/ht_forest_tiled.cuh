@@ -5,10 +5,14 @@
 
 namespace ht {
 
+// Bytes of per-tree records the tile kernel needs in the workspace (0 when the shape does not qualify).
+size_t forward_tiled_workspace_bytes(const ht_forest_problem *p);
+
 // Runs the forward with the tile kernel when the shape qualifies; returns HT_ERR_UNSUPPORTED
 // (and launches nothing) when it does not, so that the caller can use the any-shape kernel.
-// `ord` are the compact (validated, clamped) int32 ordinals.
+// `ord` are the compact (validated, clamped) int32 ordinals; `records` is 256-byte aligned
+// scratch of forward_tiled_workspace_bytes() bytes.
 int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
-                  float *out, cudaStream_t stream);
+                  float *out, void *records, uint32_t *status_word, cudaStream_t stream);
 
 }  // namespace ht

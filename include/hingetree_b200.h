@@ -44,6 +44,7 @@ typedef enum ht_status {
 
 /* bits OR-ed into the device status word */
 #define HT_FLAG_ORDINAL_RANGE 1u /* an ordinal was < 0 or >= C (reference: RuntimeError) */
+#define HT_FLAG_PIPELINE_TIMEOUT 0x80000000u /* a bounded wait inside a kernel ran out; outputs are incomplete */
 
 #define HT_KIND_TREE 0 /* complete binary tree: HingeTreeCommon<>  (HingeTreeCommon.h:129) */
 #define HT_KIND_FERN 1 /* oblivious fern:       HingeFernCommon<>  (HingeTreeCommon.h:42)  */

@@ -155,3 +155,31 @@ int ho_backward(int kind, const float *x, const float *vec, int64_t Cv, const fl
       }
   return 0;
 }
+
+/* Test helper (no counterpart in the reference): the sum of |term| that ho_backward adds into
+ * every gradient element, in double precision.  Tests scale their floating point tolerance
+ * for the non-deterministic backward with it. */
+int ho_backward_magnitudes(int kind, const float *x, const float *thr, const int64_t *ord, const float *w,
+                           const float *g, double *ax, double *athr, double *aw,
+                           int64_t B, int64_t C, int64_t K, int64_t T, int64_t L, int64_t M) {
+  const int d = ho_depth_of(L);
+  if (d < 0) return -1;
+  const int64_t N = ho_threshold_count(kind, d);
+  for (int64_t i = 0; i < B; ++i)
+    for (int64_t j = 0; j < T; ++j)
+      for (int64_t k = 0; k < K; ++k) {
+        ho_feat f = { x + (i * C) * K + k, K, NULL, C };
+        const ho_path p = ho_traverse(kind, &f, thr + j * N, ord + j * N, d);
+        const double sign = (double)((0.0f < p.margin) - (p.margin < 0.0f));
+        const float *wl = w + (j * L + p.key) * M;
+        const float *gl = g + ((i * T + j) * K + k) * M;
+        const int64_t c = ord[j * N + p.vertex];
+        for (int64_t m = 0; m < M; ++m) {
+          const double t = fabs(sign * (double)wl[m] * (double)gl[m]);
+          ax[(i * C + c) * K + k] += t;
+          athr[j * N + p.vertex] += t;
+          aw[(j * L + p.key) * M + m] += fabs((double)p.margin * (double)gl[m]);
+        }
+      }
+  return 0;
+}

@@ -104,3 +104,15 @@ def backward(kind, x, thr, ord_, w, g, vec=None, need=(True, True, True)):
     if vec is None:
         return gx, gthr, gw
     return gx, gvec, gthr, gw
+
+
+def backward_magnitudes(kind, x, thr, ord_, w, g):
+    """Sum of |term| added into each element of (gx, gthr, gw), float64: the scale of a tolerance."""
+    x, thr, ord_, w, g = _f32(x), _f32(thr), _i64(ord_), _f32(w), _f32(g)
+    B, C, K, T, L, M = _dims(x, w)
+    ax, athr, aw = np.zeros(x.shape), np.zeros(thr.shape), np.zeros(w.shape)
+    rc = lib().ho_backward_magnitudes(_KIND[kind], _p(x), _p(thr), _p(ord_), _p(w), _p(g), _p(ax), _p(athr), _p(aw),
+                                      _i(B), _i(C), _i(K), _i(T), _i(L), _i(M))
+    if rc != 0:
+        raise ValueError("leaf count is not a power of two")
+    return ax, athr, aw
