@@ -53,7 +53,7 @@ bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
   plan.ord_bytes = p->C <= 256 ? 1 : 2;
   plan.thr_bytes = round16((int)(4 * N));
   plan.w_offset = plan.thr_bytes + round16((int)(plan.ord_bytes * N));
-  plan.rec_bytes = plan.w_offset + (int)(4 * L);
+  plan.rec_bytes = round16(plan.w_offset + (int)(4 * L));
   for (int S = 256; S >= 32; S >>= 1) {
     const int slots = kWarps / (S / 32);
     for (int G = 32; G >= slots && G >= 4; G >>= 1) {
@@ -71,8 +71,9 @@ bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
 
 __device__ __forceinline__ uint32_t bit_reverse(uint32_t v, int bits) { return __brev(v) >> (32 - bits); }
 
-// One thread per record element: thresholds, compact ordinals, leaf weights permuted so that
-// the heap index reached by the traversal addresses them directly (trees), or as given (ferns).
+// One thread per record element: thresholds, compact ordinals, and the leaf weights permuted so
+// that the path bits in the order the traversal collects them (root first, most significant)
+// address them directly.
 template <typename OrdT>
 __global__ void repack_records_kernel(const float *__restrict__ thr, const int32_t *__restrict__ ord,
                                       const float *__restrict__ w, unsigned char *__restrict__ records, int kind,
@@ -86,11 +87,12 @@ __global__ void repack_records_kernel(const float *__restrict__ thr, const int32
   const int64_t r = e - j * per_tree;
   unsigned char *rec = records + j * rec_bytes;
   if (r < N) {
-    reinterpret_cast<float *>(rec)[r] = thr[j * N + r];
+    const float t = thr[j * N + r];
+    reinterpret_cast<float *>(rec)[r] = t == 0.0f ? 0.0f : t;  // -0 becomes +0
     reinterpret_cast<OrdT *>(rec + thr_bytes)[r] = (OrdT)ord[j * N + r];
   } else {
     const int64_t h = r - N;  // slot in the record
-    const int64_t key = kind == TREE ? (int64_t)bit_reverse((uint32_t)h, depth) : h;
+    const int64_t key = (int64_t)bit_reverse((uint32_t)h, depth);  // slot h holds the leaf whose key is h reversed
     reinterpret_cast<float *>(rec + w_offset)[h] = w[j * L + key];
   }
 }
@@ -127,6 +129,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     if (done) return true;
   }
   return false;
+}
+
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+
+template <typename OrdT>
+__device__ __forceinline__ uint32_t lds_ord(uint32_t addr) {
+  uint32_t v;
+  if (sizeof(OrdT) == 1)
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  else
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
 }
 
 struct TiledArgs {
@@ -193,8 +211,13 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
   }
   __syncthreads();
 
-  const float *xl = xs + sample_group * 32 + lane;  // feature c of this lane's sample is xl[c * S]
-  constexpr int N = KIND == FERN ? DEPTH : (1 << DEPTH) - 1;
+  // feature c of this lane's sample sits at shared address xl_addr + c * x_stride
+  const uint32_t xl_addr = smem_addr(xs + sample_group * 32 + lane);
+  const uint32_t x_stride = (uint32_t)S * 4u;
+  constexpr uint32_t kN = KIND == FERN ? DEPTH : (1u << DEPTH) - 1u;
+  constexpr uint32_t kThrBytes = (4u * kN + 15u) & ~15u;
+  constexpr uint32_t kWOffset = kThrBytes + (((uint32_t)sizeof(OrdT) * kN + 15u) & ~15u);
+  constexpr uint32_t kRec = (kWOffset + 4u * (1u << DEPTH) + 15u) & ~15u;
   bool timed_out = false;
 
   for (int group = 0; group < num_groups; ++group) {
@@ -204,44 +227,48 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
       if (tid == 0 && a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
       return;
     }
-    const unsigned char *base = params + (size_t)(group & 1) * G * a.rec_bytes;
     const int in_group = (int)min((int64_t)G, a.T - (int64_t)group * G);
 
-    // two trees per thread per pass
+    // Two trees per thread per pass.  All addresses are 32-bit shared-memory addresses.  The
+    // vertex index is kept 1-based (root = 1, children 2v and 2v+1), so that one funnel shift
+    // appends the branch bit: the bit is the sign of (threshold - feature), which is set
+    // exactly when the margin is positive (records hold +0 for a -0 threshold, and an add
+    // that yields NaN yields the canonical positive NaN, so NaN margins go left as required).
+    const uint32_t base_addr = smem_addr(params) + (uint32_t)(group & 1) * (uint32_t)(G * kRec);
     for (int t0 = slot; t0 < in_group; t0 += 2 * slots) {
       const int t1 = t0 + slots;
       const bool has1 = t1 < in_group;
-      const unsigned char *rec[2] = {base + (size_t)t0 * a.rec_bytes, base + (size_t)(has1 ? t1 : t0) * a.rec_bytes};
-      uint32_t v[2] = {0u, 0u};
-      uint32_t key[2] = {0u, 0u};
+      const uint32_t rec[2] = {base_addr + (uint32_t)t0 * kRec, base_addr + (uint32_t)(has1 ? t1 : t0) * kRec};
+      uint32_t v[2] = {1u, 1u};
       float best[2], first[2];
 #pragma unroll
       for (int l = 0; l < DEPTH; ++l) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-          const uint32_t at = KIND == FERN ? (uint32_t)l : v[u];
-          const float thr = reinterpret_cast<const float *>(rec[u])[at];
-          const uint32_t c = reinterpret_cast<const OrdT *>(rec[u] + a.thr_bytes)[at];
-          const float m = xl[c * S] - thr;
-          const float am = fabsf(m);
+          float thr;
+          uint32_t c;
+          if (KIND == FERN) {
+            thr = lds_f32(rec[u] + 4u * l);
+            c = lds_ord<OrdT>(rec[u] + kThrBytes + (uint32_t)sizeof(OrdT) * l);
+          } else {
+            thr = lds_f32(rec[u] + 4u * v[u] - 4u);
+            c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * v[u] + (kThrBytes - (uint32_t)sizeof(OrdT)));
+          }
+          const float nm = thr - lds_f32(c * x_stride + xl_addr);
+          const float am = fabsf(nm);
           if (l == 0) {
             best[u] = am;
             first[u] = am;
           } else {
             best[u] = fminf(best[u], am);
           }
-          const uint32_t bit = m > 0.0f ? 1u : 0u;
-          if (KIND == FERN)
-            key[u] |= bit << l;
-          else
-            v[u] = 2 * v[u] + 1 + bit;
+          v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
         }
       }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         if (u == 1 && !has1) break;
-        const uint32_t leaf = KIND == FERN ? key[u] : v[u] - (uint32_t)N;
-        const float wv = reinterpret_cast<const float *>(rec[u] + a.w_offset)[leaf];
+        const float wv = lds_f32(rec[u] + 4u * v[u] + (kWOffset - 4u * (1u << DEPTH)));
         const float am = (first[u] != first[u]) ? first[u] : best[u];
         outs[(sample_group * 32 + lane) * (G + 1) + (u == 0 ? t0 : t1)] = am * wv;
       }

@@ -176,3 +176,38 @@ def test_large_batch_properties(cabi):
     leaf = f.leafmap(dx, dthr, dord)
     counts = torch.zeros_like(reach).scatter_add_(1, leaf.t().contiguous(), torch.ones(T, B, dtype=torch.int64, device="cuda"))
     assert torch.equal(counts, reach)
+
+
+TILED_SHAPES = [
+    # B, C, T, depth: large enough for the shared-memory tile kernel (tabular input, one output per leaf)
+    (1000, 128, 40, 8),
+    (513, 64, 70, 5),
+    (300, 300, 129, 7),   # more than 256 features: 16-bit compact ordinals
+    (257, 1000, 132, 7),  # wide rows: small sample tiles
+    (4096, 16, 9, 10),
+    (2048, 32, 17, 1),
+]
+
+
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+@pytest.mark.parametrize("shape", TILED_SHAPES, ids=[str(s) for s in TILED_SHAPES])
+def test_tile_kernel_shapes_with_special_values(cabi, kind, shape):
+    """Forward on shapes the tile kernel takes, with NaN, infinities, signed zeros and exact ties
+    planted in the data and in the thresholds; bit-exact against the oracle."""
+    B, C, T, depth = shape
+    x, thr, ord_, w = random_forest_inputs(7 + TILED_SHAPES.index(shape), kind, B, C, (), T, depth, (), quantise=True)
+    rng = np.random.default_rng(3)
+    flat = x.reshape(-1)
+    for value in (np.nan, np.inf, -np.inf, 0.0, -0.0, 1e-42):
+        flat[rng.choice(flat.size, max(4, flat.size // 50), replace=False)] = value
+    tflat = thr.reshape(-1)
+    for value in (np.nan, np.inf, -np.inf, 0.0, -0.0):
+        tflat[rng.choice(tflat.size, max(1, tflat.size // 40), replace=False)] = value
+    dx, dthr, dord, dw = dev(x, thr, ord_, w)
+    f = cabi.Forest(kind, dx, dw)
+    got = f.forward(dx, dthr, dord, dw).cpu().numpy()
+    want = ho.forward(kind, x, thr, ord_, w)
+    assert np.array_equal(got.view(np.uint32) & 0x7fffffff == 0, want.view(np.uint32) & 0x7fffffff == 0)
+    assert np.array_equal(got, want, equal_nan=True)
+    assert np.array_equal(f.leafmap(dx, dthr, dord).cpu().numpy(), ho.maps(kind, x, thr, ord_, w)[0])
+    assert f.ordinal_flags() == 0
