@@ -6,18 +6,28 @@
 //   * the samples' features sit in shared memory feature-major, xs[c][s]: lane l of a warp
 //     always reads bank l whatever feature its current vertex tests, so the data gather never
 //     conflicts although the 32 lanes are at 32 different vertices;
-//   * a warp is (sample group, tree slot): S/32 sample groups, 32/(S/32) slots; within a tree
-//     group a slot takes every `slots`-th tree, two at a time per thread for instruction-level
-//     parallelism (the traversal is one dependent chain of shared-memory loads per level);
-//   * tree parameters arrive as per-tree records {thresholds, uint8/uint16 feature indices,
-//     leaf weights in heap order}, written once per call by a tiny repack kernel, and are
-//     streamed into shared memory in groups with 1-D bulk async copies (cp.async.bulk, the TMA
-//     engine) completing on an mbarrier, double buffered against the traversal;
-//   * the per-group results are staged in shared memory and leave as full-sector row segments.
+//   * a warp is (sample group, slot): S/32 sample groups of 32 samples, 32/(S/32) slots.  Trees
+//     are processed in groups of G; inside a group slot q owns G/slots consecutive trees and
+//     walks them all at once (independent dependent-load chains hide shared-memory latency);
+//   * tree parameters arrive as per-tree records {root and its two children for a single
+//     broadcast load, thresholds, uint8/uint16 feature indices, leaf weights in path order},
+//     written once per call by a small repack kernel, and are streamed into shared memory with
+//     1-D bulk async copies (cp.async.bulk, the TMA engine) completing on an mbarrier.  Two
+//     buffers; the last warp to finish a group issues the copy that refills its buffer, so no
+//     warp ever waits for another in order to keep the pipeline fed;
+//   * results of a group are transposed through a per-sample-group staging area (named
+//     barriers over the 4..32 warps of the sample group only) and leave as row segments.
 //
 // Only the smallest |margin| matters in the forward, so the minimum is tracked on absolute
 // values.  CUDA's fminf ignores a NaN operand; the reference keeps a NaN only when the root
 // margin is NaN, which is patched after the loop.
+//
+// The vertex index is kept 1-based (root 1, children 2v and 2v+1) so that one funnel shift
+// appends the branch bit.  The bit is the sign of (threshold - feature): it is set exactly
+// when the margin (feature - threshold) is positive, given that records hold +0 for a -0
+// threshold and that an add producing NaN produces the canonical positive NaN (so NaN margins
+// go left, as `margin > 0` does in the reference).  |threshold - feature| equals
+// |feature - threshold| bit for bit.
 #include "ht_forest_tiled.cuh"
 
 namespace ht {
@@ -27,42 +37,49 @@ namespace {
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr size_t kSmemBudget = 227 * 1024;
+constexpr int kHeadBytes = 16;  // tree records start with {thr(1), thr(2), thr(3), packed ordinals}
 // Spin limit for the parameter pipeline: far beyond any real copy latency, small enough that a
 // lost copy ends the kernel (with a flag) instead of hanging the device.
 constexpr uint32_t kMaxSpins = 1u << 22;
 
-struct TilePlan {
-  int S;            // samples per tile
-  int G;            // trees per parameter group
-  int ord_bytes;    // 1 or 2
-  int rec_bytes;    // bytes of one tree record (multiple of 16)
-  int thr_bytes;    // offset of the ordinals inside a record
-  int w_offset;     // offset of the leaf weights inside a record
-  size_t smem;      // dynamic shared memory of the tile kernel
-  size_t x_bytes, param_bytes, out_bytes;
+__host__ __device__ constexpr uint32_t round16(uint32_t v) { return (v + 15u) & ~15u; }
+
+// Byte layout of one tree record; the same arithmetic runs on the host (plan) and in the kernel.
+struct RecordLayout {
+  uint32_t thr, ord, w, bytes;
 };
 
-__host__ __device__ inline int round16(int v) { return (v + 15) & ~15; }
+__host__ __device__ constexpr RecordLayout record_layout(int kind, int depth, uint32_t ord_size) {
+  const uint32_t n = kind == FERN ? (uint32_t)depth : (1u << depth) - 1u;
+  const uint32_t thr = kind == FERN ? 0u : (uint32_t)kHeadBytes;
+  const uint32_t ord = thr + round16(4u * n);
+  const uint32_t w = ord + round16(ord_size * n);
+  return RecordLayout{thr, ord, w, round16(w + 4u * (1u << depth))};
+}
+
+struct TilePlan {
+  int S;           // samples per tile
+  int G;           // trees per parameter group
+  int per_warp;    // trees a warp walks at once: G / slots
+  int ord_bytes;   // 1 or 2
+  RecordLayout rec;
+  size_t smem;
+};
 
 bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
   if (p->K != 1 || p->M != 1) return false;
   if (p->C > 65536 || p->depth > 12) return false;
   if (p->B * p->T < 32 * 1024) return false;  // too small to fill the machine with sample tiles
-  const int64_t N = threshold_count(p->kind, p->depth);
-  const int64_t L = ((int64_t)1) << p->depth;
   plan.ord_bytes = p->C <= 256 ? 1 : 2;
-  plan.thr_bytes = round16((int)(4 * N));
-  plan.w_offset = plan.thr_bytes + round16((int)(plan.ord_bytes * N));
-  plan.rec_bytes = round16(plan.w_offset + (int)(4 * L));
+  plan.rec = record_layout(p->kind, p->depth, (uint32_t)plan.ord_bytes);
   for (int S = 256; S >= 32; S >>= 1) {
     const int slots = kWarps / (S / 32);
-    for (int G = 32; G >= slots && G >= 4; G >>= 1) {
+    for (int per_warp = 4; per_warp >= 1; per_warp >>= 1) {
+      const int G = slots * per_warp;
       plan.S = S;
       plan.G = G;
-      plan.x_bytes = (size_t)p->C * S * 4;
-      plan.param_bytes = 2 * (size_t)G * plan.rec_bytes;
-      plan.out_bytes = (size_t)S * (G + 1) * 4;
-      plan.smem = plan.x_bytes + plan.param_bytes + plan.out_bytes + 64;
+      plan.per_warp = per_warp;
+      plan.smem = (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + (size_t)S * (G + 1) * 4 + 64;
       if (plan.smem <= kSmemBudget) return true;
     }
   }
@@ -71,13 +88,12 @@ bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
 
 __device__ __forceinline__ uint32_t bit_reverse(uint32_t v, int bits) { return __brev(v) >> (32 - bits); }
 
-// One thread per record element: thresholds, compact ordinals, and the leaf weights permuted so
-// that the path bits in the order the traversal collects them (root first, most significant)
-// address them directly.
+// One thread per record element.  Leaf weights are permuted so that the path bits in the order
+// the traversal collects them (root first, most significant) address them directly.
 template <typename OrdT>
 __global__ void repack_records_kernel(const float *__restrict__ thr, const int32_t *__restrict__ ord,
                                       const float *__restrict__ w, unsigned char *__restrict__ records, int kind,
-                                      int depth, int64_t T, int rec_bytes, int thr_bytes, int w_offset) {
+                                      int depth, int64_t T, RecordLayout lay) {
   const int64_t N = threshold_count(kind, depth);
   const int64_t L = ((int64_t)1) << depth;
   const int64_t per_tree = N + L;
@@ -85,15 +101,26 @@ __global__ void repack_records_kernel(const float *__restrict__ thr, const int32
   if (e >= T * per_tree) return;
   const int64_t j = e / per_tree;
   const int64_t r = e - j * per_tree;
-  unsigned char *rec = records + j * rec_bytes;
+  unsigned char *rec = records + j * lay.bytes;
   if (r < N) {
-    const float t = thr[j * N + r];
-    reinterpret_cast<float *>(rec)[r] = t == 0.0f ? 0.0f : t;  // -0 becomes +0
-    reinterpret_cast<OrdT *>(rec + thr_bytes)[r] = (OrdT)ord[j * N + r];
+    float t = thr[j * N + r];
+    t = t == 0.0f ? 0.0f : t;  // -0 becomes +0
+    const uint32_t c = (uint32_t)ord[j * N + r];
+    reinterpret_cast<float *>(rec + lay.thr)[r] = t;
+    reinterpret_cast<OrdT *>(rec + lay.ord)[r] = (OrdT)c;
+    if (kind == TREE && r < 3) {  // root and its children again, for one broadcast load
+      reinterpret_cast<float *>(rec)[r] = t;
+      if (sizeof(OrdT) == 1) rec[12 + r] = (unsigned char)c;
+    }
+    if (kind == TREE && r == 0 && N < 3) {  // depth 1: no children; keep the head defined
+      reinterpret_cast<float *>(rec)[1] = 0.0f;
+      reinterpret_cast<float *>(rec)[2] = 0.0f;
+      rec[13] = rec[14] = 0;
+    }
+    if (kind == TREE && r == 0) rec[15] = 0;
   } else {
-    const int64_t h = r - N;  // slot in the record
-    const int64_t key = (int64_t)bit_reverse((uint32_t)h, depth);  // slot h holds the leaf whose key is h reversed
-    reinterpret_cast<float *>(rec + w_offset)[h] = w[j * L + key];
+    const int64_t h = r - N;
+    reinterpret_cast<float *>(rec + lay.w)[h] = w[j * L + (int64_t)bit_reverse((uint32_t)h, depth)];
   }
 }
 
@@ -108,9 +135,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 }
 
 // 1-D bulk copy global -> shared through the TMA engine; completion is counted in bytes on `bar`.
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_addr(dst)),
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(smem_addr(bar))
                : "memory");
 }
@@ -131,9 +157,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   return false;
 }
 
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+
+__device__ __forceinline__ uint4 lds_b128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
 
@@ -153,17 +189,101 @@ struct TiledArgs {
   float *out;
   uint32_t *status_word;
   int64_t B, T;
-  int C, S, G, rec_bytes, thr_bytes, w_offset;
+  int C, S, G, per_warp;
 };
+
+__device__ __forceinline__ uint32_t pick(const uint4 &q, int i) {
+  return i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w;
+}
+
+// Walks NT trees (records at rec[0..NT)) for this lane's sample: |min margin| * leaf weight each.
+template <int KIND, int DEPTH, typename OrdT, int NT>
+__device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr, uint32_t x_stride,
+                                     float (&result)[NT]) {
+  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+  uint32_t v[NT];
+  float best[NT], first[NT];
+  if (KIND == FERN) {
+    // every lane tests the same decisions: thresholds and feature indices come in 16-byte broadcasts
+    constexpr int kPerWord = 4 / (int)sizeof(OrdT);   // feature indices per 32-bit word
+    constexpr int kPerQuad = 4 * kPerWord;            // ... per 16-byte load
+    uint4 tq[NT], oq[NT];
+#pragma unroll
+    for (int u = 0; u < NT; ++u) v[u] = 1u;
+#pragma unroll
+    for (int l = 0; l < DEPTH; ++l) {
+#pragma unroll
+      for (int u = 0; u < NT; ++u) {
+        if (l % 4 == 0) tq[u] = lds_b128(rec[u] + lay.thr + 4u * l);
+        if (l % kPerQuad == 0) oq[u] = lds_b128(rec[u] + lay.ord + (uint32_t)sizeof(OrdT) * l);
+        const uint32_t tbits = pick(tq[u], l % 4);
+        const uint32_t obits = pick(oq[u], (l % kPerQuad) / kPerWord);
+        const uint32_t c = (obits >> (8 * (int)sizeof(OrdT) * (l % kPerWord))) & (sizeof(OrdT) == 1 ? 0xffu : 0xffffu);
+        const float nm = __uint_as_float(tbits) - lds_f32(c * x_stride + xl_addr);
+        const float am = fabsf(nm);
+        if (l == 0) {
+          best[u] = am;
+          first[u] = am;
+        } else {
+          best[u] = fminf(best[u], am);
+        }
+        v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
+      }
+    }
+  } else {
+    constexpr bool kHead = sizeof(OrdT) == 1;  // root + children in one 16-byte broadcast
+    uint4 head[NT];
+#pragma unroll
+    for (int u = 0; u < NT; ++u) {
+      v[u] = 1u;
+      if (kHead) head[u] = lds_b128(rec[u]);
+    }
+#pragma unroll
+    for (int l = 0; l < DEPTH; ++l) {
+#pragma unroll
+      for (int u = 0; u < NT; ++u) {
+        float thr;
+        uint32_t c;
+        if (kHead && l == 0) {
+          thr = __uint_as_float(head[u].x);
+          c = head[u].w & 0xffu;
+        } else if (kHead && l == 1) {
+          thr = __uint_as_float((v[u] & 1u) ? head[u].z : head[u].y);
+          c = __byte_perm(head[u].w, 0u, 0x4440u + (v[u] - 1u));
+        } else {
+          thr = lds_f32(rec[u] + 4u * v[u] + (lay.thr - 4u));
+          c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * v[u] + (lay.ord - (uint32_t)sizeof(OrdT)));
+        }
+        const float nm = thr - lds_f32(c * x_stride + xl_addr);
+        const float am = fabsf(nm);
+        if (l == 0) {
+          best[u] = am;
+          first[u] = am;
+        } else {
+          best[u] = fminf(best[u], am);
+        }
+        v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < NT; ++u) {
+    const float wv = lds_f32(rec[u] + 4u * v[u] + (lay.w - 4u * (1u << DEPTH)));
+    const float am = (first[u] != first[u]) ? first[u] : best[u];
+    result[u] = am * wv;
+  }
+}
 
 template <int KIND, int DEPTH, typename OrdT>
 __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(TiledArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
+  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
   const int S = a.S, G = a.G, C = a.C;
   float *xs = reinterpret_cast<float *>(smem);
   unsigned char *params = smem + (size_t)C * S * 4;
-  float *outs = reinterpret_cast<float *>(params + 2 * (size_t)G * a.rec_bytes);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(outs + (size_t)S * (G + 1));
+  float *outs = reinterpret_cast<float *>(params + 2 * (size_t)G * lay.bytes);
+  uint64_t *full = reinterpret_cast<uint64_t *>(outs + (size_t)S * (G + 1));  // [2] copy landed
+  uint32_t *finished = reinterpret_cast<uint32_t *>(full + 2);                 // [2] warps done with a buffer
 
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -171,24 +291,29 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
   const int slots = kWarps / groups_of_samples;
   const int sample_group = warp % groups_of_samples;
   const int slot = warp / groups_of_samples;
+  const int per_warp = a.per_warp;
   const int64_t row0 = (int64_t)blockIdx.x * S;
   const int num_groups = (int)((a.T + G - 1) / G);
+  const uint32_t params_addr = smem_addr(params);
 
-  if (tid == 0) {
-    mbar_init(&bars[0], 1);
-    mbar_init(&bars[1], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
   auto issue = [&](int group) {
-    const int64_t first = (int64_t)group * G;
-    const int64_t count = min((int64_t)G, a.T - first);
-    const uint32_t bytes = (uint32_t)(count * a.rec_bytes);
-    uint64_t *bar = &bars[group & 1];
+    const int64_t first_tree = (int64_t)group * G;
+    const int64_t count = min((int64_t)G, a.T - first_tree);
+    const uint32_t bytes = (uint32_t)(count * lay.bytes);
+    uint64_t *bar = &full[group & 1];
     mbar_expect_tx(bar, bytes);
-    bulk_load(params + (size_t)(group & 1) * G * a.rec_bytes, a.records + first * a.rec_bytes, bytes, bar);
+    bulk_load(params_addr + (uint32_t)(group & 1) * (uint32_t)G * lay.bytes, a.records + first_tree * lay.bytes, bytes,
+              bar);
   };
-  if (tid == 0) issue(0);
+  if (tid == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    finished[0] = 0;
+    finished[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    issue(0);
+    if (num_groups > 1) issue(1);
+  }
 
   // Stage the tile's features: lanes run along samples so that the shared-memory writes are
   // conflict free; each lane fetches 16 bytes of its row at a time when the row allows it.
@@ -209,91 +334,83 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
       xs[c * S + s] = (row0 + s < a.B) ? __ldg(a.x + (row0 + s) * C + c) : 0.f;
     }
   }
-  __syncthreads();
+  __syncthreads();  // features staged; barrier initialisation visible
 
-  // feature c of this lane's sample sits at shared address xl_addr + c * x_stride
   const uint32_t xl_addr = smem_addr(xs + sample_group * 32 + lane);
   const uint32_t x_stride = (uint32_t)S * 4u;
-  constexpr uint32_t kN = KIND == FERN ? DEPTH : (1u << DEPTH) - 1u;
-  constexpr uint32_t kThrBytes = (4u * kN + 15u) & ~15u;
-  constexpr uint32_t kWOffset = kThrBytes + (((uint32_t)sizeof(OrdT) * kN + 15u) & ~15u);
-  constexpr uint32_t kRec = (kWOffset + 4u * (1u << DEPTH) + 15u) & ~15u;
-  bool timed_out = false;
+  float *stage = outs + (size_t)sample_group * 32 * (G + 1);  // this sample group's [32][G + 1] staging rows
+  const int group_threads = slots * 32;
+  const int tid_in_group = slot * 32 + lane;
+  bool poisoned = false;  // a bounded wait ran out: keep the barriers matched, stop waiting
 
   for (int group = 0; group < num_groups; ++group) {
-    if (tid == 0 && group + 1 < num_groups) issue(group + 1);
-    if (!mbar_wait(&bars[group & 1], (uint32_t)((group >> 1) & 1))) timed_out = true;
-    if (__syncthreads_or(timed_out)) {
-      if (tid == 0 && a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
-      return;
+    if (!poisoned && !mbar_wait(&full[group & 1], (uint32_t)((group >> 1) & 1))) {
+      poisoned = true;
+      if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
     }
     const int in_group = (int)min((int64_t)G, a.T - (int64_t)group * G);
-
-    // Two trees per thread per pass.  All addresses are 32-bit shared-memory addresses.  The
-    // vertex index is kept 1-based (root = 1, children 2v and 2v+1), so that one funnel shift
-    // appends the branch bit: the bit is the sign of (threshold - feature), which is set
-    // exactly when the margin is positive (records hold +0 for a -0 threshold, and an add
-    // that yields NaN yields the canonical positive NaN, so NaN margins go left as required).
-    const uint32_t base_addr = smem_addr(params) + (uint32_t)(group & 1) * (uint32_t)(G * kRec);
-    for (int t0 = slot; t0 < in_group; t0 += 2 * slots) {
-      const int t1 = t0 + slots;
-      const bool has1 = t1 < in_group;
-      const uint32_t rec[2] = {base_addr + (uint32_t)t0 * kRec, base_addr + (uint32_t)(has1 ? t1 : t0) * kRec};
-      uint32_t v[2] = {1u, 1u};
-      float best[2], first[2];
+    const uint32_t base_addr = params_addr + (uint32_t)(group & 1) * (uint32_t)G * lay.bytes;
+    const int t_first = slot * per_warp;  // this warp's consecutive trees inside the group
+    float result[4] = {0.f, 0.f, 0.f, 0.f};
+    if (t_first < in_group) {
+      // trees beyond the end of a short last group repeat the last valid one (results unused)
+      if (per_warp == 4) {
+        uint32_t rec[4];
 #pragma unroll
-      for (int l = 0; l < DEPTH; ++l) {
+        for (int u = 0; u < 4; ++u) rec[u] = base_addr + (uint32_t)min(t_first + u, in_group - 1) * lay.bytes;
+        walk<KIND, DEPTH, OrdT, 4>(rec, xl_addr, x_stride, result);
+      } else if (per_warp == 2) {
+        uint32_t rec[2];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          float thr;
-          uint32_t c;
-          if (KIND == FERN) {
-            thr = lds_f32(rec[u] + 4u * l);
-            c = lds_ord<OrdT>(rec[u] + kThrBytes + (uint32_t)sizeof(OrdT) * l);
-          } else {
-            thr = lds_f32(rec[u] + 4u * v[u] - 4u);
-            c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * v[u] + (kThrBytes - (uint32_t)sizeof(OrdT)));
-          }
-          const float nm = thr - lds_f32(c * x_stride + xl_addr);
-          const float am = fabsf(nm);
-          if (l == 0) {
-            best[u] = am;
-            first[u] = am;
-          } else {
-            best[u] = fminf(best[u], am);
-          }
-          v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (u == 1 && !has1) break;
-        const float wv = lds_f32(rec[u] + 4u * v[u] + (kWOffset - 4u * (1u << DEPTH)));
-        const float am = (first[u] != first[u]) ? first[u] : best[u];
-        outs[(sample_group * 32 + lane) * (G + 1) + (u == 0 ? t0 : t1)] = am * wv;
+        for (int u = 0; u < 2; ++u) rec[u] = base_addr + (uint32_t)min(t_first + u, in_group - 1) * lay.bytes;
+        float r2[2];
+        walk<KIND, DEPTH, OrdT, 2>(rec, xl_addr, x_stride, r2);
+        result[0] = r2[0];
+        result[1] = r2[1];
+      } else {
+        uint32_t rec[1] = {base_addr + (uint32_t)t_first * lay.bytes};
+        float r1[1];
+        walk<KIND, DEPTH, OrdT, 1>(rec, xl_addr, x_stride, r1);
+        result[0] = r1[0];
       }
     }
-    __syncthreads();
+    // This warp no longer reads the parameter buffer.  The last warp to get here refills it.
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      const uint32_t before = atomicAdd(&finished[group & 1], 1u);
+      if (before == kWarps - 1) {
+        atomicExch(&finished[group & 1], 0u);
+        __threadfence_block();
+        if (group + 2 < num_groups) issue(group + 2);
+      }
+    }
 
-    // write the [S x in_group] block of results as row segments
+    named_barrier(1 + sample_group, group_threads);  // previous group's rows have left the staging area
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (u < per_warp && t_first + u < in_group) stage[lane * (G + 1) + t_first + u] = result[u];
+    named_barrier(1 + sample_group, group_threads);  // staging area complete
+
+    // the sample group's warps write its [32 x in_group] block of results as row segments
     const int64_t col0 = (int64_t)group * G;
+    const int64_t row_base = row0 + sample_group * 32;
     if ((a.T & 3) == 0 && (in_group & 3) == 0) {
       const int quads = in_group >> 2;
-      for (int idx = tid; idx < S * quads; idx += kThreads) {
+      for (int idx = tid_in_group; idx < 32 * quads; idx += group_threads) {
         const int s = idx / quads, q = idx - s * quads;
-        if (row0 + s < a.B) {
-          const float *src = outs + s * (G + 1) + 4 * q;
-          *reinterpret_cast<float4 *>(a.out + (row0 + s) * a.T + col0 + 4 * q) =
+        if (row_base + s < a.B) {
+          const float *src = stage + s * (G + 1) + 4 * q;
+          *reinterpret_cast<float4 *>(a.out + (row_base + s) * a.T + col0 + 4 * q) =
               make_float4(src[0], src[1], src[2], src[3]);
         }
       }
     } else {
-      for (int idx = tid; idx < S * in_group; idx += kThreads) {
+      for (int idx = tid_in_group; idx < 32 * in_group; idx += group_threads) {
         const int s = idx / in_group, t = idx - s * in_group;
-        if (row0 + s < a.B) a.out[(row0 + s) * a.T + col0 + t] = outs[s * (G + 1) + t];
+        if (row_base + s < a.B) a.out[(row_base + s) * a.T + col0 + t] = stage[s * (G + 1) + t];
       }
     }
-    // no barrier here: the one after the next group's wait also protects the staging buffer
   }
 }
 
@@ -341,7 +458,7 @@ int launch_kind(int depth, const TilePlan &plan, const TiledArgs &a, unsigned gr
 size_t forward_tiled_workspace_bytes(const ht_forest_problem *p) {
   TilePlan plan;
   if (!make_plan(p, plan)) return 0;
-  return align_up((size_t)p->T * plan.rec_bytes, 256);
+  return align_up((size_t)p->T * plan.rec.bytes, 256);
 }
 
 int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
@@ -356,11 +473,9 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
   const unsigned pack_grid = (unsigned)((elements + 255) / 256);
   unsigned char *rec = static_cast<unsigned char *>(records);
   if (plan.ord_bytes == 1)
-    repack_records_kernel<uint8_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p->kind, p->depth, p->T,
-                                                                   plan.rec_bytes, plan.thr_bytes, plan.w_offset);
+    repack_records_kernel<uint8_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p->kind, p->depth, p->T, plan.rec);
   else
-    repack_records_kernel<uint16_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p->kind, p->depth, p->T,
-                                                                    plan.rec_bytes, plan.thr_bytes, plan.w_offset);
+    repack_records_kernel<uint16_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p->kind, p->depth, p->T, plan.rec);
   HT_CHECK_LAUNCH();
 
   TiledArgs a;
@@ -373,9 +488,7 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
   a.C = (int)p->C;
   a.S = plan.S;
   a.G = plan.G;
-  a.rec_bytes = plan.rec_bytes;
-  a.thr_bytes = plan.thr_bytes;
-  a.w_offset = plan.w_offset;
+  a.per_warp = plan.per_warp;
   const unsigned grid = (unsigned)((p->B + plan.S - 1) / plan.S);
   return p->kind == TREE ? launch_kind<TREE>(p->depth, plan, a, grid, stream)
                          : launch_kind<FERN>(p->depth, plan, a, grid, stream);
