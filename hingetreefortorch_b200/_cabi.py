@@ -19,6 +19,7 @@ SYMBOLS = [
     "ht_version", "ht_status_string", "ht_last_cuda_error", "ht_forest_workspace_bytes",
     "ht_forest_forward_f32", "ht_forest_leafmap_f32", "ht_forest_marginmap_f32",
     "ht_forest_reachability_f32", "ht_forest_backward_f32",
+    "ht_forest_static_scratch_bytes", "ht_forest_forward_static_f32",
 ]
 
 
@@ -50,6 +51,7 @@ def library():
         lib.ht_status_string.argtypes = [ctypes.c_int]
         lib.ht_forest_workspace_bytes.restype = ctypes.c_size_t
         lib.ht_forest_workspace_bytes.argtypes = [ctypes.POINTER(ForestProblem)]
+        lib.ht_forest_static_scratch_bytes.restype = ctypes.c_size_t
         _lib = lib
     return _lib
 
@@ -100,6 +102,15 @@ class Forest:
             out = torch.empty(self.out_shape, dtype=torch.float32, device=x.device)
         _check(library().ht_forest_forward_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(w),
                                                _ptr(out), *self._tail(x)))
+        return out
+
+    def forward_static(self, x, thr, ord_, w, out=None):
+        """The forward through the entry point that uses the library's built-in scratch array."""
+        import torch
+        if out is None:
+            out = torch.empty(self.out_shape, dtype=torch.float32, device=x.device)
+        _check(library().ht_forest_forward_static_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_),
+                                                      _ptr(w), _ptr(out), _ptr(self.status), _stream(x)))
         return out
 
     def leafmap(self, x, thr, ord_):

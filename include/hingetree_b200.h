@@ -79,6 +79,26 @@ int ht_forest_forward_f32(const ht_forest_problem *p, const float *x, const floa
                           const float *w, float *out, void *workspace, size_t workspace_bytes,
                           uint32_t *status_word, ht_stream_t stream);
 
+/* The same forward for callers that cannot supply a workspace.  It has no counterpart in the
+ * reference.  It is meant for code that may not allocate device memory at the point of the
+ * call -- a serving loop running against a frozen memory pool, a plugin host that hands a
+ * binding nothing but its input and output buffers, a runtime whose allocator is out of the
+ * binding's reach -- and that therefore has no buffer to pass as `workspace`.  The scratch
+ * lives in a fixed array inside the library image (ht_forest_static_scratch_bytes() bytes,
+ * currently 16 MiB, resident on every device that loads the library until the process exits).
+ *   - Nothing is allocated or freed, here or in anything this calls.
+ *   - A problem whose ht_forest_workspace_bytes() exceeds the array is refused with
+ *     HT_ERR_WORKSPACE; use ht_forest_forward_f32 with your own workspace for those.
+ *   - The first call on a device looks up the array's device address (once per device, with
+ *     that device current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array, which simply keeps what the last call wrote;
+ *     every byte that is read is rewritten first, so nothing needs clearing.  Two calls that
+ *     overlap on the GPU (different streams, or different host threads) race on it: serialise
+ *     them.  x, thr, ord, w, out and status_word are as for ht_forest_forward_f32. */
+size_t ht_forest_static_scratch_bytes(void);
+int ht_forest_forward_static_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
+                                 const float *w, float *out, uint32_t *status_word, ht_stream_t stream);
+
 /* leaf[i,j,k] = leaf key (bit l = decision at depth l), int64.
  * Replaces hingetree_gpu_leafmap / LeafMapKernel (hingetree_gpu.cu:791-860, 116-139). */
 int ht_forest_leafmap_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
