@@ -20,7 +20,86 @@ SYMBOLS = [
     "ht_forest_forward_f32", "ht_forest_leafmap_f32", "ht_forest_marginmap_f32",
     "ht_forest_reachability_f32", "ht_forest_backward_f32",
     "ht_forest_static_scratch_bytes", "ht_forest_forward_static_f32",
+    "ht_forest_fusion_workspace_bytes", "ht_forest_fusion_forward_f32", "ht_forest_fusion_backward_f32",
+    "ht_forest_linear_workspace_bytes", "ht_forest_linear_forward_f32", "ht_forest_linear_backward_f32",
+    "ht_conv_output_size", "ht_conv_workspace_bytes", "ht_conv_forward_f32", "ht_conv_backward_f32",
+    "ht_contract", "ht_expand",
 ]
+
+
+class ConvProblem(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_int32), ("depth", ctypes.c_int32), ("dims", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("B", ctypes.c_int64), ("Ci", ctypes.c_int64), ("Co", ctypes.c_int64),
+                ("M", ctypes.c_int64), ("size", ctypes.c_int64 * 3), ("kernel", ctypes.c_int64 * 3),
+                ("stride", ctypes.c_int64 * 3), ("padding", ctypes.c_int64 * 3), ("dilation", ctypes.c_int64 * 3)]
+
+
+def _triple(values, fill):
+    values = list(values) + [fill] * (3 - len(values))
+    return (ctypes.c_int64 * 3)(*values)
+
+
+class Conv:
+    """Convolutional hinge trees through the C ABI: x [B,Ci,*size], thr/ord [Co,Ci,N], w [Co,Ci,L,*extra]."""
+
+    def __init__(self, kind, x, w, kernel, stride, padding, dilation):
+        import math
+        import torch
+        dims = x.dim() - 2
+        L = w.shape[2]
+        self.problem = ConvProblem(HT_KIND[kind], L.bit_length() - 1, dims, 0, x.shape[0], x.shape[1], w.shape[0],
+                                   math.prod(w.shape[3:]), _triple(x.shape[2:], 1), _triple(kernel, 1),
+                                   _triple(stride, 1), _triple(padding, 0), _triple(dilation, 1))
+        lib = library()
+        lib.ht_conv_workspace_bytes.restype = ctypes.c_size_t
+        osize = (ctypes.c_int64 * 3)()
+        _check(lib.ht_conv_output_size(ctypes.byref(self.problem), osize))
+        self.out_shape = (x.shape[0], w.shape[0]) + tuple(osize[:dims]) + tuple(w.shape[3:])
+        nbytes = lib.ht_conv_workspace_bytes(ctypes.byref(self.problem))
+        self.workspace = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=x.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=x.device)
+
+    def _tail(self, x):
+        return (_ptr(self.workspace), ctypes.c_size_t(self.workspace.numel()), _ptr(self.status), _stream(x))
+
+    def forward(self, x, thr, ord_, w):
+        import torch
+        out = torch.empty(self.out_shape, dtype=torch.float32, device=x.device)
+        _check(library().ht_conv_forward_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(w),
+                                             _ptr(out), *self._tail(x)))
+        return out
+
+    def backward(self, x, thr, ord_, w, g):
+        import torch
+        outs = [torch.empty_like(t) for t in (x, thr, w)]
+        _check(library().ht_conv_backward_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(w),
+                                              _ptr(g), *[_ptr(t) for t in outs], *self._tail(x)))
+        return outs
+
+
+def _i64_array(values):
+    return (ctypes.c_int64 * len(values))(*[int(v) for v in values])
+
+
+def contract(x, window, padding):
+    import torch
+    dims = len(window)
+    osize = [(s + 2 * p - w) // w + 1 for s, p, w in zip(x.shape[2:], padding, window)]
+    out = torch.empty(tuple(x.shape[:2]) + tuple(osize) + tuple(window), dtype=x.dtype, device=x.device)
+    _check(library().ht_contract(dims, x.element_size(), _ptr(x), _ptr(out), ctypes.c_int64(x.shape[0] * x.shape[1]),
+                                 _i64_array(x.shape[2:]), _i64_array(window), _i64_array(padding), _stream(x)))
+    return out
+
+
+def expand(x, padding):
+    import torch
+    dims = len(padding)
+    osize, window = x.shape[2:2 + dims], x.shape[2 + dims:]
+    size = [o * w - ((2 * p) // w) * w for o, w, p in zip(osize, window, padding)]
+    out = torch.empty(tuple(x.shape[:2]) + tuple(size), dtype=x.dtype, device=x.device)
+    _check(library().ht_expand(dims, x.element_size(), _ptr(x), _ptr(out), ctypes.c_int64(x.shape[0] * x.shape[1]),
+                               _i64_array(osize), _i64_array(window), _i64_array(padding), _stream(x)))
+    return out
 
 
 class ForestProblem(ctypes.Structure):
@@ -147,3 +226,61 @@ class Forest:
     def ordinal_flags(self):
         """Reads the device status word (blocks until the stream has drained)."""
         return int(self.status.item())
+
+
+class ForestFamily:
+    """Fusion (image + vector) and fused-linear calls on one problem shape; vec / lin are optional."""
+
+    def __init__(self, kind, x, w, vec=None, lin=None):
+        import torch
+        self.problem = forest_problem(kind, x, w)
+        self.vec_channels = 0 if vec is None else vec.shape[1]
+        self.out_channels = 0 if lin is None else lin.shape[0]
+        lib = library()
+        lib.ht_forest_linear_workspace_bytes.restype = ctypes.c_size_t
+        lib.ht_forest_fusion_workspace_bytes.restype = ctypes.c_size_t
+        nbytes = max(lib.ht_forest_linear_workspace_bytes(ctypes.byref(self.problem)),
+                     lib.ht_forest_fusion_workspace_bytes(ctypes.byref(self.problem)))
+        self.workspace = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=x.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=x.device)
+        inner = tuple(x.shape[2:]) + tuple(w.shape[2:])
+        self.out_shape = (x.shape[0], w.shape[0] if lin is None else lin.shape[0]) + inner
+
+    def _tail(self, x):
+        return (_ptr(self.workspace), ctypes.c_size_t(self.workspace.numel()), _ptr(self.status), _stream(x))
+
+    def fusion_forward(self, img, vec, thr, ord_, w):
+        import torch
+        out = torch.empty(self.out_shape, dtype=torch.float32, device=img.device)
+        _check(library().ht_forest_fusion_forward_f32(ctypes.byref(self.problem), _ptr(img), _ptr(vec),
+                                                      ctypes.c_int64(self.vec_channels), _ptr(thr), _ptr(ord_), _ptr(w),
+                                                      _ptr(out), *self._tail(img)))
+        return out
+
+    def fusion_backward(self, img, vec, thr, ord_, w, g):
+        import torch
+        outs = [torch.empty_like(t) for t in (img, vec, thr, w)]
+        _check(library().ht_forest_fusion_backward_f32(ctypes.byref(self.problem), _ptr(img), _ptr(vec),
+                                                       ctypes.c_int64(self.vec_channels), _ptr(thr), _ptr(ord_), _ptr(w),
+                                                       _ptr(g), *[_ptr(t) for t in outs], *self._tail(img)))
+        return outs
+
+    def linear_forward(self, x, vec, thr, ord_, w, lin, bias):
+        import torch
+        out = torch.empty(self.out_shape, dtype=torch.float32, device=x.device)
+        _check(library().ht_forest_linear_forward_f32(ctypes.byref(self.problem), ctypes.c_int64(self.out_channels),
+                                                      _ptr(x), _ptr(vec), ctypes.c_int64(self.vec_channels), _ptr(thr),
+                                                      _ptr(ord_), _ptr(w), _ptr(lin), _ptr(bias), _ptr(out),
+                                                      *self._tail(x)))
+        return out
+
+    def linear_backward(self, x, vec, thr, ord_, w, lin, g):
+        """Returns (gx, gvec or None, gthr, gw, glin)."""
+        import torch
+        gx, gthr, gw, glin = [torch.empty_like(t) for t in (x, thr, w, lin)]
+        gvec = None if vec is None else torch.empty_like(vec)
+        _check(library().ht_forest_linear_backward_f32(ctypes.byref(self.problem), ctypes.c_int64(self.out_channels),
+                                                       _ptr(x), _ptr(vec), ctypes.c_int64(self.vec_channels), _ptr(thr),
+                                                       _ptr(ord_), _ptr(w), _ptr(lin), _ptr(g), _ptr(gx), _ptr(gvec),
+                                                       _ptr(gthr), _ptr(gw), _ptr(glin), *self._tail(x)))
+        return gx, gvec, gthr, gw, glin

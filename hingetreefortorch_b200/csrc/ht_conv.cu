@@ -1,0 +1,406 @@
+// Convolutional hinge trees / ferns (1-D, 2-D, 3-D) and contract / expand.
+//
+// Output channel j sums, over the input channels c in ascending order, the value of the
+// single-channel tree (j, c) evaluated on the kernel window of channel c at every output
+// position.  The reference launches one im2col gather and one tree kernel per (sample, input
+// channel) and materialises index and feature matrices (hingetree_conv_gpu.cu:368-380);
+// here one launch covers the whole call: a thread owns one output position of one (sample,
+// output channel), reads window cells straight from the image (padding cells read as 0) and
+// walks the input channels itself, adding in the reference's order, so the forward is
+// deterministic and equal to the reference CPU loop bit for bit.
+#include "ht_common.cuh"
+
+namespace ht {
+
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kMaxCells = 2048;  // window cells whose offsets are tabulated in shared memory
+
+struct ConvArgs {
+  const float *x;
+  const float *thr;
+  const int32_t *ord;
+  const float *w;
+  int64_t B, Ci, Co, M, N, L;
+  int64_t in_count, out_count;
+  int dims, depth, cells;
+  int size[3], osize[3], kernel[3], stride[3], pad[3], dil[3];
+};
+
+// Offsets (in elements along z, y, x; dilation applied) of every window cell, 10 bits each.
+__device__ __forceinline__ void fill_cell_table(const ConvArgs &a, uint32_t *table) {
+  for (int q = threadIdx.x; q < a.cells; q += blockDim.x) {
+    int rest = q;
+    uint32_t packed = 0;
+    for (int d = a.dims - 1; d >= 0; --d) {
+      const int qd = rest % a.kernel[d];
+      rest /= a.kernel[d];
+      packed |= (uint32_t)(qd * a.dil[d]) << (10 * (a.dims - 1 - d));
+    }
+    table[q] = packed;
+  }
+}
+
+// Image coordinates of the first window cell of output position p (may be negative: padding).
+__device__ __forceinline__ void window_origin(const ConvArgs &a, int64_t p, int (&origin)[3]) {
+#pragma unroll
+  for (int d = 2; d >= 0; --d) {
+    if (d < a.dims) {
+      const int od = (int)(p % a.osize[d]);
+      p /= a.osize[d];
+      origin[d] = od * a.stride[d] - a.pad[d];
+    } else {
+      origin[d] = 0;
+    }
+  }
+}
+
+// Flat index of window cell `packed` inside one channel image, or -1 when it lies in the padding.
+__device__ __forceinline__ int cell_index(const ConvArgs &a, const int (&origin)[3], uint32_t packed) {
+  int index = 0;
+  bool inside = true;
+#pragma unroll
+  for (int d = 0; d < 3; ++d) {
+    if (d < a.dims) {
+      const int at = origin[d] + (int)((packed >> (10 * (a.dims - 1 - d))) & 1023u);
+      inside = inside && at >= 0 && at < a.size[d];
+      index = index * a.size[d] + at;
+    }
+  }
+  return inside ? index : -1;
+}
+
+struct WindowFeature {
+  const ConvArgs &a;
+  const float *chan;
+  const int (&origin)[3];
+  const uint32_t *table;
+  __device__ __forceinline__ float operator()(int q) const {
+    const int idx = cell_index(a, origin, table[q]);
+    return idx < 0 ? 0.0f : __ldg(chan + idx);
+  }
+};
+
+template <int KIND>
+__global__ void __launch_bounds__(kBlock) conv_forward_kernel(ConvArgs a, float *__restrict__ out) {
+  __shared__ uint32_t table[kMaxCells];
+  fill_cell_table(a, table);
+  __syncthreads();
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // (i, j, p), p fastest
+  if (e >= a.B * a.Co * a.out_count) return;
+  const int64_t p = e % a.out_count;
+  const int64_t j = (e / a.out_count) % a.Co;
+  const int64_t i = e / (a.out_count * a.Co);
+  int origin[3];
+  window_origin(a, p, origin);
+  float *o = out + e * a.M;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const bool in_registers = a.M <= 8;
+  if (!in_registers)
+    for (int64_t m = 0; m < a.M; ++m) o[m] = 0.0f;
+  for (int64_t c = 0; c < a.Ci; ++c) {
+    const int64_t tree = j * a.Ci + c;
+    const WindowFeature feat{a, a.x + (i * a.Ci + c) * a.in_count, origin, table};
+    const Path path = traverse<KIND>(feat, a.thr + tree * a.N, a.ord + tree * a.N, a.depth);
+    const float am = fabsf(path.margin);
+    const float *wl = a.w + (tree * a.L + path.key) * a.M;
+    if (in_registers) {
+#pragma unroll
+      for (int m = 0; m < 8; ++m)
+        if (m < a.M) acc[m] = __fadd_rn(acc[m], __fmul_rn(__ldg(wl + m), am));
+    } else {
+      for (int64_t m = 0; m < a.M; ++m) o[m] = __fadd_rn(o[m], __fmul_rn(__ldg(wl + m), am));
+    }
+  }
+  if (in_registers) {
+#pragma unroll
+    for (int m = 0; m < 8; ++m)
+      if (m < a.M) o[m] = acc[m];
+  }
+}
+
+// One thread per (i, j, p) walking the input channels; the three gradients are scattered with atomics.
+template <int KIND>
+__global__ void __launch_bounds__(kBlock) conv_backward_kernel(ConvArgs a, const float *__restrict__ g, float *gx,
+                                                               float *gthr, float *gw) {
+  __shared__ uint32_t table[kMaxCells];
+  fill_cell_table(a, table);
+  __syncthreads();
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= a.B * a.Co * a.out_count) return;
+  const int64_t p = e % a.out_count;
+  const int64_t j = (e / a.out_count) % a.Co;
+  const int64_t i = e / (a.out_count * a.Co);
+  int origin[3];
+  window_origin(a, p, origin);
+  const float *gl = g + e * a.M;
+  for (int64_t c = 0; c < a.Ci; ++c) {
+    const int64_t tree = j * a.Ci + c;
+    const WindowFeature feat{a, a.x + (i * a.Ci + c) * a.in_count, origin, table};
+    const Path path = traverse<KIND>(feat, a.thr + tree * a.N, a.ord + tree * a.N, a.depth);
+    const float s = sign_of(path.margin), am = fabsf(path.margin);
+    const float *wl = a.w + (tree * a.L + path.key) * a.M;
+    float acc = 0.0f;
+    for (int64_t m = 0; m < a.M; ++m) {
+      const float gm = __ldg(gl + m);
+      acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s, __ldg(wl + m)), gm));
+      if (gw != nullptr) atomicAdd(gw + (tree * a.L + path.key) * a.M + m, __fmul_rn(am, gm));
+    }
+    if (gx != nullptr) {
+      const int idx = cell_index(a, origin, table[a.ord[tree * a.N + path.vertex]]);
+      if (idx >= 0) atomicAdd(gx + (i * a.Ci + c) * a.in_count + idx, acc);  // a padding cell has no gradient
+    }
+    if (gthr != nullptr) atomicAdd(gthr + tree * a.N + path.vertex, -acc);
+  }
+}
+
+// ---- contract / expand: non-overlapping windows <-> image, any element size ----------------
+
+struct PatchArgs {
+  int dims;
+  int64_t BC, image_count, window_count, cells;
+  int64_t size[3], osize[3], win[3], pad[3];
+};
+
+// One thread per patch element (b, window p, cell q): its image coordinate, or -1 outside.
+__device__ __forceinline__ int64_t patch_image_index(const PatchArgs &a, int64_t p, int64_t q) {
+  int64_t index = 0, scale = 1;
+  for (int d = a.dims - 1; d >= 0; --d) {
+    const int64_t at = (p % a.osize[d]) * a.win[d] - a.pad[d] + (q % a.win[d]);
+    p /= a.osize[d];
+    q /= a.win[d];
+    if (at < 0 || at >= a.size[d]) return -1;
+    index += at * scale;
+    scale *= a.size[d];
+  }
+  return index;
+}
+
+template <typename Word>
+__global__ void __launch_bounds__(kBlock) contract_kernel(PatchArgs a, const Word *__restrict__ image,
+                                                          Word *__restrict__ patches) {
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t per_image = a.window_count * a.cells;
+  if (e >= a.BC * per_image) return;
+  const int64_t b = e / per_image, r = e - b * per_image;
+  const int64_t idx = patch_image_index(a, r / a.cells, r % a.cells);
+  patches[e] = idx < 0 ? Word(0) : image[b * a.image_count + idx];
+}
+
+// One thread per image element: every pixel belongs to exactly one window cell (or to none, when
+// the windows do not reach it), so expand is a gather as well and needs no clearing pass.
+template <typename Word>
+__global__ void __launch_bounds__(kBlock) expand_kernel(PatchArgs a, const Word *__restrict__ patches,
+                                                        Word *__restrict__ image) {
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= a.BC * a.image_count) return;
+  const int64_t b = e / a.image_count;
+  int64_t rest = e - b * a.image_count;
+  int64_t p = 0, q = 0, pscale = 1, qscale = 1;
+  bool covered = true;
+  for (int d = a.dims - 1; d >= 0; --d) {
+    const int64_t at = rest % a.size[d] + a.pad[d];
+    rest /= a.size[d];
+    const int64_t od = at / a.win[d];
+    covered = covered && od < a.osize[d];
+    p += od * pscale;
+    q += (at % a.win[d]) * qscale;
+    pscale *= a.osize[d];
+    qscale *= a.win[d];
+  }
+  image[e] = covered ? patches[(b * a.window_count + p) * a.cells + q] : Word(0);
+}
+
+inline unsigned blocks_for(int64_t n) { return (unsigned)((n + kBlock - 1) / kBlock); }
+
+int check_conv(const ht_conv_problem *p, ConvArgs &a) {
+  if (p == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  if (p->kind != TREE && p->kind != FERN) return HT_ERR_INVALID_ARGUMENT;
+  if (p->depth < 1 || p->depth > 31) return HT_ERR_DEPTH;
+  if (p->dims < 1 || p->dims > 3 || p->B < 0 || p->Ci < 1 || p->Co < 0 || p->M < 0) return HT_ERR_INVALID_ARGUMENT;
+  a.dims = p->dims;
+  a.depth = p->depth;
+  a.B = p->B;
+  a.Ci = p->Ci;
+  a.Co = p->Co;
+  a.M = p->M;
+  a.N = threshold_count(p->kind, p->depth);
+  a.L = ((int64_t)1) << p->depth;
+  a.in_count = a.out_count = 1;
+  int64_t cells = 1;
+  for (int d = 0; d < 3; ++d) {
+    a.size[d] = a.osize[d] = a.kernel[d] = a.stride[d] = a.dil[d] = 1;
+    a.pad[d] = 0;
+  }
+  for (int d = 0; d < p->dims; ++d) {
+    if (p->kernel[d] <= 0 || p->stride[d] <= 0 || p->padding[d] < 0 || p->dilation[d] <= 0 || p->size[d] < 1)
+      return HT_ERR_INVALID_ARGUMENT;
+    const int64_t window = p->kernel[d] + (p->kernel[d] - 1) * (p->dilation[d] - 1);
+    if (p->size[d] + 2 * p->padding[d] < window) return HT_ERR_INVALID_ARGUMENT;
+    if ((p->kernel[d] - 1) * p->dilation[d] >= 1024 || p->size[d] > 0x3fffffff) return HT_ERR_UNSUPPORTED;
+    a.size[d] = (int)p->size[d];
+    a.kernel[d] = (int)p->kernel[d];
+    a.stride[d] = (int)p->stride[d];
+    a.pad[d] = (int)p->padding[d];
+    a.dil[d] = (int)p->dilation[d];
+    a.osize[d] = (int)((p->size[d] + 2 * p->padding[d] - window) / p->stride[d] + 1);
+    a.in_count *= p->size[d];
+    a.out_count *= a.osize[d];
+    cells *= p->kernel[d];
+  }
+  if (cells > kMaxCells || a.in_count > 0x7fffffff) return HT_ERR_UNSUPPORTED;
+  a.cells = (int)cells;
+  return HT_OK;
+}
+
+size_t conv_ordinal_bytes(const ConvArgs &a) { return align_up((size_t)(a.Co * a.Ci * a.N) * sizeof(int32_t), 256); }
+
+int prepare_conv(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
+                 void *workspace, size_t workspace_bytes, uint32_t *status_word, cudaStream_t stream, ConvArgs &a) {
+  const int rc = check_conv(p, a);
+  if (rc != HT_OK) return rc;
+  const int64_t decisions = a.Co * a.Ci * a.N;
+  if ((x == nullptr && a.B * a.Ci * a.in_count > 0) || ((thr == nullptr || ord == nullptr) && decisions > 0) ||
+      (w == nullptr && a.Co * a.M > 0))
+    return HT_ERR_INVALID_ARGUMENT;
+  if (workspace == nullptr || workspace_bytes < conv_ordinal_bytes(a) + 256 ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    return HT_ERR_WORKSPACE;
+  a.x = x;
+  a.thr = thr;
+  a.w = w;
+  a.ord = static_cast<const int32_t *>(workspace);
+  return pack_ordinals(ord, decisions, a.cells, static_cast<int32_t *>(workspace), status_word, stream);
+}
+
+template <typename Word>
+int launch_patches(bool contract, const PatchArgs &a, const void *in, void *out, cudaStream_t stream) {
+  if (contract) {
+    const int64_t n = a.BC * a.window_count * a.cells;
+    if (n > 0) contract_kernel<Word><<<blocks_for(n), kBlock, 0, stream>>>(a, static_cast<const Word *>(in), static_cast<Word *>(out));
+  } else {
+    const int64_t n = a.BC * a.image_count;
+    if (n > 0) expand_kernel<Word><<<blocks_for(n), kBlock, 0, stream>>>(a, static_cast<const Word *>(in), static_cast<Word *>(out));
+  }
+  HT_CHECK_LAUNCH();
+  return HT_OK;
+}
+
+int run_patches(bool contract, int dims, int elem_bytes, const void *in, void *out, int64_t BC, const int64_t *size,
+                const int64_t *osize, const int64_t *window, const int64_t *padding, cudaStream_t stream) {
+  if (dims < 2 || dims > 3 || BC < 0 || size == nullptr || osize == nullptr || window == nullptr || padding == nullptr)
+    return HT_ERR_INVALID_ARGUMENT;
+  PatchArgs a;
+  a.dims = dims;
+  a.BC = BC;
+  a.image_count = a.window_count = a.cells = 1;
+  for (int d = 0; d < dims; ++d) {
+    if (size[d] < 1 || osize[d] < 1 || window[d] < 1 || padding[d] < 0) return HT_ERR_INVALID_ARGUMENT;
+    a.size[d] = size[d];
+    a.osize[d] = osize[d];
+    a.win[d] = window[d];
+    a.pad[d] = padding[d];
+    a.image_count *= size[d];
+    a.window_count *= osize[d];
+    a.cells *= window[d];
+  }
+  if ((in == nullptr || out == nullptr) && BC > 0) return HT_ERR_INVALID_ARGUMENT;
+  switch (elem_bytes) {
+    case 1: return launch_patches<uint8_t>(contract, a, in, out, stream);
+    case 2: return launch_patches<uint16_t>(contract, a, in, out, stream);
+    case 4: return launch_patches<uint32_t>(contract, a, in, out, stream);
+    case 8: return launch_patches<uint64_t>(contract, a, in, out, stream);
+    default: return HT_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace
+}  // namespace ht
+
+using namespace ht;
+
+extern "C" {
+
+int ht_conv_output_size(const ht_conv_problem *p, int64_t *osize) {
+  ConvArgs a;
+  const int rc = check_conv(p, a);
+  if (rc != HT_OK) return rc;
+  if (osize == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  for (int d = 0; d < p->dims; ++d) osize[d] = a.osize[d];
+  return HT_OK;
+}
+
+size_t ht_conv_workspace_bytes(const ht_conv_problem *p) {
+  ConvArgs a;
+  if (check_conv(p, a) != HT_OK) return 0;
+  return conv_ordinal_bytes(a) + 256;
+}
+
+int ht_conv_forward_f32(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
+                        float *out, void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream) {
+  ConvArgs a;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int rc = prepare_conv(p, x, thr, ord, w, workspace, workspace_bytes, status_word, s, a);
+  if (rc != HT_OK) return rc;
+  const int64_t threads = a.B * a.Co * a.out_count;
+  if (threads * a.M == 0) return HT_OK;
+  if (out == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  if (p->kind == TREE)
+    conv_forward_kernel<TREE><<<blocks_for(threads), kBlock, 0, s>>>(a, out);
+  else
+    conv_forward_kernel<FERN><<<blocks_for(threads), kBlock, 0, s>>>(a, out);
+  HT_CHECK_LAUNCH();
+  return HT_OK;
+}
+
+int ht_conv_backward_f32(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
+                         const float *g, float *gx, float *gthr, float *gw, void *workspace, size_t workspace_bytes,
+                         uint32_t *status_word, ht_stream_t stream) {
+  ConvArgs a;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int rc = prepare_conv(p, x, thr, ord, w, workspace, workspace_bytes, status_word, s, a);
+  if (rc != HT_OK) return rc;
+  if (gx != nullptr && a.B * a.Ci * a.in_count > 0)
+    HT_CUDA_TRY(cudaMemsetAsync(gx, 0, sizeof(float) * (size_t)(a.B * a.Ci * a.in_count), s));
+  if (gthr != nullptr && a.Co * a.Ci * a.N > 0)
+    HT_CUDA_TRY(cudaMemsetAsync(gthr, 0, sizeof(float) * (size_t)(a.Co * a.Ci * a.N), s));
+  if (gw != nullptr && a.Co * a.Ci * a.L * a.M > 0)
+    HT_CUDA_TRY(cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)(a.Co * a.Ci * a.L * a.M), s));
+  const int64_t threads = a.B * a.Co * a.out_count;
+  if (threads * a.M == 0 || (gx == nullptr && gthr == nullptr && gw == nullptr)) return HT_OK;
+  if (g == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  if (p->kind == TREE)
+    conv_backward_kernel<TREE><<<blocks_for(threads), kBlock, 0, s>>>(a, g, gx, gthr, gw);
+  else
+    conv_backward_kernel<FERN><<<blocks_for(threads), kBlock, 0, s>>>(a, g, gx, gthr, gw);
+  HT_CHECK_LAUNCH();
+  return HT_OK;
+}
+
+int ht_contract(int dims, int elem_bytes, const void *image, void *patches, int64_t batch_times_channels,
+                const int64_t *size, const int64_t *window, const int64_t *padding, ht_stream_t stream) {
+  if (dims < 2 || dims > 3 || size == nullptr || window == nullptr || padding == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  int64_t osize[3];
+  for (int d = 0; d < dims; ++d) {
+    if (window[d] < 1 || padding[d] < 0 || window[d] > size[d] + 2 * padding[d]) return HT_ERR_INVALID_ARGUMENT;
+    osize[d] = (size[d] + 2 * padding[d] - window[d]) / window[d] + 1;
+  }
+  return run_patches(true, dims, elem_bytes, image, patches, batch_times_channels, size, osize, window, padding,
+                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ht_expand(int dims, int elem_bytes, const void *patches, void *image, int64_t batch_times_channels,
+              const int64_t *osize, const int64_t *window, const int64_t *padding, ht_stream_t stream) {
+  if (dims < 2 || dims > 3 || osize == nullptr || window == nullptr || padding == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  int64_t size[3];
+  for (int d = 0; d < dims; ++d) {
+    if (window[d] < 1 || padding[d] < 0 || osize[d] < 1) return HT_ERR_INVALID_ARGUMENT;
+    size[d] = osize[d] * window[d] - ((2 * padding[d]) / window[d]) * window[d];
+    if (size[d] < 1) return HT_ERR_INVALID_ARGUMENT;
+  }
+  return run_patches(false, dims, elem_bytes, patches, image, batch_times_channels, size, osize, window, padding,
+                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -132,6 +132,82 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
                            const float *w, const float *g, float *gx, float *gthr, float *gw,
                            void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
 
+/* ---- image + per-sample vector ("fusion") forests ------------------------------------------
+ * Feature f of sample i at position k is img[i,f,k] for f < C (p->C = image channels) and
+ * vec[i, f - C] otherwise, without materialising the concatenation; ordinals range over
+ * [0, C + vec_channels).  Replaces hingetree_fusion_gpu_forward / _backward and their kernels
+ * (hingetree_fusion_gpu.cu:352-558, 58-88, 135-177, 218-251, 304-346).  The vector gradient
+ * sums over k.  gimg / gvec / gthr / gw may each be NULL; the others are cleared here. */
+size_t ht_forest_fusion_workspace_bytes(const ht_forest_problem *p);
+int ht_forest_fusion_forward_f32(const ht_forest_problem *p, const float *img, const float *vec, int64_t vec_channels,
+                                 const float *thr, const int64_t *ord, const float *w, float *out, void *workspace,
+                                 size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+int ht_forest_fusion_backward_f32(const ht_forest_problem *p, const float *img, const float *vec, int64_t vec_channels,
+                                  const float *thr, const int64_t *ord, const float *w, const float *g, float *gimg,
+                                  float *gvec, float *gthr, float *gw, void *workspace, size_t workspace_bytes,
+                                  uint32_t *status_word, ht_stream_t stream);
+
+/* ---- forest followed by a linear layer over the tree dimension ("fused linear") -------------
+ *   out[i,o,k,m] = bias[o] + sum_j lin[o,j] * |margin(i,j,k)| * w[j,leaf,m]        out [B,O,K,M]
+ * lin is [O, T], bias [O].  With vec != NULL the features are the fusion ones above.
+ * Replaces hingetree_fused_linear_gpu_forward / _backward and hingetree_fusion_fused_linear_gpu_*
+ * (hingetree_fused_linear_gpu.cu:509-603, 605-703, 705-839, 841-982 and kernels 58-503).  The
+ * forward adds the terms for j ascending, as the reference CPU loop does
+ * (hingetree_fused_linear.cpp:154-181): it is deterministic and equal to that loop bit for bit.
+ * The backward returns gimg, gvec, gthr, gw and glin (any may be NULL); the bias gradient is
+ * the plain sum of g over every dimension but O and is left to the caller, as the reference
+ * leaves it to Tensor::sum (hingetree_fused_linear_gpu.cu:828-836). */
+size_t ht_forest_linear_workspace_bytes(const ht_forest_problem *p);
+int ht_forest_linear_forward_f32(const ht_forest_problem *p, int64_t out_channels, const float *img, const float *vec,
+                                 int64_t vec_channels, const float *thr, const int64_t *ord, const float *w,
+                                 const float *lin, const float *bias, float *out, void *workspace,
+                                 size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+int ht_forest_linear_backward_f32(const ht_forest_problem *p, int64_t out_channels, const float *img, const float *vec,
+                                  int64_t vec_channels, const float *thr, const int64_t *ord, const float *w,
+                                  const float *lin, const float *g, float *gimg, float *gvec, float *gthr, float *gw,
+                                  float *glin, void *workspace, size_t workspace_bytes, uint32_t *status_word,
+                                  ht_stream_t stream);
+
+/* ---- convolutional hinge trees / ferns, 1-D / 2-D / 3-D -------------------------------------
+ *   out[i,j,p,m] = sum over input channels c (ascending) of |margin(i,c,j,p)| * w[j,c,leaf,m]
+ * where tree (j,c) is evaluated on the kernel window of input channel c at output position p;
+ * ordinals index the window cells in row-major kernel order, cells in the padding read 0, and
+ * the output size per dimension is (size + 2*padding - (kernel + (kernel-1)*(dilation-1))) / stride + 1.
+ *   x [B, Ci, size...]   thr, ord [Co, Ci, N]   w [Co, Ci, L, M]   out [B, Co, osize..., M]
+ * Replaces hingetree_conv_gpu_forward / _backward with their per-(sample, channel) launches
+ * (hingetree_conv_gpu.cu:214-618, kernels 64-210) and the im2col helpers they call
+ * (ImageToMatrix_gpu.cu:132-239; geometry ImageToMatrix.h:189-221, 304-347).  One group only
+ * (w.shape[1] == x.shape[1]), which is all the reference's modules ever build.  The forward adds the
+ * input channels in ascending order and equals the reference CPU loop bit for bit; the
+ * backward scatters with atomics.  A decision that looked at a padding cell has no data gradient. */
+typedef struct ht_conv_problem {
+  int32_t kind;   /* HT_KIND_TREE or HT_KIND_FERN */
+  int32_t depth;  /* 1..31 */
+  int32_t dims;   /* 1, 2 or 3 spatial dimensions */
+  int32_t reserved;
+  int64_t B, Ci, Co, M;
+  int64_t size[3], kernel[3], stride[3], padding[3], dilation[3]; /* first `dims` entries are used */
+} ht_conv_problem;
+
+int ht_conv_output_size(const ht_conv_problem *p, int64_t *osize /* [dims] */);
+size_t ht_conv_workspace_bytes(const ht_conv_problem *p);
+int ht_conv_forward_f32(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
+                        float *out, void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+int ht_conv_backward_f32(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
+                         const float *g, float *gx, float *gthr, float *gw, void *workspace, size_t workspace_bytes,
+                         uint32_t *status_word, ht_stream_t stream);
+
+/* ---- contract / expand -------------------------------------------------------------------------
+ * contract: image [BC, size...] -> non-overlapping windows [BC, osize..., window...], zero padded,
+ *           osize = (size + 2*padding - window) / window + 1 per dimension.
+ * expand:   the inverse, image size = osize*window - (2*padding / window)*window; pixels no window
+ *           reaches are 0.  dims is 2 or 3; elements are moved as opaque 1, 2, 4 or 8 byte words.
+ * Replaces contract2d/3d_gpu and expand2d/3d_gpu (expand_gpu.cu:198-396, kernels 110-194). */
+int ht_contract(int dims, int elem_bytes, const void *image, void *patches, int64_t batch_times_channels,
+                const int64_t *size, const int64_t *window, const int64_t *padding, ht_stream_t stream);
+int ht_expand(int dims, int elem_bytes, const void *patches, void *image, int64_t batch_times_channels,
+              const int64_t *osize, const int64_t *window, const int64_t *padding, ht_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

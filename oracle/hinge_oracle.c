@@ -183,3 +183,77 @@ int ho_backward_magnitudes(int kind, const float *x, const float *thr, const int
       }
   return 0;
 }
+
+/* ---- trees followed by a linear layer over the tree dimension ("fused linear") --------------
+ * hingetree_fused_linear.cpp:154-181 (forward): out starts as the bias and receives, for j
+ * ascending, (|margin| * L[o,j]) * w[j,leaf,m].  With vec != NULL the feature lookup is the
+ * image+vector one (hingetree_fused_linear.cpp:414-767).  out is [B, O, K, M]. */
+int ho_linear_forward(int kind, const float *x, const float *vec, int64_t Cv, const float *thr, const int64_t *ord,
+                      const float *w, const float *lin, const float *bias, float *out,
+                      int64_t B, int64_t C, int64_t K, int64_t T, int64_t L, int64_t M, int64_t O) {
+  const int d = ho_depth_of(L);
+  if (d < 0) return -1;
+  const int64_t N = ho_threshold_count(kind, d);
+  for (int64_t o = 0; o < O; ++o)
+    for (int64_t i = 0; i < B; ++i)
+      for (int64_t k = 0; k < K; ++k)
+        for (int64_t m = 0; m < M; ++m) out[((i * O + o) * K + k) * M + m] = bias[o];
+  for (int64_t i = 0; i < B; ++i)
+    for (int64_t j = 0; j < T; ++j)
+      for (int64_t k = 0; k < K; ++k) {
+        ho_feat f = { x + (i * C) * K + k, K, vec ? vec + i * Cv : NULL, C };
+        const ho_path p = ho_traverse(kind, &f, thr + j * N, ord + j * N, d);
+        const float am = fabsf(p.margin);
+        for (int64_t o = 0; o < O; ++o) {
+          const float scale = am * lin[o * T + j];
+          for (int64_t m = 0; m < M; ++m)
+            out[((i * O + o) * K + k) * M + m] += scale * w[(j * L + p.key) * M + m];
+        }
+      }
+  return 0;
+}
+
+/* hingetree_fused_linear.cpp:267-409 (backward); g is [B, O, K, M].  Loop order i, j, k, o, m.
+ * The bias gradient is the plain sum of g over every dimension but O (the reference calls
+ * Tensor::sum, :385-390); it is accumulated in double here and rounded once. */
+int ho_linear_backward(int kind, const float *x, const float *vec, int64_t Cv, const float *thr, const int64_t *ord,
+                       const float *w, const float *lin, const float *g, float *gx, float *gvec, float *gthr,
+                       float *gw, float *glin, float *gbias,
+                       int64_t B, int64_t C, int64_t K, int64_t T, int64_t L, int64_t M, int64_t O) {
+  const int d = ho_depth_of(L);
+  if (d < 0) return -1;
+  const int64_t N = ho_threshold_count(kind, d);
+  for (int64_t i = 0; i < B; ++i)
+    for (int64_t j = 0; j < T; ++j)
+      for (int64_t k = 0; k < K; ++k) {
+        ho_feat f = { x + (i * C) * K + k, K, vec ? vec + i * Cv : NULL, C };
+        const ho_path p = ho_traverse(kind, &f, thr + j * N, ord + j * N, d);
+        const float sign = (float)((0.0f < p.margin) - (p.margin < 0.0f));
+        const float am = fabsf(p.margin);
+        const float *wl = w + (j * L + p.key) * M;
+        const int64_t c = ord[j * N + p.vertex];
+        for (int64_t o = 0; o < O; ++o) {
+          const float *gl = g + ((i * O + o) * K + k) * M;
+          const float lw = lin[o * T + j];
+          for (int64_t m = 0; m < M; ++m) {
+            if (gx || gvec) {
+              const float t = (sign * lw) * wl[m] * gl[m];
+              if (vec == NULL || c < C) { if (gx) gx[(i * C + c) * K + k] += t; }
+              else if (gvec) gvec[i * Cv + (c - C)] += t;
+            }
+            if (gthr) gthr[j * N + p.vertex] += (-sign * lw) * wl[m] * gl[m];
+            if (gw) gw[(j * L + p.key) * M + m] += (am * lw) * gl[m];
+            if (glin) glin[o * T + j] += am * wl[m] * gl[m];
+          }
+        }
+      }
+  if (gbias)
+    for (int64_t o = 0; o < O; ++o) {
+      double s = 0.0;
+      for (int64_t i = 0; i < B; ++i)
+        for (int64_t k = 0; k < K; ++k)
+          for (int64_t m = 0; m < M; ++m) s += (double)g[((i * O + o) * K + k) * M + m];
+      gbias[o] = (float)s;
+    }
+  return 0;
+}
