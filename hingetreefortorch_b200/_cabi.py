@@ -24,6 +24,7 @@ SYMBOLS = [
     "ht_forest_linear_workspace_bytes", "ht_forest_linear_forward_f32", "ht_forest_linear_backward_f32",
     "ht_conv_output_size", "ht_conv_workspace_bytes", "ht_conv_forward_f32", "ht_conv_backward_f32",
     "ht_contract", "ht_expand",
+    "ht_trie_forward_f32", "ht_trie_backward_f32", "ht_forest_touched_f32",
 ]
 
 

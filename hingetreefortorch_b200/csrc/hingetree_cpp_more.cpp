@@ -188,6 +188,166 @@ std::vector<torch::Tensor> linear_backward(int kind, torch::Tensor data, bool ne
   return {gdata, gthr, torch::Tensor(), gw, glin, gbias};
 }
 
+// ---- sparse gradients ----------------------------------------------------------------------------
+// The dense backward gives the values, ht_forest_touched_f32 the elements that were contributed
+// to; both are compacted into a coalesced COO tensor of the full shape, which is what the
+// reference's sparse operators return (hingetree_sparse_gpu.cu:422-457).
+
+torch::Tensor to_sparse(const torch::Tensor &dense, const torch::Tensor &mask_bytes) {
+  torch::Tensor mask = mask_bytes.view(dense.sizes()).to(torch::kBool);
+  torch::Tensor indices = mask.nonzero().t().contiguous();  // row-major order: sorted, unique
+  torch::Tensor values = dense.masked_select(mask);
+  torch::Tensor sparse = torch::sparse_coo_tensor(indices, values, dense.sizes(), dense.options().layout(torch::kSparse));
+  return sparse._coalesced_(true);
+}
+
+struct TouchedMasks {
+  torch::Tensor x, thr, w;
+};
+
+TouchedMasks touched_masks(const ht_forest_problem &problem, const torch::Tensor &x, bool need_x, const torch::Tensor &thr,
+                           bool need_thr, const torch::Tensor &ord, const torch::Tensor &w, bool need_w) {
+  TouchedMasks masks;
+  auto bytes = x.options().dtype(torch::kUInt8);
+  if (need_x) masks.x = torch::empty({x.numel()}, bytes);
+  if (need_thr) masks.thr = torch::empty({thr.numel()}, bytes);
+  if (need_w) masks.w = torch::empty({w.numel()}, bytes);
+  torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&problem), x);
+  raise_status(ht_forest_touched_f32(&problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
+                                     need_x ? masks.x.data_ptr<uint8_t>() : nullptr,
+                                     need_thr ? masks.thr.data_ptr<uint8_t>() : nullptr,
+                                     need_w ? masks.w.data_ptr<uint8_t>() : nullptr, ws.data_ptr(), ws.numel(), nullptr,
+                                     current_stream(x)),
+               "touched masks");
+  return masks;
+}
+
+std::vector<torch::Tensor> sparse_backward(int kind, torch::Tensor x, bool need_x, torch::Tensor thr, bool need_thr,
+                                           torch::Tensor ord, bool need_ord, torch::Tensor w, bool need_w, torch::Tensor g) {
+  if (need_ord) bad_runtime("Error: Gradient on inOrdinals is requested, but inOrdinals never has a gradient.");
+  ForestCall call(kind, x, thr, ord, w, &g);
+  c10::DeviceGuard guard(x.device());
+  std::vector<torch::Tensor> grads(4);
+  if (!need_x && !need_thr && !need_w) return grads;
+  torch::Tensor gx, gthr, gw;
+  if (need_x) gx = torch::empty_like(x);
+  if (need_thr) gthr = torch::empty_like(thr);
+  if (need_w) gw = torch::empty_like(w);
+  torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
+  OrdinalGuard og(ord, call.problem.C);
+  raise_status(ht_forest_backward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
+                                      w.data_ptr<float>(), g.data_ptr<float>(), ptr_or_null(gx), ptr_or_null(gthr),
+                                      ptr_or_null(gw), ws.data_ptr(), ws.numel(), og.word(), current_stream(x)),
+               "sparse forest backward");
+  og.finish();
+  TouchedMasks masks = touched_masks(call.problem, x, need_x, thr, need_thr, ord, w, need_w);
+  if (need_x) grads[0] = to_sparse(gx, masks.x);
+  if (need_thr) grads[1] = to_sparse(gthr, masks.thr);
+  if (need_w) grads[3] = to_sparse(gw, masks.w);
+  return grads;
+}
+
+std::vector<torch::Tensor> linear_backward(int kind, torch::Tensor data, bool need_data, const torch::Tensor *vec,
+                                           bool need_vec, torch::Tensor thr, bool need_thr, torch::Tensor ord,
+                                           bool need_ord, torch::Tensor w, bool need_w, torch::Tensor lin, bool need_lin,
+                                           torch::Tensor bias, bool need_bias, torch::Tensor g);
+
+// Sparse data / threshold / leaf-weight gradients; the linear layer's gradients stay dense
+// (hingetree_sparse_gpu.cu:743-761).
+std::vector<torch::Tensor> sparse_linear_backward(int kind, torch::Tensor x, bool need_x, torch::Tensor thr, bool need_thr,
+                                                  torch::Tensor ord, bool need_ord, torch::Tensor w, bool need_w,
+                                                  torch::Tensor lin, bool need_lin, torch::Tensor bias, bool need_bias,
+                                                  torch::Tensor g) {
+  std::vector<torch::Tensor> grads =
+      linear_backward(kind, x, need_x, nullptr, false, thr, need_thr, ord, need_ord, w, need_w, lin, need_lin, bias,
+                      need_bias, g);
+  if (!need_x && !need_thr && !need_w) return grads;
+  FamilyCall call(kind, x, nullptr, thr, ord, w, &lin, &bias, &g);
+  c10::DeviceGuard guard(x.device());
+  TouchedMasks masks = touched_masks(call.problem, x, need_x, thr, need_thr, ord, w, need_w);
+  if (need_x) grads[0] = to_sparse(grads[0], masks.x);
+  if (need_thr) grads[1] = to_sparse(grads[1], masks.thr);
+  if (need_w) grads[3] = to_sparse(grads[3], masks.w);
+  return grads;
+}
+
+// ---- trie ------------------------------------------------------------------------------------------
+// Weights are [T, 2^depth - 1, ...]: one row per internal vertex (hingetrie.cpp:43-49).
+
+struct TrieCall {
+  ht_forest_problem problem;
+  std::vector<int64_t> out_sizes;
+  TrieCall(const torch::Tensor &x, const torch::Tensor &thr, const torch::Tensor &ord, const torch::Tensor &w,
+           const torch::Tensor *g) {
+    if (x.dtype() != thr.dtype() || torch::kInt64 != ord.scalar_type() || x.dtype() != w.dtype() ||
+        (g != nullptr && x.dtype() != g->dtype()))
+      bad_argument("Error: inData, inThresholds, inWeights (and outDataGrad) are expected to share the same torch real "
+                   "number data type. inOrdinals is expected to be type torch.int64.");
+    if (x.device() != thr.device() || x.device() != ord.device() || x.device() != w.device() ||
+        (g != nullptr && x.device() != g->device()))
+      bad_argument("Error: All tensors are expected to be on the same device.");
+    if (!x.is_contiguous() || !thr.is_contiguous() || !ord.is_contiguous() || !w.is_contiguous() ||
+        (g != nullptr && !g->is_contiguous()))
+      bad_argument("Error: All tensors are expected to be contiguous.");
+    require_float32(x);
+    require_cuda(x);
+    if (x.dim() < 2 || thr.dim() != 2 || ord.dim() != 2 || w.dim() < 2)
+      bad_argument("Error: inData, inWeights must have at least 2 dimensions. inThresholds and inOrdinals must have 2 "
+                   "dimensions.");
+    if (thr.sizes() != ord.sizes() || w.size(0) != thr.size(0) || w.size(1) != thr.size(1))
+      bad_argument("Error: inThresholds and inOrdinals must be the same shape, and inWeights.shape[:2] must equal it.");
+    const int depth = depth_of(w.size(1) + 1);
+    if (depth > 31 || depth < 1) {
+      std::ostringstream ss;
+      ss << "Error: The tree depth exceeds compile-time constraints or the number of thresholds is incorrect for the "
+            "tree depth (tree depth = "
+         << depth << ").";
+      bad_runtime(ss.str());
+    }
+    problem = {HT_KIND_TREE, depth, x.size(0), x.size(1), inner_count(x, 2), w.size(0), inner_count(w, 2), 0, 0};
+    out_sizes = {x.size(0), w.size(0)};
+    for (int64_t d = 2; d < x.dim(); ++d) out_sizes.push_back(x.size(d));
+    for (int64_t d = 2; d < w.dim(); ++d) out_sizes.push_back(w.size(d));
+    if (g != nullptr && g->sizes() != c10::IntArrayRef(out_sizes))
+      bad_argument("Error: outDataGrad.shape does not match the expected shape.");
+  }
+};
+
+torch::Tensor trie_forward(torch::Tensor x, torch::Tensor thr, torch::Tensor ord, torch::Tensor w) {
+  TrieCall call(x, thr, ord, w, nullptr);
+  c10::DeviceGuard guard(x.device());
+  torch::Tensor out = torch::empty(call.out_sizes, x.options());
+  torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
+  OrdinalGuard og(ord, call.problem.C);
+  raise_status(ht_trie_forward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
+                                   w.data_ptr<float>(), out.data_ptr<float>(), ws.data_ptr(), ws.numel(), og.word(),
+                                   current_stream(x)),
+               "trie forward");
+  og.finish();
+  return out;
+}
+
+std::vector<torch::Tensor> trie_backward(torch::Tensor x, bool need_x, torch::Tensor thr, bool need_thr, torch::Tensor ord,
+                                         bool need_ord, torch::Tensor w, bool need_w, torch::Tensor g) {
+  if (need_ord) bad_runtime("Error: Gradient on inOrdinals is requested, but inOrdinals never has a gradient.");
+  TrieCall call(x, thr, ord, w, &g);
+  c10::DeviceGuard guard(x.device());
+  std::vector<torch::Tensor> grads(4);
+  if (!need_x && !need_thr && !need_w) return grads;
+  if (need_x) grads[0] = torch::empty_like(x);
+  if (need_thr) grads[1] = torch::empty_like(thr);
+  if (need_w) grads[3] = torch::empty_like(w);
+  torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
+  OrdinalGuard og(ord, call.problem.C);
+  raise_status(ht_trie_backward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
+                                    w.data_ptr<float>(), g.data_ptr<float>(), ptr_or_null(grads[0]),
+                                    ptr_or_null(grads[1]), ptr_or_null(grads[3]), ws.data_ptr(), ws.numel(), og.word(),
+                                    current_stream(x)),
+               "trie backward");
+  og.finish();
+  return grads;
+}
+
 // ---- convolution -------------------------------------------------------------------------------
 // Checks follow hingetree_conv.cpp:51-130 (argument problems -> ValueError; geometry, ordinal
 // range and depth -> RuntimeError).
@@ -437,12 +597,29 @@ void bind_more_ops(pybind11::module_ &m) {
   HT_BIND_CONV("fern", HT_KIND_FERN, 3)
   m.def("contract", &contract_op, "Collapse batched 2D or 3D image to 2D or 3D images of patches.");
   m.def("expand", &expand_op, "Expand batched 2D or 3D images of patches to 2D or 3D images.");
-  static const char *const names[] = {"sparse_tree_backward",  "sparse_fern_backward",
-                                      "trie_forward",          "trie_backward",
-                                      "trie_init_medians",     "sparse_tree_fused_linear_backward",
-                                      "sparse_fern_fused_linear_backward"};
-  for (const char *name : names)
-    m.def(name, [name](pybind11::args, pybind11::kwargs) -> pybind11::object { pending(name); });
+  m.def("sparse_tree_backward", [](torch::Tensor x, bool nx, torch::Tensor t, bool nt, torch::Tensor o, bool no,
+                                   torch::Tensor w, bool nw, torch::Tensor g) {
+    return sparse_backward(HT_KIND_TREE, x, nx, t, nt, o, no, w, nw, g);
+  });
+  m.def("sparse_fern_backward", [](torch::Tensor x, bool nx, torch::Tensor t, bool nt, torch::Tensor o, bool no,
+                                   torch::Tensor w, bool nw, torch::Tensor g) {
+    return sparse_backward(HT_KIND_FERN, x, nx, t, nt, o, no, w, nw, g);
+  });
+  m.def("sparse_tree_fused_linear_backward",
+        [](torch::Tensor x, bool nx, torch::Tensor t, bool nt, torch::Tensor o, bool no, torch::Tensor w, bool nw,
+           torch::Tensor l, bool nl, torch::Tensor b, bool nb, torch::Tensor g) {
+          return sparse_linear_backward(HT_KIND_TREE, x, nx, t, nt, o, no, w, nw, l, nl, b, nb, g);
+        });
+  m.def("sparse_fern_fused_linear_backward",
+        [](torch::Tensor x, bool nx, torch::Tensor t, bool nt, torch::Tensor o, bool no, torch::Tensor w, bool nw,
+           torch::Tensor l, bool nl, torch::Tensor b, bool nb, torch::Tensor g) {
+          return sparse_linear_backward(HT_KIND_FERN, x, nx, t, nt, o, no, w, nw, l, nl, b, nb, g);
+        });
+  m.def("trie_forward", &trie_forward, "Hinge trie forward.");
+  m.def("trie_backward", &trie_backward, "Hinge trie backward.");
+  m.def("trie_init_medians", [](torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor) -> bool {
+    pending("trie_init_medians (a one-time CPU initialisation outside the evaluation path)");
+  });
 }
 
 }  // namespace htx

@@ -168,6 +168,30 @@ int ht_forest_linear_backward_f32(const ht_forest_problem *p, int64_t out_channe
                                   float *glin, void *workspace, size_t workspace_bytes, uint32_t *status_word,
                                   ht_stream_t stream);
 
+/* ---- hinge trie ---------------------------------------------------------------------------------
+ *   out[i,j,k,m] = sum over depth d (ascending) of |margin_d| * w[j, vertex_d, m]
+ * every decision on the path contributes; w is [T, 2^depth - 1, M], one row per internal vertex
+ * (p->kind must be HT_KIND_TREE).  The reference implements tries on the CPU only
+ * (hingetrie.cpp:33-267, traversal HingeTrieCommon.h:71-85; CUDA tensors get an empty result,
+ * hingetrie.cpp:286-288); these entries evaluate the same arithmetic on the GPU, the forward in
+ * the same order.  Workspace: ht_forest_workspace_bytes(p). */
+int ht_trie_forward_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
+                        float *out, void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+int ht_trie_backward_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
+                         const float *g, float *gx, float *gthr, float *gw, void *workspace, size_t workspace_bytes,
+                         uint32_t *status_word, ht_stream_t stream);
+
+/* ---- which gradient elements receive a contribution --------------------------------------------
+ * Byte masks (1 = some (i,j,k) contributes) shaped like x, thr and w; any may be NULL; cleared
+ * here.  Together with ht_forest_backward_f32 / ht_forest_linear_backward_f32 this replaces the
+ * hash-table construction of sparse gradients in sparse_hingetree_gpu_backward and
+ * sparse_hingetree_fused_linear_gpu_backward (hingetree_sparse_gpu.cu:461-764, IndexMap 61-101):
+ * the binding compacts (mask, dense values) into a coalesced COO tensor.
+ * Workspace: ht_forest_workspace_bytes(p). */
+int ht_forest_touched_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
+                          uint8_t *touched_x, uint8_t *touched_thr, uint8_t *touched_w, void *workspace,
+                          size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+
 /* ---- convolutional hinge trees / ferns, 1-D / 2-D / 3-D -------------------------------------
  *   out[i,j,p,m] = sum over input channels c (ascending) of |margin(i,c,j,p)| * w[j,c,leaf,m]
  * where tree (j,c) is evaluated on the kernel window of input channel c at output position p;

@@ -13,7 +13,7 @@ import subprocess
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = [os.path.join(HERE, "hinge_oracle.c"), os.path.join(HERE, "hinge_oracle_conv.c")]
+SOURCES = [os.path.join(HERE, name) for name in ("hinge_oracle.c", "hinge_oracle_conv.c", "hinge_oracle_trie.c")]
 LIB = os.path.join(HERE, "libhinge_oracle.so")
 
 _KIND = {"tree": 0, "fern": 1}
@@ -150,6 +150,26 @@ def linear_backward(kind, x, thr, ord_, w, lin, g, vec=None):
     if vec is None:
         return gx, gthr, gw, glin, gbias
     return gx, gvec, gthr, gw, glin, gbias
+
+
+def trie_forward(x, thr, ord_, w):
+    """Hinge trie: w is [T, 2^depth - 1, *extra] (one row per internal vertex)."""
+    x, thr, ord_, w = _f32(x), _f32(thr), _i64(ord_), _f32(w)
+    B, C, K, T, N, M = _dims(x, w)
+    out = np.empty((B, T) + x.shape[2:] + w.shape[2:], dtype=np.float32)
+    if lib().ho_trie_forward(_p(x), _p(thr), _p(ord_), _p(w), _p(out), _i(B), _i(C), _i(K), _i(T), _i(N), _i(M)) != 0:
+        raise ValueError("threshold count + 1 is not a power of two")
+    return out
+
+
+def trie_backward(x, thr, ord_, w, g):
+    x, thr, ord_, w, g = _f32(x), _f32(thr), _i64(ord_), _f32(w), _f32(g)
+    B, C, K, T, N, M = _dims(x, w)
+    gx, gthr, gw = np.zeros_like(x), np.zeros_like(thr), np.zeros_like(w)
+    if lib().ho_trie_backward(_p(x), _p(thr), _p(ord_), _p(w), _p(g), _p(gx), _p(gthr), _p(gw), _i(B), _i(C), _i(K),
+                              _i(T), _i(N), _i(M)) != 0:
+        raise ValueError("threshold count + 1 is not a power of two")
+    return gx, gthr, gw
 
 
 def _i64s(values):

@@ -99,6 +99,114 @@ def main():
 
     np.savez_compressed(os.path.join(HERE, "forest.npz"), **out)
     print("wrote forest.npz with", len(out), "arrays")
+    families(ref)
+
+
+LINEAR_CASES = [
+    # kind, B, C, inner, T, depth, extra, O, Cv (0 = no vector: plain fused linear)
+    ("tree", 7, 9, (), 5, 3, (), 4, 0),
+    ("fern", 5, 11, (3,), 4, 4, (2,), 3, 0),
+    ("tree", 6, 5, (2,), 4, 3, (2,), 3, 4),
+    ("fern", 6, 5, (), 4, 3, (), 2, 3),
+]
+
+CONV_CASES = [
+    # dims, x shape, Co, depth, extra, kernel, stride, padding, dilation
+    (1, (2, 3, 9), 4, 2, (), (3,), (1,), (1,), (1,)),
+    (2, (2, 3, 6, 7), 4, 3, (), (3, 3), (1, 1), (1, 1), (1, 1)),
+    (2, (1, 2, 8, 9), 3, 2, (2,), (2, 3), (2, 1), (1, 2), (2, 1)),
+    (3, (1, 2, 5, 6, 4), 2, 2, (), (2, 3, 2), (1, 2, 1), (1, 0, 1), (1, 1, 2)),
+]
+
+PATCH_CASES = [((2, 3, 7, 9), (2, 3), (1, 0)), ((1, 2, 8, 8), (4, 4), (2, 2)), ((1, 2, 5, 6, 7), (2, 3, 2), (1, 1, 0))]
+
+
+def families(ref):
+    """Fused linear, image+vector fusion, convolution and contract/expand vectors -> families.npz."""
+    out = {}
+    for idx, (kind, B, C, inner, T, depth, extra, O, Cv) in enumerate(LINEAR_CASES):
+        gen = torch.Generator().manual_seed(500 + idx)
+        N = decisions(kind, depth)
+        x = torch.randn((B, C) + inner, generator=gen)
+        thr = torch.rand((T, N), generator=gen) * 6 - 3
+        ord_ = torch.randint(0, C + Cv, (T, N), generator=gen)
+        w = torch.randn((T, 2 ** depth) + extra, generator=gen)
+        lin = torch.randn((O, T), generator=gen)
+        bias = torch.randn(O, generator=gen)
+        p = "linear%02d_" % idx
+        out[p + "kind"] = np.array(kind)
+        tensors = [("x", x), ("thr", thr), ("ord", ord_), ("w", w), ("lin", lin), ("bias", bias)]
+        if Cv:
+            vec = torch.randn((B, Cv), generator=gen)
+            tensors.append(("vec", vec))
+            f = getattr(ref, kind + "_fusion_fused_linear_forward")(x, vec, thr, ord_, w, lin, bias)
+            g = torch.randn(f.shape, generator=gen)
+            grads = getattr(ref, kind + "_fusion_fused_linear_backward")(x, True, vec, True, thr, True, ord_, False, w,
+                                                                         True, lin, True, bias, True, g)
+            names = ["gx", "gvec", "gthr", None, "gw", "glin", "gbias"]
+            ff = getattr(ref, kind + "_fusion_forward")(x, vec, thr, ord_, w)
+            g2 = torch.randn(ff.shape, generator=gen)
+            fg = getattr(ref, kind + "_fusion_backward")(x, True, vec, True, thr, True, ord_, False, w, True, g2)
+            tensors += [("fusion_out", ff), ("fusion_g", g2), ("fusion_gx", fg[0]), ("fusion_gvec", fg[1]),
+                        ("fusion_gthr", fg[2]), ("fusion_gw", fg[4])]
+        else:
+            f = getattr(ref, kind + "_fused_linear_forward")(x, thr, ord_, w, lin, bias)
+            g = torch.randn(f.shape, generator=gen)
+            grads = getattr(ref, kind + "_fused_linear_backward")(x, True, thr, True, ord_, False, w, True, lin, True,
+                                                                  bias, True, g)
+            names = ["gx", "gthr", None, "gw", "glin", "gbias"]
+        tensors += [("out", f), ("g", g)] + [(n, t) for n, t in zip(names, grads) if n is not None]
+        for name, t in tensors:
+            out[p + name] = t.numpy()
+    out["linear_count"] = np.array(len(LINEAR_CASES))
+
+    for kidx, kind in enumerate(("tree", "fern")):
+        for cidx, (dims, xs, Co, depth, extra, kernel, stride, padding, dilation) in enumerate(CONV_CASES):
+            gen = torch.Generator().manual_seed(700 + 10 * kidx + cidx)
+            Ci, N, cells = xs[1], decisions(kind, depth), int(np.prod(kernel))
+            x = torch.randn(xs, generator=gen)
+            thr = torch.rand((Co, Ci, N), generator=gen) * 2 - 1
+            ord_ = torch.randint(0, cells, (Co, Ci, N), generator=gen)
+            w = torch.randn((Co, Ci, 2 ** depth) + extra, generator=gen)
+            geometry = [list(kernel), list(stride), list(padding), list(dilation)]
+            f = getattr(ref, "%s_conv%dd_forward" % (kind, dims))(x, thr, ord_, w, *geometry)
+            g = torch.randn(f.shape, generator=gen)
+            gx, gthr, _, gw = getattr(ref, "%s_conv%dd_backward" % (kind, dims))(x, True, thr, True, ord_, False, w, True,
+                                                                               g, *geometry)
+            p = "conv%02d_" % (len(CONV_CASES) * kidx + cidx)
+            out[p + "kind"] = np.array(kind)
+            out[p + "geometry"] = np.array(geometry)
+            for name, t in [("x", x), ("thr", thr), ("ord", ord_), ("w", w), ("out", f), ("g", g), ("gx", gx),
+                            ("gthr", gthr), ("gw", gw)]:
+                out[p + name] = t.numpy()
+    out["conv_count"] = np.array(2 * len(CONV_CASES))
+
+    for idx, (xs, window, padding) in enumerate(PATCH_CASES):
+        x = torch.randint(-100, 100, xs, generator=torch.Generator().manual_seed(900 + idx)).to(torch.int16)
+        c = ref.contract(x, list(window), list(padding))
+        p = "patch%02d_" % idx
+        out[p + "x"], out[p + "window"], out[p + "padding"] = x.numpy(), np.array(window), np.array(padding)
+        out[p + "contracted"], out[p + "expanded"] = c.numpy(), ref.expand(c, list(padding)).numpy()
+    out["patch_count"] = np.array(len(PATCH_CASES))
+
+    # hinge tries (CPU only in the reference): weights sit on the internal vertices
+    for idx, (B, C, inner, T, depth, extra) in enumerate([(9, 7, (), 5, 3, ()), (4, 6, (3,), 3, 4, (2,))]):
+        gen = torch.Generator().manual_seed(950 + idx)
+        N = 2 ** depth - 1
+        x = torch.randn((B, C) + inner, generator=gen)
+        thr = torch.rand((T, N), generator=gen) * 4 - 2
+        ord_ = torch.randint(0, C, (T, N), generator=gen)
+        w = torch.randn((T, N) + extra, generator=gen)
+        f = ref.trie_forward(x, thr, ord_, w)
+        g = torch.randn(f.shape, generator=gen)
+        gx, gthr, _, gw = ref.trie_backward(x, True, thr, True, ord_, False, w, True, g)
+        p = "trie%02d_" % idx
+        for name, t in [("x", x), ("thr", thr), ("ord", ord_), ("w", w), ("out", f), ("g", g), ("gx", gx),
+                        ("gthr", gthr), ("gw", gw)]:
+            out[p + name] = t.numpy()
+    out["trie_count"] = np.array(2)
+    np.savez_compressed(os.path.join(HERE, "families.npz"), **out)
+    print("wrote families.npz with", len(out), "arrays")
 
 
 if __name__ == "__main__":
