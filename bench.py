@@ -1,21 +1,24 @@
 #!/usr/bin/env python
 """Benchmark of the hinge forest evaluation path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c2|c1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c2|c1|c4|c5]
 
 A step is one pass of the hot path over one batch of seeded synthetic input.  The default
-workload is the large-batch forest inference configuration (x [1048576,128] ~ N(0,1), 1024
-trees of depth 8, thresholds U(-3,3), feature indices U[0,127], leaf weights N(0,1)); with N
-GPUs every rank evaluates its own batch of that size against replicated parameters (weak
-scaling, no communication in the data path).  Rank 0 prints ONE JSON line:
+workload (c3) is the large-batch forest inference configuration: x [1048576,128] ~ N(0,1), 1024
+trees of depth 8, thresholds U(-3,3), feature indices U[0,127], leaf weights N(0,1).  With N GPUs
+every rank evaluates its own batch of that size against replicated parameters (weak scaling; the
+forward has no communication, the training workloads all-reduce the parameter gradients once per
+step).  Rank 0 prints ONE JSON line:
 
-  value      tree-evals/s, whole job, inputs resident in HBM, timed with CUDA events, max over ranks
-  e2e        the same metric through the reference-facing operator (hingetree_cpp.tree_forward) with
-             HOST buffers: pinned input copied in, full output copied back, inside the timed region
-  roofline   algorithmic bytes of one forward / measured launch time, against the measured HBM peak
-  cpu_baseline   the CPU restatement of the reference algorithm on this machine's host cores
-                 (bounded sample of the same workload)
+  value         tree-evals/s, whole job, inputs resident in HBM, CUDA events, max over ranks
+  e2e           the same metric through the reference-facing operators / modules with HOST buffers:
+                pinned input copied in and the result copied back inside the timed region
+  roofline      algorithmic bytes of one step / measured step time, against the measured HBM peak
+  cpu_baseline  the C restatement of the reference algorithm on all host threads (bounded sample)
+  fwd_bwd       (c3 only) forward + backward of the same shape, device resident
 
+Other workloads: c1 (the reference's speedtest shape, fwd+bwd), c2 (ferns, fwd+bwd), c4 (2-D
+convolution, fwd+bwd), c5 (Linear -> BatchNorm1d -> sequential-ordinal forest training step).
 `--impl reference` times the reference's own CPU implementation (oracle/_ref when it was built,
 else the C restatement) on all host cores, on a bounded sample per step.
 """
@@ -32,13 +35,16 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: kind, B, C, T, depth, M (0 = no inner weight dim), backward
-    "c3": dict(kind="tree", B=1048576, C=128, T=1024, depth=8, M=0, x="randn", bwd=False,
+    "c3": dict(op="forest", kind="tree", B=1048576, C=128, T=1024, depth=8, M=0, x="randn", bwd=False,
                name="C3 large-batch forest inference x[1048576,128] T=1024 depth=8"),
-    "c2": dict(kind="fern", B=4096, C=256, T=500, depth=10, M=10, x="randn", bwd=True,
+    "c2": dict(op="forest", kind="fern", B=4096, C=256, T=500, depth=10, M=10, x="randn", bwd=True,
                name="C2 fern fwd+bwd x[4096,256] T=500 depth=10 extra_outputs=10"),
-    "c1": dict(kind="tree", B=100, C=1000, T=100, depth=7, M=1, x="rand", bwd=True,
+    "c1": dict(op="forest", kind="tree", B=100, C=1000, T=100, depth=7, M=1, x="rand", bwd=True,
                name="C1 forest fwd+bwd x[100,1000] T=100 depth=7 extra_outputs=1"),
+    "c4": dict(op="conv", kind="tree", B=64, C=64, T=128, depth=5, M=0, x="randn", bwd=True, H=64, W=64,
+               name="C4 HingeTreeConv2d fwd+bwd x[64,64,64,64] 3x3 s1 p1, 128x64 trees depth 5"),
+    "c5": dict(op="pipeline", kind="tree", B=8192, C=784, T=100, depth=7, M=0, x="rand", bwd=True, hidden=12700,
+               name="C5 Linear(784->12700) -> BatchNorm1d -> forest(100 trees depth 7, sequential ordinals) train step"),
 }
 
 
@@ -46,34 +52,56 @@ def decisions(kind, depth):
     return depth if kind == "fern" else 2 ** depth - 1
 
 
-def algorithmic_bytes(wl, B, backward=False):
+def evals_per_step(wl, B):
+    if wl["op"] == "conv":
+        return B * wl["H"] * wl["W"] * wl["T"] * wl["C"]  # one tree per (out channel, in channel, position)
+    return B * wl["T"]
+
+
+def algorithmic_bytes(wl, B, backward):
     """Compulsory traffic with the API's dtypes (fp32 data, int64 ordinals), each tensor touched once."""
-    C, T, depth, M = wl["C"], wl["T"], wl["depth"], max(wl["M"], 1)
+    depth, M = wl["depth"], max(wl["M"], 1)
     N, L = decisions(wl["kind"], depth), 2 ** depth
-    fwd = 4 * B * C + 12 * T * N + 4 * T * L * M + 4 * B * T * M
+    if wl["op"] == "conv":
+        trees = wl["T"] * wl["C"]
+        x_bytes, out_bytes = 4 * B * wl["C"] * wl["H"] * wl["W"], 4 * B * wl["T"] * wl["H"] * wl["W"] * M
+    else:
+        C = wl["hidden"] if wl["op"] == "pipeline" else wl["C"]
+        trees = wl["T"]
+        x_bytes, out_bytes = 4 * B * C, 4 * B * wl["T"] * M
+    params = 12 * trees * N + 4 * trees * L * M
+    fwd = x_bytes + params + out_bytes
     if not backward:
         return fwd
-    bwd = (4 * B * C + 12 * T * N + 4 * T * L * M + 4 * B * T * M) + (4 * B * C + 4 * T * N + 4 * T * L * M)
-    return fwd + bwd
+    return fwd + (x_bytes + params + out_bytes) + (x_bytes + 4 * trees * N + 4 * trees * L * M)
 
 
 def make_params(wl, seed=0):
     import torch
     gen = torch.Generator().manual_seed(seed)
     N, L = decisions(wl["kind"], wl["depth"]), 2 ** wl["depth"]
+    extra = (wl["M"],) if wl["M"] else ()
+    if wl["op"] == "conv":
+        thr = torch.rand((wl["T"], wl["C"], N), generator=gen) * 6 - 3
+        ord_ = torch.randint(0, 9, (wl["T"], wl["C"], N), generator=gen)
+        w = torch.randn((wl["T"], wl["C"], L) + extra, generator=gen)
+        return thr, ord_, w
+    C = wl["hidden"] if wl["op"] == "pipeline" else wl["C"]
     thr = torch.rand((wl["T"], N), generator=gen) * 6 - 3
-    ord_ = torch.randint(0, wl["C"], (wl["T"], N), generator=gen)
-    wshape = (wl["T"], L) + ((wl["M"],) if wl["M"] else ())
-    w = torch.randn(wshape, generator=gen)
+    if wl["op"] == "pipeline":
+        ord_ = (torch.arange(wl["T"] * N) % C).view(wl["T"], N)
+    else:
+        ord_ = torch.randint(0, C, (wl["T"], N), generator=gen)
+    w = torch.randn((wl["T"], L) + extra, generator=gen)
     return thr, ord_, w
 
 
-def make_x(wl, rows, seed):
+def make_x(wl, rows, seed, channels=None):
     import torch
     gen = torch.Generator().manual_seed(1000 + seed)
-    if wl["x"] == "rand":
-        return torch.rand((rows, wl["C"]), generator=gen)
-    return torch.randn((rows, wl["C"]), generator=gen)
+    C = channels or wl["C"]
+    shape = (rows, C, wl["H"], wl["W"]) if wl["op"] == "conv" else (rows, C)
+    return torch.rand(shape, generator=gen) if wl["x"] == "rand" else torch.randn(shape, generator=gen)
 
 
 # ---- clocks -------------------------------------------------------------------------------
@@ -93,7 +121,7 @@ class ClockSampler:
         try:
             self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -124,64 +152,79 @@ class ClockSampler:
                     reasons.add(name)
         self.file.close()
         os.unlink(self.file.name)
-        # samples taken under load are the upper half of the clock readings when the region is short
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
 # ---- CPU legs ------------------------------------------------------------------------------
 
-def _cpu_forward_port(args):
-    kind, x, thr, ord_, w = args
+def cpu_channels(wl):
+    """Feature count the trees see on the CPU legs (the pipeline's forest stage reads the hidden activations)."""
+    return wl["hidden"] if wl["op"] == "pipeline" else wl["C"]
+
+
+def _cpu_forward_port(job):
     from oracle import hinge_oracle as ho
+    op, kind, x, thr, ord_, w = job
+    if op == "conv":
+        return ho.conv_forward(kind, x, thr, ord_, w, (3, 3), (1, 1), (1, 1), (1, 1)).shape[0]
     return ho.forward(kind, x, thr, ord_, w).shape[0]
 
 
 def cpu_port_rate(wl, rows, threads):
-    """The C restatement on `threads` host threads (ctypes releases the GIL), rows split evenly."""
+    """The C restatement (forward) on `threads` host threads (ctypes releases the GIL), rows split evenly."""
     import numpy as np
     from concurrent.futures import ThreadPoolExecutor
     from oracle import hinge_oracle as ho
     ho.lib()
     thr, ord_, w = [t.numpy() for t in make_params(wl)]
-    x = make_x(wl, rows, 0).numpy()
+    x = make_x(wl, rows, 0, cpu_channels(wl)).numpy()
     parts = [p for p in np.array_split(x, threads) if len(p)]
-    jobs = [(wl["kind"], p, thr, ord_, w) for p in parts]
+    jobs = [(wl["op"], wl["kind"], p, thr, ord_, w) for p in parts]
     with ThreadPoolExecutor(max_workers=threads) as ex:
         t0 = time.perf_counter()
         list(ex.map(_cpu_forward_port, jobs))
         dt = time.perf_counter() - t0
-    return rows * wl["T"] / dt, dt
+    return evals_per_step(wl, rows) / dt, dt
+
+
+def cpu_sample_rows(wl, cores, seconds=12.0):
+    """Rows whose forward takes about `seconds` of wall time on `cores` cores at ~80 ns per tree evaluation."""
+    per_row = evals_per_step(wl, 1) * 80e-9
+    return int(max(min(cores, wl["B"]), min(wl["B"], seconds * cores / per_row)))
 
 
 _REF_STATE = {}
 
 
-def _ref_worker_init(kind, thr, ord_, w):
+def _ref_worker_init(op, kind, thr, ord_, w):
     import torch
     torch.set_num_threads(1)
     from oracle import build_ref
     _REF_STATE["mod"] = build_ref.load()
-    _REF_STATE["args"] = (kind, thr, ord_, w)
+    _REF_STATE["args"] = (op, kind, thr, ord_, w)
 
 
 def _ref_worker_run(x):
-    kind, thr, ord_, w = _REF_STATE["args"]
-    out = getattr(_REF_STATE["mod"], kind + "_forward")(x, thr, ord_, w)
+    op, kind, thr, ord_, w = _REF_STATE["args"]
+    mod = _REF_STATE["mod"]
+    if op == "conv":
+        out = getattr(mod, kind + "_conv2d_forward")(x, thr, ord_, w, [3, 3], [1, 1], [1, 1], [1, 1])
+    else:
+        out = getattr(mod, kind + "_forward")(x, thr, ord_, w)
     return out.shape[0]
 
 
 def reference_arm(a, wl):
-    """The reference's own CPU implementation on all host cores, bounded sample per step."""
+    """The reference's own CPU implementation (forward) on all host cores, bounded sample per step."""
     import torch
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     cores = os.cpu_count() or 1
-    rows_per_core = max(1, min(wl["B"] // cores, 512 if wl["T"] * wl["depth"] >= 4096 else wl["B"]))
-    rows = rows_per_core * cores
+    rows = cpu_sample_rows(wl, cores, seconds=0.5)
+    rows = max(cores, rows - rows % cores) if rows >= cores else rows
     thr, ord_, w = make_params(wl)
-    x = make_x(wl, rows, 0)
+    x = make_x(wl, rows, 0, cpu_channels(wl))
     kind_used = "reference"
     try:
         from oracle import build_ref
@@ -192,8 +235,8 @@ def reference_arm(a, wl):
     if kind_used == "reference":
         import multiprocessing as mp
         ctx = mp.get_context("fork")
-        with ctx.Pool(cores, initializer=_ref_worker_init, initargs=(wl["kind"], thr, ord_, w)) as pool:
-            chunks = list(torch.chunk(x, cores))
+        with ctx.Pool(cores, initializer=_ref_worker_init, initargs=(wl["op"], wl["kind"], thr, ord_, w)) as pool:
+            chunks = [c for c in torch.chunk(x, cores) if c.shape[0]]
             for step in range(a.warmup + a.steps):
                 t0 = time.perf_counter()
                 pool.map(_ref_worker_run, chunks)
@@ -206,8 +249,8 @@ def reference_arm(a, wl):
             if step >= a.warmup:
                 times.append(dt)
     total = sum(times)
-    value = rows * wl["T"] * len(times) / total
-    sample = "%d of %d rows per step (%d per core), all %d trees" % (rows, wl["B"], rows_per_core, wl["T"])
+    value = evals_per_step(wl, rows) * len(times) / total
+    sample = "forward of %d of %d rows per step on %d cores" % (rows, wl["B"], cores)
     line = {
         "impl": "reference", "metric": "tree-evals/sec fwd", "value": value, "unit": "tree-evals/s",
         "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 * total / len(times),
@@ -220,72 +263,217 @@ def reference_arm(a, wl):
     print(json.dumps(line), flush=True)
 
 
-# ---- our arm --------------------------------------------------------------------------------
+# ---- our arm: one runner per kind of workload ------------------------------------------------
+
+class ForestRunner:
+    """Plain forest / fern through the C ABI (device resident) and through hingetree_cpp (end to end)."""
+
+    def __init__(self, wl, B, device, rank):
+        import torch
+        from hingetreefortorch_b200 import _cabi
+        from hingetreefortorch_b200._ext import hingetree_cpp
+        self.wl, self.B, self.device, self.torch, self.ext = wl, B, device, torch, hingetree_cpp
+        self.thr, self.ord, self.w = [t.to(device) for t in make_params(wl)]
+        self.x_host = make_x(wl, B, rank)
+        self.x = self.x_host.to(device)
+        self.forest = _cabi.Forest(wl["kind"], self.x, self.w)
+        self.out = torch.empty(self.forest.out_shape, dtype=torch.float32, device=device)
+        self.g = None
+        # ordinal pack (+ record repack when the tile kernel runs) + the evaluation kernel
+        self.launches = 3 if wl["M"] in (0, 1) and B * wl["T"] >= 32768 else 2
+
+    def enable_backward(self):
+        torch = self.torch
+        if self.g is None:
+            self.g = torch.randn(self.forest.out_shape, generator=torch.Generator(device=self.device).manual_seed(5),
+                                 device=self.device)
+            self.grads = (torch.empty_like(self.x), torch.empty_like(self.thr), torch.empty_like(self.w))
+
+    def step(self, backward):
+        self.forest.forward(self.x, self.thr, self.ord, self.w, out=self.out)
+        if backward:
+            self.forest.backward(self.x, self.thr, self.ord, self.w, self.g, outs=self.grads)
+
+    def launches_per_step(self, backward):
+        return self.launches + (2 if backward else 0)
+
+    def check(self):
+        if self.forest.ordinal_flags() != 0:
+            raise SystemExit("bench.py: device status word set (ordinal range or pipeline timeout)")
+
+    def prepare_e2e(self):
+        torch, B = self.torch, self.B
+        self.chunk = min(B, 65536)
+        self.x_pinned = self.x_host.pin_memory()
+        self.out_pinned = torch.empty(self.forest.out_shape, dtype=torch.float32).pin_memory()
+        self.copy_in, self.copy_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        self.fwd = getattr(self.ext, self.wl["kind"] + "_forward")
+        self.bwd = getattr(self.ext, self.wl["kind"] + "_backward")
+        if self.wl["bwd"]:
+            self.g_pinned = self.g.cpu().pin_memory()
+            self.gx_pinned = torch.empty_like(self.x_host).pin_memory()
+        elem = 4 * max(self.wl["M"], 1)
+        h2d, d2h = 4 * B * self.wl["C"], elem * B * self.wl["T"]
+        if self.wl["bwd"]:
+            h2d, d2h = h2d + d2h, d2h + 4 * B * self.wl["C"]
+        return h2d, d2h, ("hingetree_cpp.%s_forward%s on %d-row chunks, pinned host buffers, 3 streams"
+                          % (self.wl["kind"], "/_backward" if self.wl["bwd"] else "", self.chunk))
+
+    def e2e_step(self):
+        torch, B, chunk = self.torch, self.B, self.chunk
+        compute = torch.cuda.current_stream(self.device)
+        keep = []
+        for lo in range(0, B, chunk):
+            hi = min(B, lo + chunk)
+            with torch.cuda.stream(self.copy_in):
+                xc = self.x_pinned[lo:hi].to(self.device, non_blocking=True)
+                gc = self.g_pinned[lo:hi].to(self.device, non_blocking=True) if self.wl["bwd"] else None
+                ready = torch.cuda.Event()
+                ready.record(self.copy_in)
+            compute.wait_event(ready)
+            oc = self.fwd(xc, self.thr, self.ord, self.w)
+            gxc = None
+            if self.wl["bwd"]:
+                gxc = self.bwd(xc, True, self.thr, True, self.ord, False, self.w, True, gc)[0]
+                gc.record_stream(compute)
+            xc.record_stream(compute)
+            done = torch.cuda.Event()
+            done.record(compute)
+            self.copy_out.wait_event(done)
+            with torch.cuda.stream(self.copy_out):
+                self.out_pinned[lo:hi].copy_(oc, non_blocking=True)
+                oc.record_stream(self.copy_out)
+                if gxc is not None:
+                    self.gx_pinned[lo:hi].copy_(gxc, non_blocking=True)
+                    gxc.record_stream(self.copy_out)
+            keep.append((oc, gxc))
+        self.copy_out.synchronize()
+
+    def verify_e2e(self):
+        if not self.torch.equal(self.out_pinned[:256], self.out[:256].cpu()):
+            raise SystemExit("bench.py: end-to-end output differs from the device-resident output")
+
+
+class ModuleRunner:
+    """Workloads driven through the nn.Module surface: convolution (c4) and the Linear->BN->forest pipeline (c5)."""
+
+    def __init__(self, wl, B, device, rank, world):
+        import torch
+        import torch.nn as nn
+        from hingetreefortorch_b200 import RandomHingeForest as R
+        self.wl, self.B, self.device, self.torch, self.world = wl, B, device, torch, world
+        torch.manual_seed(0)
+        thr, ord_, w = make_params(wl)
+        if wl["op"] == "conv":
+            module = R.HingeTreeConv2d(wl["C"], wl["T"], wl["depth"], 3, stride=1, padding=1)
+            self.model = module
+        else:
+            module = R.RandomHingeForest(wl["hidden"], wl["T"], wl["depth"], init_type="sequential")
+            self.model = nn.Sequential(nn.Linear(wl["C"], wl["hidden"], bias=False),
+                                       nn.BatchNorm1d(wl["hidden"], affine=False), module)
+        with torch.no_grad():
+            module.thresholds.copy_(thr)
+            module.ordinals.copy_(ord_)
+            module.weights.copy_(w)
+        self.model = self.model.to(device)
+        self.x_host = make_x(wl, B, rank)
+        self.x = self.x_host.to(device).requires_grad_(wl["op"] == "conv")
+        self.bucket = None
+        if world > 1:
+            from hingetreefortorch_b200.distributed import GradientBucket
+            self.bucket = GradientBucket([p for p in self.model.parameters() if p.requires_grad])
+
+    def enable_backward(self):
+        pass
+
+    def _train_step(self, x):
+        for p in self.model.parameters():
+            p.grad = None
+        if x.grad is not None:
+            x.grad = None
+        loss = self.model(x).sum()
+        loss.backward()
+        if self.bucket is not None:
+            self.bucket.all_reduce()
+        return loss
+
+    def step(self, backward):
+        self._train_step(self.x)
+
+    def launches_per_step(self, backward):
+        # this library's kernels only: ordinal pack + forward, ordinal pack + backward (torch's GEMM / BN not counted)
+        return 4
+
+    def check(self):
+        pass
+
+    def prepare_e2e(self):
+        self.x_pinned = self.x_host.pin_memory()
+        self.loss_host = self.torch.empty((), dtype=self.torch.float32).pin_memory()
+        return self.x_host.numel() * 4, 4, "nn.Module forward + loss.backward(), pinned host input, loss read back"
+
+    def e2e_step(self):
+        x = self.x_pinned.to(self.device, non_blocking=True).requires_grad_(self.wl["op"] == "conv")
+        loss = self._train_step(x)
+        self.loss_host.copy_(loss.detach(), non_blocking=True)
+        self.torch.cuda.current_stream(self.device).synchronize()
+
+    def verify_e2e(self):
+        if not self.torch.isfinite(self.loss_host):
+            raise SystemExit("bench.py: end-to-end loss is not finite")
+
 
 def our_arm(a, wl):
     import torch
     import torch.distributed as dist
-    from hingetreefortorch_b200 import _cabi
-    from hingetreefortorch_b200._ext import hingetree_cpp
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU path for the product arm")
+        raise SystemExit("bench.py: no CUDA device; the product arm has no CPU path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
     B = a.rows or wl["B"]
-    thr, ord_, w = [t.to(device) for t in make_params(wl)]
-    x_host = make_x(wl, B, rank)
-    x = x_host.to(device)
-    forest = _cabi.Forest(wl["kind"], x, w)
-    out = torch.empty(forest.out_shape, dtype=torch.float32, device=device)
-    g = gx = gthr = gw = None
+    runner = ForestRunner(wl, B, device, rank) if wl["op"] == "forest" else ModuleRunner(wl, B, device, rank, world)
     if wl["bwd"]:
-        g = torch.randn(forest.out_shape, generator=torch.Generator(device=device).manual_seed(5), device=device)
-        gx, gthr, gw = torch.empty_like(x), torch.empty_like(thr), torch.empty_like(w)
-
-    def step():
-        forest.forward(x, thr, ord_, w, out=out)
-        if wl["bwd"]:
-            forest.backward(x, thr, ord_, w, g, outs=(gx, gthr, gw))
+        runner.enable_backward()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def timed(steps, backward):
+        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        begin.record()
+        for s, e in events:
+            s.record()
+            runner.step(backward)
+            e.record()
+        end.record()
+        barrier()
+        t = torch.tensor([begin.elapsed_time(end)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), [s.elapsed_time(e) for s, e in events]
+
     for _ in range(a.warmup):
-        step()
+        runner.step(wl["bwd"])
     barrier()
-    if forest.ordinal_flags() != 0:
-        raise SystemExit("bench.py: ordinals out of range")
+    runner.check()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    barrier()
-    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(a.steps)]
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    begin.record()
-    for s, e in events:
-        s.record()
-        step()
-        e.record()
-    end.record()
-    barrier()
+    elapsed_ms, per_step_ms = timed(a.steps, wl["bwd"])
     clocks = sampler.stop() if rank == 0 else None
-    elapsed_ms = begin.elapsed_time(end)
-    per_step_ms = [s.elapsed_time(e) for s, e in events]
-    t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(t.item())
-    evals = B * wl["T"]
+    evals = evals_per_step(wl, B)
     value = evals * world * a.steps / (elapsed_ms * 1e-3)
 
     if a.kernel_only:
@@ -295,51 +483,35 @@ def our_arm(a, wl):
             dist.destroy_process_group()
         return
 
-    # ---- end to end through the reference-facing operator, host buffers in and out -----------
-    fwd_op = getattr(hingetree_cpp, wl["kind"] + "_forward")
-    chunk = min(B, 65536)
-    n_chunks = (B + chunk - 1) // chunk
-    x_pinned = x_host.pin_memory()
-    out_pinned = torch.empty(forest.out_shape, dtype=torch.float32).pin_memory()
-    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
-    compute = torch.cuda.current_stream(device)
+    # forward + backward of the inference shape, as a second device-resident figure
+    fwd_bwd = None
+    if wl["op"] == "forest" and not wl["bwd"]:
+        runner.enable_backward()
+        runner.step(True)
+        fb_steps = max(1, min(a.steps, 3))
+        fb_ms, _ = timed(fb_steps, True)
+        fb_bytes = algorithmic_bytes(wl, B, True)
+        fwd_bwd = {"value": evals * world * fb_steps / (fb_ms * 1e-3), "unit": "tree-evals/s",
+                   "ms_per_step": fb_ms / fb_steps, "steps": fb_steps, "bytes_per_step": fb_bytes,
+                   "achieved_gbs": fb_bytes / (fb_ms / fb_steps * 1e-3) / 1e9}
+        runner.g = runner.grads = None
+        torch.cuda.empty_cache()
 
-    def e2e_step():
-        staged = []
-        for c in range(n_chunks):
-            lo, hi = c * chunk, min(B, (c + 1) * chunk)
-            with torch.cuda.stream(copy_in):
-                xc = x_pinned[lo:hi].to(device, non_blocking=True)
-                ready = torch.cuda.Event()
-                ready.record(copy_in)
-            compute.wait_event(ready)
-            oc = fwd_op(xc, thr, ord_, w)
-            xc.record_stream(compute)
-            done = torch.cuda.Event()
-            done.record(compute)
-            copy_out.wait_event(done)
-            with torch.cuda.stream(copy_out):
-                out_pinned[lo:hi].copy_(oc, non_blocking=True)
-                oc.record_stream(copy_out)
-            staged.append(oc)
-        copy_out.synchronize()
-
+    # ---- end to end through the reference-facing surface, host buffers in and out -------------
+    h2d, d2h, call = runner.prepare_e2e()
     e2e_steps = max(1, min(a.steps, 5))
     for _ in range(2):
-        e2e_step()
+        runner.e2e_step()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        e2e_step()
+        runner.e2e_step()
     torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    t = torch.tensor([e2e_s], dtype=torch.float64, device=device)
+    t = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = evals * world * e2e_steps / float(t.item())
-    # the end-to-end output must be the resident-path output
-    if not torch.equal(out_pinned[:1024], out[:1024].cpu()):
-        raise SystemExit("bench.py: end-to-end output differs from the device-resident output")
+    runner.verify_e2e()
 
     if rank == 0:
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -348,31 +520,36 @@ def our_arm(a, wl):
         else:
             peak, peak_src = 6650.0, "fallback"
         launch_ms = statistics.mean(per_step_ms)
-        bytes_per_launch = algorithmic_bytes(wl, B, wl["bwd"])
-        achieved = bytes_per_launch / (launch_ms * 1e-3) / 1e9
+        bytes_per_step = algorithmic_bytes(wl, B, wl["bwd"])
+        achieved = bytes_per_step / (launch_ms * 1e-3) / 1e9
+        if fwd_bwd is not None:
+            fwd_bwd["frac"] = fwd_bwd["achieved_gbs"] / peak
         cores = os.cpu_count() or 1
-        sample_rows = min(B, max(cores * 8, int(15.0 * cores / (wl["T"] * 80e-9))))
+        sample_rows = cpu_sample_rows(wl, cores)
         cpu_value, cpu_dt = cpu_port_rate(wl, sample_rows, cores)
-        elem = 4 * (wl["M"] or 1)
         line = {
             "metric": "tree-evals/sec " + ("fwd+bwd" if wl["bwd"] else "fwd"),
             "value": value, "unit": "tree-evals/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": elapsed_ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl["name"] + ("" if B == wl["B"] else " (rows overridden)"), "rows_per_gpu": B, "l2": "inputs and outputs exceed L2 (126 MB)"
-                       if bytes_per_launch > 4 * 126e6 else "working set fits L2",
-                       "parallelism": "batch-sharded x%d, replicated parameters" % world},
+            "config": {"workload": wl["name"] + ("" if B == wl["B"] else " (rows overridden)"), "rows_per_gpu": B,
+                       "l2": "inputs and outputs exceed L2 (126 MB)" if bytes_per_step > 4 * 126e6
+                       else "working set fits L2; launch-latency regime",
+                       "parallelism": "batch-sharded x%d, replicated parameters%s"
+                       % (world, ", one NCCL all-reduce of parameter gradients per step"
+                          if world > 1 and wl["op"] != "forest" else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "bytes_per_launch": bytes_per_launch,
+                         "traffic": None, "peak_source": peak_src, "bytes_per_launch": bytes_per_step,
                          "launch_ms": launch_ms, "frac_of_8TBs": achieved / 8000.0},
             "cpu_baseline": {"value": cpu_value, "unit": "tree-evals/s", "cores": cores, "kind": "port",
-                             "sample": "%d of %d rows, all %d trees, %.1f s" % (sample_rows, B, wl["T"], cpu_dt)},
-            "e2e": {"value": e2e_value, "unit": "tree-evals/s", "h2d_bytes_per_step": 4 * B * wl["C"],
-                    "d2h_bytes_per_step": elem * B * wl["T"], "steps": e2e_steps,
-                    "call": "hingetree_cpp.%s_forward on %d-row chunks, pinned host buffers, 3 streams" % (wl["kind"], chunk)},
-            "gpu_launches": a.steps * (2 + (2 if wl["bwd"] else 0)),
+                             "sample": "forward of %d of %d rows, %.1f s" % (sample_rows, wl["B"], cpu_dt)},
+            "e2e": {"value": e2e_value, "unit": "tree-evals/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "call": call},
+            "gpu_launches": a.steps * runner.launches_per_step(wl["bwd"]),
             "clocks": clocks,
         }
+        if fwd_bwd is not None:
+            line["fwd_bwd"] = fwd_bwd
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -389,7 +566,8 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="time the device-resident step only (profiler captures): no end-to-end and no CPU leg")
     a = ap.parse_args()
-    a.warmup = max(a.warmup, 3) if a.impl == "ours" else a.warmup
+    if a.impl == "ours":
+        a.warmup = max(a.warmup, 3)
     wl = WORKLOADS[a.workload]
     if a.impl == "reference":
         reference_arm(a, wl)
