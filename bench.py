@@ -48,6 +48,13 @@ WORKLOADS = {
 }
 
 
+# DRAM bytes (read + write) of the tile kernel per input row of the c3 shape, from the committed
+# capture profiles/forest_forward_tiled_65536rows_ncu.md: (38 281 728 + 216 945 920) B / 65 536 rows.
+# Traffic grows in proportion to the rows (every CTA handles 256 rows the same way), so the
+# full-size launch is that figure times its rows.
+C3_DRAM_BYTES_PER_ROW = (38281728 + 216945920) / 65536
+
+
 def decisions(kind, depth):
     return depth if kind == "fern" else 2 ** depth - 1
 
@@ -539,7 +546,8 @@ def our_arm(a, wl):
                        % (world, ", one NCCL all-reduce of parameter gradients per step"
                           if world > 1 and wl["op"] != "forest" else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "bytes_per_launch": bytes_per_step,
+                         "traffic": C3_DRAM_BYTES_PER_ROW * B if a.workload == "c3" else None,
+                         "peak_source": peak_src, "bytes_per_launch": bytes_per_step,
                          "launch_ms": launch_ms, "frac_of_8TBs": achieved / 8000.0},
             "cpu_baseline": {"value": cpu_value, "unit": "tree-evals/s", "cores": cores, "kind": "port",
                              "sample": "forward of %d of %d rows, %.1f s" % (sample_rows, wl["B"], cpu_dt)},

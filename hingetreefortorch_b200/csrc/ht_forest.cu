@@ -395,6 +395,9 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
   if (pr.evals * a.M == 0 || (gx == nullptr && gthr == nullptr && gw == nullptr)) return HT_OK;
 
   if ((p->flags & HT_DETERMINISTIC) == 0) {
+    const int trc = backward_tiled(p, x, thr, a.ord, w, g, gx, gthr, gw,
+                                   static_cast<unsigned char *>(workspace) + ordinals_bytes(p), status_word, pr.stream);
+    if (trc != HT_ERR_UNSUPPORTED) return trc;
     const unsigned grid = blocks_for(pr.evals, kBlock);
     if (p->kind == TREE)
       forest_backward_atomic_kernel<TREE><<<grid, kBlock, 0, pr.stream>>>(a, g, gx, gthr, gw);

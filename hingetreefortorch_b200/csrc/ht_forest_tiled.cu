@@ -29,33 +29,14 @@
 // go left, as `margin > 0` does in the reference).  |threshold - feature| equals
 // |feature - threshold| bit for bit.
 #include "ht_forest_tiled.cuh"
+#include "ht_tile_common.cuh"
 
 namespace ht {
 
+using namespace tile;
+
 namespace {
 
-constexpr int kThreads = 1024;
-constexpr int kWarps = kThreads / 32;
-constexpr size_t kSmemBudget = 227 * 1024;
-constexpr int kHeadBytes = 16;  // tree records start with {thr(1), thr(2), thr(3), packed ordinals}
-// Spin limit for the parameter pipeline: far beyond any real copy latency, small enough that a
-// lost copy ends the kernel (with a flag) instead of hanging the device.
-constexpr uint32_t kMaxSpins = 1u << 22;
-
-__host__ __device__ constexpr uint32_t round16(uint32_t v) { return (v + 15u) & ~15u; }
-
-// Byte layout of one tree record; the same arithmetic runs on the host (plan) and in the kernel.
-struct RecordLayout {
-  uint32_t thr, ord, w, bytes;
-};
-
-__host__ __device__ constexpr RecordLayout record_layout(int kind, int depth, uint32_t ord_size) {
-  const uint32_t n = kind == FERN ? (uint32_t)depth : (1u << depth) - 1u;
-  const uint32_t thr = kind == FERN ? 0u : (uint32_t)kHeadBytes;
-  const uint32_t ord = thr + round16(4u * n);
-  const uint32_t w = ord + round16(ord_size * n);
-  return RecordLayout{thr, ord, w, round16(w + 4u * (1u << depth))};
-}
 
 struct TilePlan {
   int S;           // samples per tile
@@ -84,103 +65,6 @@ bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
     }
   }
   return false;
-}
-
-__device__ __forceinline__ uint32_t bit_reverse(uint32_t v, int bits) { return __brev(v) >> (32 - bits); }
-
-// One thread per record element.  Leaf weights are permuted so that the path bits in the order
-// the traversal collects them (root first, most significant) address them directly.
-template <typename OrdT>
-__global__ void repack_records_kernel(const float *__restrict__ thr, const int32_t *__restrict__ ord,
-                                      const float *__restrict__ w, unsigned char *__restrict__ records, int kind,
-                                      int depth, int64_t T, RecordLayout lay) {
-  const int64_t N = threshold_count(kind, depth);
-  const int64_t L = ((int64_t)1) << depth;
-  const int64_t per_tree = N + L;
-  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= T * per_tree) return;
-  const int64_t j = e / per_tree;
-  const int64_t r = e - j * per_tree;
-  unsigned char *rec = records + j * lay.bytes;
-  if (r < N) {
-    float t = thr[j * N + r];
-    t = t == 0.0f ? 0.0f : t;  // -0 becomes +0
-    const uint32_t c = (uint32_t)ord[j * N + r];
-    reinterpret_cast<float *>(rec + lay.thr)[r] = t;
-    reinterpret_cast<OrdT *>(rec + lay.ord)[r] = (OrdT)c;
-    if (kind == TREE && r < 3) {  // root and its children again, for one broadcast load
-      reinterpret_cast<float *>(rec)[r] = t;
-      if (sizeof(OrdT) == 1) rec[12 + r] = (unsigned char)c;
-    }
-    if (kind == TREE && r == 0 && N < 3) {  // depth 1: no children; keep the head defined
-      reinterpret_cast<float *>(rec)[1] = 0.0f;
-      reinterpret_cast<float *>(rec)[2] = 0.0f;
-      rec[13] = rec[14] = 0;
-    }
-    if (kind == TREE && r == 0) rec[15] = 0;
-  } else {
-    const int64_t h = r - N;
-    reinterpret_cast<float *>(rec + lay.w)[h] = w[j * L + (int64_t)bit_reverse((uint32_t)h, depth)];
-  }
-}
-
-__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-
-// 1-D bulk copy global -> shared through the TMA engine; completion is counted in bytes on `bar`.
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint64_t *bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(smem_addr(bar))
-               : "memory");
-}
-
-// Bounded wait on a phase of the barrier.  Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kMaxSpins; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(smem_addr(bar)), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-
-__device__ __forceinline__ void named_barrier(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-__device__ __forceinline__ float lds_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
-  return v;
-}
-
-__device__ __forceinline__ uint4 lds_b128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-
-template <typename OrdT>
-__device__ __forceinline__ uint32_t lds_ord(uint32_t addr) {
-  uint32_t v;
-  if (sizeof(OrdT) == 1)
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
-  else
-    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
 }
 
 struct TiledArgs {

@@ -15,4 +15,10 @@ size_t forward_tiled_workspace_bytes(const ht_forest_problem *p);
 int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
                   float *out, void *records, uint32_t *status_word, cudaStream_t stream);
 
+// Backward (default mode) with the tile kernel of ht_forest_tiled_bwd.cu; same contract as
+// forward_tiled.  Any of gx / gthr / gw may be null; gthr and gw must have been cleared.
+int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
+                   const float *g, float *gx, float *gthr, float *gw, void *records, uint32_t *status_word,
+                   cudaStream_t stream);
+
 }  // namespace ht

@@ -211,3 +211,25 @@ def test_tile_kernel_shapes_with_special_values(cabi, kind, shape):
     assert np.array_equal(got, want, equal_nan=True)
     assert np.array_equal(f.leafmap(dx, dthr, dord).cpu().numpy(), ho.maps(kind, x, thr, ord_, w)[0])
     assert f.ordinal_flags() == 0
+
+
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+@pytest.mark.parametrize("shape", TILED_SHAPES, ids=[str(s) for s in TILED_SHAPES])
+def test_tile_kernel_backward(cabi, kind, shape):
+    """Default-mode backward on shapes the backward tile kernel takes (and on the wide ones it leaves to
+    the any-shape kernel): within 1e-5 of the summed term magnitudes, with exact ties and zero margins."""
+    B, C, T, depth = shape
+    x, thr, ord_, w = random_forest_inputs(70 + TILED_SHAPES.index(shape), kind, B, C, (), T, depth, (), quantise=True)
+    g = np.random.default_rng(4).standard_normal((B, T)).astype(np.float32)
+    dx, dthr, dord, dw, dg = dev(x, thr, ord_, w, g)
+    f = cabi.Forest(kind, dx, dw)
+    gx, gthr, gw = f.backward(dx, dthr, dord, dw, dg)
+    rx, rthr, rw = ho.backward(kind, x, thr, ord_, w, g)
+    ax, athr, aw = ho.backward_magnitudes(kind, x, thr, ord_, w, g)
+    assert grad_close(gx, rx, ax) and grad_close(gthr, rthr, athr) and grad_close(gw, rw, aw)
+    assert f.ordinal_flags() == 0
+    # only some gradients requested
+    only_w = f.backward(dx, dthr, dord, dw, dg, need=(False, False, True))
+    assert only_w[0] is None and only_w[1] is None and grad_close(only_w[2], rw, aw)
+    only_x = f.backward(dx, dthr, dord, dw, dg, need=(True, False, False))
+    assert grad_close(only_x[0], rx, ax)
