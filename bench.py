@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the hinge forest evaluation path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c2|c1|c4|c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c3b|c2|c1|c4|c5]
 
 A step is one pass of the hot path over one batch of seeded synthetic input.  The default
 workload (c3) is the large-batch forest inference configuration: x [1048576,128] ~ N(0,1), 1024
@@ -37,6 +37,8 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     "c3": dict(op="forest", kind="tree", B=1048576, C=128, T=1024, depth=8, M=0, x="randn", bwd=False,
                name="C3 large-batch forest inference x[1048576,128] T=1024 depth=8"),
+    "c3b": dict(op="forest", kind="tree", B=1048576, C=128, T=1024, depth=8, M=0, x="randn", bwd=True,
+                name="C3 shape, forward + backward x[1048576,128] T=1024 depth=8"),
     "c2": dict(op="forest", kind="fern", B=4096, C=256, T=500, depth=10, M=10, x="randn", bwd=True,
                name="C2 fern fwd+bwd x[4096,256] T=500 depth=10 extra_outputs=10"),
     "c1": dict(op="forest", kind="tree", B=100, C=1000, T=100, depth=7, M=1, x="rand", bwd=True,

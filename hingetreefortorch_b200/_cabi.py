@@ -12,6 +12,7 @@ from . import _build
 
 HT_KIND = {"tree": 0, "fern": 1}
 HT_DETERMINISTIC = 1
+HT_WORKSPACE_FOR_BACKWARD = 2
 HT_FLAG_ORDINAL_RANGE = 1
 
 # every symbol include/hingetree_b200.h declares (checked by the CPU test-suite)
@@ -163,10 +164,11 @@ def forest_problem(kind, x, w, deterministic=False):
 class Forest:
     """Scratch memory and status word for repeated calls on one problem shape."""
 
-    def __init__(self, kind, x, w, deterministic=False):
+    def __init__(self, kind, x, w, deterministic=False, backward_workspace=True):
         import torch
         self.kind = kind
         self.problem = forest_problem(kind, x, w, deterministic)
+        self.problem.flags |= HT_WORKSPACE_FOR_BACKWARD if backward_workspace else 0
         nbytes = library().ht_forest_workspace_bytes(ctypes.byref(self.problem))
         self.workspace = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=x.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=x.device)

@@ -231,6 +231,7 @@ std::vector<torch::Tensor> forest_backward(int kind, bool deterministic, torch::
   std::vector<torch::Tensor> grads(4);
   if (!need_x && !need_thr && !need_w) return grads;
   if (deterministic) call.problem.flags |= HT_DETERMINISTIC;
+  call.problem.flags |= HT_WORKSPACE_FOR_BACKWARD;
   if (need_x) grads[0] = torch::empty_like(x);
   if (need_thr) grads[1] = torch::empty_like(thr);
   if (need_w) grads[3] = torch::empty_like(w);

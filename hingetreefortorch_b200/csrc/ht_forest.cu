@@ -329,7 +329,8 @@ const char *ht_status_string(int status) {
 
 size_t ht_forest_workspace_bytes(const ht_forest_problem *p) {
   if (check_forest_problem(p) != HT_OK) return 0;
-  return ordinals_bytes(p) + forward_tiled_workspace_bytes(p) + 256;
+  const size_t base = ordinals_bytes(p) + forward_tiled_workspace_bytes(p) + 256;
+  return (p->flags & HT_WORKSPACE_FOR_BACKWARD) != 0 ? base + backward_records_bytes(p) : base;
 }
 
 int ht_forest_forward_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
@@ -394,10 +395,18 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
     HT_CUDA_TRY(cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)(a.T * a.L * a.M), pr.stream));
   if (pr.evals * a.M == 0 || (gx == nullptr && gthr == nullptr && gw == nullptr)) return HT_OK;
 
-  if ((p->flags & HT_DETERMINISTIC) == 0) {
-    const int trc = backward_tiled(p, x, thr, a.ord, w, g, gx, gthr, gw,
-                                   static_cast<unsigned char *>(workspace) + ordinals_bytes(p), status_word, pr.stream);
+  {
+    // Tile kernels when the shape qualifies; with room for the evaluation records in the workspace
+    // they serve both modes (that path is fixed-order), without it only the default mode.
+    unsigned char *ws = static_cast<unsigned char *>(workspace);
+    const size_t records_at = ordinals_bytes(p) + forward_tiled_workspace_bytes(p);
+    const size_t eval_bytes = backward_records_bytes(p);
+    void *eval_records = eval_bytes > 0 && workspace_bytes >= records_at + eval_bytes ? ws + records_at : nullptr;
+    const int trc = backward_tiled(p, x, thr, a.ord, w, g, gx, gthr, gw, ws + ordinals_bytes(p), eval_records,
+                                   status_word, pr.stream);
     if (trc != HT_ERR_UNSUPPORTED) return trc;
+  }
+  if ((p->flags & HT_DETERMINISTIC) == 0) {
     const unsigned grid = blocks_for(pr.evals, kBlock);
     if (p->kind == TREE)
       forest_backward_atomic_kernel<TREE><<<grid, kBlock, 0, pr.stream>>>(a, g, gx, gthr, gw);

@@ -15,10 +15,15 @@ size_t forward_tiled_workspace_bytes(const ht_forest_problem *p);
 int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
                   float *out, void *records, uint32_t *status_word, cudaStream_t stream);
 
-// Backward (default mode) with the tile kernel of ht_forest_tiled_bwd.cu; same contract as
-// forward_tiled.  Any of gx / gthr / gw may be null; gthr and gw must have been cleared.
+// Backward with the tile kernels of ht_forest_tiled_bwd.cu; same contract as forward_tiled.  With
+// `eval_records` (backward_records_bytes() bytes of 256-byte aligned scratch; 0 = shape not
+// supported) the traversal kernel writes per-evaluation records and two reduction kernels add
+// them in the reference's order: deterministic, and the only tile path taken in HT_DETERMINISTIC
+// mode.  Without it the traversal kernel scatters with global reductions (default mode only).
+// Any of gx / gthr / gw may be null; the others must have been cleared.
+size_t backward_records_bytes(const ht_forest_problem *p);
 int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
-                   const float *g, float *gx, float *gthr, float *gw, void *records, uint32_t *status_word,
-                   cudaStream_t stream);
+                   const float *g, float *gx, float *gthr, float *gw, void *records, void *eval_records,
+                   uint32_t *status_word, cudaStream_t stream);
 
 }  // namespace ht

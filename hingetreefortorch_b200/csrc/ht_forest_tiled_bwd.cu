@@ -3,15 +3,12 @@
 //
 // Same tiling as the forward tile kernel (ht_forest_tiled.cu): a CTA owns S consecutive samples,
 // keeps their features feature-major in shared memory and walks ALL trees, whose parameter
-// records stream in through bulk async copies.  In addition:
-//   * the x-gradient tile gx[c][s] lives in shared memory next to the features; contributions are
-//     added with shared-memory atomics (the warps of a sample group work on different trees and
-//     may hit the same element) and the tile leaves once, with plain stores -- no global atomics
-//     and no clearing pass for the x gradient;
-//   * the block of upstream gradients g[i, j0 .. j0+G) of a tree group is loaded as row segments
-//     and transposed through the per-sample-group staging area;
-//   * threshold and leaf-weight gradients are scattered with global reductions (red.global.add),
-//     one per evaluation each.
+// records stream in through bulk async copies; a warp walks 4 consecutive trees at once for its
+// 32 samples.  Each lane fetches the 4 upstream gradients g[i, j .. j+3] of its sample with one
+// 16-byte load issued before the walk, and scatters the three gradients with fire-and-forget
+// global reductions (red.global.add.f32): the rows of the x gradient are private to the CTA, the
+// threshold and leaf-weight bins are shared by all CTAs.  There is no block-wide barrier after
+// the feature tile has been staged.
 // One traversal serves all three gradients (the reference runs three kernels that each repeat it,
 // hingetree_gpu.cu:699-727).  The traversal keeps the signed margin and the deciding vertex, with
 // the reference's strict `<` so that the shallowest minimum wins.
@@ -43,11 +40,33 @@ bool make_bwd_plan(const ht_forest_problem *p, BwdPlan &plan) {
       plan.S = S;
       plan.G = G;
       plan.per_warp = per_warp;
-      plan.smem = 2 * (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + (size_t)S * (G + 1) * 4 + 64;
+      plan.smem = (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + 64;
       if (plan.smem <= kSmemBudget) return true;
     }
   }
   return false;
+}
+
+// Per-evaluation results of the traversal kernel, laid out [sample block of 256][tree][256] so that
+// the x-gradient reduction streams each sample block's records sequentially and the parameter
+// reduction reads 1 KB runs: `dx` is the term sign * w * g (the x-gradient term; the threshold term is -dx),
+// `dw` is |margin| * g (the leaf-weight term), `where` packs the deciding vertex (1-based, low 16
+// bits) and the reference leaf key (high 16 bits).
+struct EvalRecords {
+  float *dx;
+  float *dw;
+  uint32_t *where;
+};
+
+constexpr int kRecordBlock = 256;
+
+__host__ __device__ inline int64_t record_index(int64_t sample, int64_t tree, int64_t trees) {
+  return ((sample / kRecordBlock) * trees + tree) * kRecordBlock + (sample % kRecordBlock);
+}
+
+inline size_t record_array_bytes(const ht_forest_problem *p) {
+  const int64_t blocks = (p->B + kRecordBlock - 1) / kRecordBlock;
+  return align_up((size_t)(blocks * kRecordBlock * p->T) * 4, 256);
 }
 
 struct BwdArgs {
@@ -55,6 +74,7 @@ struct BwdArgs {
   const unsigned char *records;
   const float *g;
   float *gx, *gthr, *gw;
+  EvalRecords evals;
   uint32_t *status_word;
   int64_t B, T;
   int C, S, G, per_warp;
@@ -92,7 +112,7 @@ __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], uint32_t xl
   for (int u = 0; u < NT; ++u) out[u].path = v[u];
 }
 
-template <int KIND, int DEPTH, typename OrdT>
+template <int KIND, int DEPTH, typename OrdT, bool RECORDS>
 __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
@@ -100,10 +120,8 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
   constexpr uint32_t kL = 1u << DEPTH;
   const int S = a.S, G = a.G, C = a.C;
   float *xs = reinterpret_cast<float *>(smem);
-  float *gxs = xs + (size_t)C * S;
-  unsigned char *params = reinterpret_cast<unsigned char *>(gxs + (size_t)C * S);
-  float *stage_all = reinterpret_cast<float *>(params + 2 * (size_t)G * lay.bytes);
-  uint64_t *full = reinterpret_cast<uint64_t *>(stage_all + (size_t)S * (G + 1));
+  unsigned char *params = reinterpret_cast<unsigned char *>(xs + (size_t)C * S);
+  uint64_t *full = reinterpret_cast<uint64_t *>(params + 2 * (size_t)G * lay.bytes);
   uint32_t *finished = reinterpret_cast<uint32_t *>(full + 2);
 
   const int tid = threadIdx.x;
@@ -136,7 +154,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
     if (num_groups > 1) issue(1);
   }
 
-  // features in, x-gradient tile cleared
+  // features in
   if ((C & 3) == 0) {
     const int quads = C >> 2;
     for (int idx = tid; idx < S * quads; idx += kThreads) {
@@ -154,68 +172,68 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
       xs[c * S + s] = (row0 + s < a.B) ? __ldg(a.x + (row0 + s) * C + c) : 0.f;
     }
   }
-  for (int idx = tid; idx < S * C; idx += kThreads) gxs[idx] = 0.0f;
   __syncthreads();
 
   const int my_sample = sample_group * 32 + lane;
   const bool row_valid = row0 + my_sample < a.B;
   const uint32_t xl_addr = smem_addr(xs + my_sample);
   const uint32_t x_stride = (uint32_t)S * 4u;
-  float *stage = stage_all + (size_t)sample_group * 32 * (G + 1);
-  const int group_threads = slots * 32;
-  const int tid_in_group = slot * 32 + lane;
-  const int64_t row_base = row0 + sample_group * 32;
+  const int64_t my_row = row0 + my_sample;
   bool poisoned = false;
 
   for (int group = 0; group < num_groups; ++group) {
     const int in_group = (int)min((int64_t)G, a.T - (int64_t)group * G);
     const int64_t col0 = (int64_t)group * G;
 
-    // upstream gradients of this sample group for the tree group: row segments -> staging rows
-    named_barrier(1 + sample_group, group_threads);  // the previous group's values have been consumed
-    if ((a.T & 3) == 0 && (in_group & 3) == 0) {
-      const int quads = in_group >> 2;
-      for (int idx = tid_in_group; idx < 32 * quads; idx += group_threads) {
-        const int s = idx / quads, q = idx - s * quads;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (row_base + s < a.B) v = __ldg(reinterpret_cast<const float4 *>(a.g + (row_base + s) * a.T + col0 + 4 * q));
-        float *dst = stage + s * (G + 1) + 4 * q;
-        dst[0] = v.x;
-        dst[1] = v.y;
-        dst[2] = v.z;
-        dst[3] = v.w;
-      }
-    } else {
-      for (int idx = tid_in_group; idx < 32 * in_group; idx += group_threads) {
-        const int s = idx / in_group, t = idx - s * in_group;
-        stage[s * (G + 1) + t] = (row_base + s < a.B) ? __ldg(a.g + (row_base + s) * a.T + col0 + t) : 0.f;
+    // upstream gradients of this lane's sample for the warp's trees, requested before the walk
+    const int t_first = slot * per_warp;
+    float gval[4] = {0.f, 0.f, 0.f, 0.f};
+    if (row_valid && t_first < in_group) {
+      const float *gp = a.g + my_row * a.T + col0 + t_first;
+      if (per_warp == 4 && (a.T & 3) == 0 && t_first + 3 < in_group) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(gp));
+        gval[0] = v.x;
+        gval[1] = v.y;
+        gval[2] = v.z;
+        gval[3] = v.w;
+      } else {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (u < per_warp && t_first + u < in_group) gval[u] = __ldg(gp + u);
       }
     }
-    named_barrier(1 + sample_group, group_threads);  // staged
 
     if (!poisoned && !mbar_wait(&full[group & 1], (uint32_t)((group >> 1) & 1))) {
       poisoned = true;
       if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
     }
     const uint32_t base_addr = params_addr + (uint32_t)(group & 1) * (uint32_t)G * lay.bytes;
-    const int t_first = slot * per_warp;
     if (t_first < in_group && !poisoned) {
-      auto scatter = [&](const Walked &wk, uint32_t rec, int t) {
+      auto scatter = [&](const Walked &wk, uint32_t rec, int u) {
+        const int t = t_first + u;
         if (t >= in_group || !row_valid) return;
         const int64_t j = col0 + t;
-        const float gval = stage[lane * (G + 1) + t];
+        const float gv = gval[u];
         const float wv = lds_f32(rec + 4u * wk.path + (lay.w - 4u * kL));
         // sign(margin) * w * g with margin = -nm
-        const float wg = __fmul_rn(wv, gval);
+        const float wg = __fmul_rn(wv, gv);
         const float dx = wk.nm < 0.0f ? wg : (wk.nm > 0.0f ? -wg : __fmul_rn(0.0f, wg));
+        if (RECORDS) {
+          const uint32_t key = __brev(wk.path - kL) >> (32 - DEPTH);
+          const int64_t at = record_index(my_row, j, a.T);
+          a.evals.dx[at] = dx;
+          a.evals.dw[at] = __fmul_rn(fabsf(wk.nm), gv);
+          a.evals.where[at] = wk.v | (key << 16);
+          return;
+        }
         if (a.gx != nullptr) {
           const uint32_t c = lds_ord<OrdT>(rec + (uint32_t)sizeof(OrdT) * wk.v + (lay.ord - (uint32_t)sizeof(OrdT)));
-          atomicAdd(gxs + c * S + my_sample, dx);
+          atomicAdd(a.gx + my_row * C + c, dx);
         }
         if (a.gthr != nullptr) atomicAdd(a.gthr + j * kN + (wk.v - 1u), -dx);
         if (a.gw != nullptr) {
           const uint32_t key = __brev(wk.path - kL) >> (32 - DEPTH);  // reference leaf key: bit l = decision at depth l
-          atomicAdd(a.gw + j * kL + key, __fmul_rn(fabsf(wk.nm), gval));
+          atomicAdd(a.gw + j * kL + key, __fmul_rn(fabsf(wk.nm), gv));
         }
       };
       if (per_warp == 4) {
@@ -225,7 +243,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
         Walked wk[4];
         walk_full<KIND, DEPTH, OrdT, 4>(rec, xl_addr, x_stride, wk);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) scatter(wk[u], rec[u], t_first + u);
+        for (int u = 0; u < 4; ++u) scatter(wk[u], rec[u], u);
       } else if (per_warp == 2) {
         uint32_t rec[2];
 #pragma unroll
@@ -233,12 +251,12 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
         Walked wk[2];
         walk_full<KIND, DEPTH, OrdT, 2>(rec, xl_addr, x_stride, wk);
 #pragma unroll
-        for (int u = 0; u < 2; ++u) scatter(wk[u], rec[u], t_first + u);
+        for (int u = 0; u < 2; ++u) scatter(wk[u], rec[u], u);
       } else {
         uint32_t rec[1] = {base_addr + (uint32_t)t_first * lay.bytes};
         Walked wk[1];
         walk_full<KIND, DEPTH, OrdT, 1>(rec, xl_addr, x_stride, wk);
-        scatter(wk[0], rec[0], t_first);
+        scatter(wk[0], rec[0], 0);
       }
     }
     __syncwarp();
@@ -253,40 +271,174 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
     }
   }
 
-  // the x-gradient tile leaves with plain stores: every element of these rows is written exactly once
-  __syncthreads();
-  if (a.gx != nullptr) {
-    if ((C & 3) == 0) {
-      const int quads = C >> 2;
-      for (int idx = tid; idx < S * quads; idx += kThreads) {
-        const int s = idx % S, q = idx / S;
-        if (row0 + s < a.B)
-          *(reinterpret_cast<float4 *>(a.gx + (row0 + s) * C) + q) =
-              make_float4(gxs[(4 * q + 0) * S + s], gxs[(4 * q + 1) * S + s], gxs[(4 * q + 2) * S + s],
-                          gxs[(4 * q + 3) * S + s]);
-      }
-    } else {
-      for (int idx = tid; idx < S * C; idx += kThreads) {
-        const int s = idx % S, c = idx / S;
-        if (row0 + s < a.B) a.gx[(row0 + s) * C + c] = gxs[c * S + s];
-      }
-    }
-  }
+}
+
+template <typename Kernel>
+int launch_one(Kernel kernel, const BwdPlan &plan, const BwdArgs &a, unsigned grid, cudaStream_t stream) {
+  HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+  kernel<<<grid, kThreads, plan.smem, stream>>>(a);
+  HT_CHECK_LAUNCH();
+  return HT_OK;
 }
 
 template <int KIND, int DEPTH>
 int launch_depth(const BwdPlan &plan, const BwdArgs &a, unsigned grid, cudaStream_t stream) {
-  if (plan.ord_bytes == 1) {
-    auto kernel = forest_backward_tiled_kernel<KIND, DEPTH, uint8_t>;
-    HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-    kernel<<<grid, kThreads, plan.smem, stream>>>(a);
-  } else {
-    auto kernel = forest_backward_tiled_kernel<KIND, DEPTH, uint16_t>;
-    HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-    kernel<<<grid, kThreads, plan.smem, stream>>>(a);
+  const bool records = a.evals.dx != nullptr;
+  if (plan.ord_bytes == 1)
+    return records ? launch_one(forest_backward_tiled_kernel<KIND, DEPTH, uint8_t, true>, plan, a, grid, stream)
+                   : launch_one(forest_backward_tiled_kernel<KIND, DEPTH, uint8_t, false>, plan, a, grid, stream);
+  return records ? launch_one(forest_backward_tiled_kernel<KIND, DEPTH, uint16_t, true>, plan, a, grid, stream)
+                 : launch_one(forest_backward_tiled_kernel<KIND, DEPTH, uint16_t, false>, plan, a, grid, stream);
+}
+
+// ---- consumers of the evaluation records -----------------------------------------------------------
+//
+// Both consumers add the terms of every gradient element in exactly the order of the reference
+// CPU loops (samples ascending for the parameter bins, trees ascending for the x gradient), so
+// the record path is deterministic and, with one output per leaf, equal to those loops bit for bit.
+
+// Runs f() on the valid lanes so that lanes sharing `key` execute in lane order.
+template <typename F>
+__device__ __forceinline__ void lanes_in_order_per_key(bool valid, uint32_t key, F &&f) {
+  const unsigned lane = threadIdx.x & 31u;
+  const uint32_t tag = valid ? key : (0x80000000u | lane);
+  const unsigned peers = __match_any_sync(0xffffffffu, tag);
+  const int rank = __popc(peers & ((1u << lane) - 1u));
+  const int last = __reduce_max_sync(0xffffffffu, valid ? rank : 0);
+  for (int r = 0; r <= last; ++r) {
+    if (valid && rank == r) f();
+    __syncwarp();
   }
-  HT_CHECK_LAUNCH();
-  return HT_OK;
+}
+
+// Threshold and leaf-weight gradients: one CTA per tree.  Each of its warps walks a share of the
+// tree's records in sample order, 32 at a time (4 chunks prefetched), into its own bins in shared
+// memory (lanes that meet in a bin add in lane order); the warps' bins are then summed in warp
+// order.  With one warp (fixed-order mode) that is exactly the reference's sequential sum over
+// the samples; with several (default mode) it is a reproducible sum with another association.
+__global__ void __launch_bounds__(512) reduce_parameter_records_kernel(EvalRecords r, int64_t B, int64_t T, int64_t N,
+                                                                       int64_t L, float *gthr, float *gw) {
+  extern __shared__ float all_bins[];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5;
+  float *bins = all_bins + (size_t)warp * (N + L);
+  float *thr_bins = bins, *w_bins = bins + N;
+  const int64_t j = blockIdx.x;
+  const unsigned lane = threadIdx.x & 31u;
+  for (int64_t t = lane; t < N + L; t += 32) bins[t] = 0.0f;
+  __syncwarp();
+  // A batch is kAhead chunks of 32 consecutive samples (all inside one 256-sample record block);
+  // the next batch is requested before the current one is consumed.
+  constexpr int kAhead = 4;
+  const int64_t stride = (int64_t)warps * 32 * kAhead;
+  float a[kAhead], b[kAhead], na[kAhead], nb[kAhead];
+  uint32_t wh[kAhead], nwh[kAhead];
+  auto fetch = [&](int64_t i0, float (&fa)[kAhead], float (&fb)[kAhead], uint32_t (&fw)[kAhead]) {
+    const int64_t first = record_index(i0, j, T) + lane;  // i0 is a multiple of 128
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const bool valid = i0 + 32 * u + lane < B;
+      fa[u] = valid ? __ldcs(r.dx + first + 32 * u) : 0.0f;
+      fb[u] = valid ? __ldcs(r.dw + first + 32 * u) : 0.0f;
+      fw[u] = valid ? __ldcs(r.where + first + 32 * u) : 1u;
+    }
+  };
+  int64_t i0 = (int64_t)warp * 32 * kAhead;
+  if (i0 < B) fetch(i0, a, b, wh);
+  for (; i0 < B; i0 += stride) {
+    if (i0 + stride < B) fetch(i0 + stride, na, nb, nwh);
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const bool valid = i0 + 32 * u + lane < B;
+      const uint32_t v = (wh[u] & 0xffffu) - 1u, key = wh[u] >> 16;
+      if (gthr != nullptr)
+        lanes_in_order_per_key(valid, v, [&]() { thr_bins[v] = __fadd_rn(thr_bins[v], -a[u]); });
+      if (gw != nullptr)
+        lanes_in_order_per_key(valid, key, [&]() { w_bins[key] = __fadd_rn(w_bins[key], b[u]); });
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      a[u] = na[u];
+      b[u] = nb[u];
+      wh[u] = nwh[u];
+    }
+  }
+  __syncthreads();
+  for (int64_t t = threadIdx.x; t < N + L; t += blockDim.x) {
+    float sum = all_bins[t];
+    for (int wi = 1; wi < warps; ++wi) sum = __fadd_rn(sum, all_bins[(size_t)wi * (N + L) + t]);
+    if (t < N) {
+      if (gthr != nullptr) gthr[j * N + t] = sum;
+    } else if (gw != nullptr) {
+      gw[j * L + (t - N)] = sum;
+    }
+  }
+}
+
+// x gradient: one thread per sample walks the trees in ascending order and adds into its private
+// column of a shared-memory tile gx[c][s]; the tile leaves with plain stores.
+__global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, const int32_t *__restrict__ ord, int64_t B,
+                                                               int64_t T, int64_t N, int C, int S, float *gx) {
+  extern __shared__ float tile[];
+  const int s = threadIdx.x;
+  const int64_t row0 = (int64_t)blockIdx.x * S;
+  for (int idx = s; idx < S * C; idx += blockDim.x) tile[idx] = 0.0f;
+  __syncthreads();
+  const int64_t i = row0 + s;
+  if (s < S && i < B) {
+    // batches of kAhead trees; the next batch (records and feature indices) is requested before
+    // the current one is added
+    constexpr int kAhead = 8;
+    const int64_t first = record_index(i, 0, T);  // tree j of this sample sits at first + j * 256
+    // three stages in flight: records of batch n+2, feature indices of batch n+1, additions of batch n
+    float a0[kAhead], a1[kAhead], a2[kAhead];
+    uint32_t wh1[kAhead], wh2[kAhead];
+    int c0[kAhead], c1[kAhead];
+    auto fetch_records = [&](int64_t j0, float (&fa)[kAhead], uint32_t (&fw)[kAhead]) {
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        const bool valid = j0 + u < T;
+        fa[u] = valid ? __ldcs(r.dx + first + (j0 + u) * kRecordBlock) : 0.0f;
+        fw[u] = valid ? __ldcs(r.where + first + (j0 + u) * kRecordBlock) : 1u;
+      }
+    };
+    auto fetch_features = [&](int64_t j0, const uint32_t (&fw)[kAhead], int (&fc)[kAhead]) {
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) fc[u] = j0 + u < T ? __ldg(ord + (j0 + u) * N + ((fw[u] & 0xffffu) - 1u)) : 0;
+    };
+    fetch_records(0, a0, wh1);
+    fetch_features(0, wh1, c0);
+    fetch_records(kAhead, a1, wh1);
+    for (int64_t j0 = 0; j0 < T; j0 += kAhead) {
+      fetch_records(j0 + 2 * kAhead, a2, wh2);
+      fetch_features(j0 + kAhead, wh1, c1);
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u)
+        if (j0 + u < T) tile[c0[u] * S + s] = __fadd_rn(tile[c0[u] * S + s], a0[u]);
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        a0[u] = a1[u];
+        c0[u] = c1[u];
+        a1[u] = a2[u];
+        wh1[u] = wh2[u];
+      }
+    }
+  }
+  __syncthreads();
+  if ((C & 3) == 0) {
+    const int quads = C >> 2;
+    for (int idx = threadIdx.x; idx < S * quads; idx += blockDim.x) {
+      const int ss = idx % S, q = idx / S;
+      if (row0 + ss < B)
+        *(reinterpret_cast<float4 *>(gx + (row0 + ss) * C) + q) =
+            make_float4(tile[(4 * q + 0) * S + ss], tile[(4 * q + 1) * S + ss], tile[(4 * q + 2) * S + ss],
+                        tile[(4 * q + 3) * S + ss]);
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < S * C; idx += blockDim.x) {
+      const int ss = idx % S, c = idx / S;
+      if (row0 + ss < B) gx[(row0 + ss) * C + c] = tile[c * S + ss];
+    }
+  }
 }
 
 template <int KIND>
@@ -315,14 +467,22 @@ int launch_kind(int depth, const BwdPlan &plan, const BwdArgs &a, unsigned grid,
 
 }  // namespace
 
+size_t backward_records_bytes(const ht_forest_problem *p) {
+  BwdPlan plan;
+  if (!make_bwd_plan(p, plan) || p->depth > 15) return 0;
+  const size_t bytes = 3 * record_array_bytes(p);
+  return bytes <= ((size_t)32 << 30) ? bytes : 0;
+}
+
 int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
-                   const float *g, float *gx, float *gthr, float *gw, void *records, uint32_t *status_word,
-                   cudaStream_t stream) {
+                   const float *g, float *gx, float *gthr, float *gw, void *records, void *eval_records,
+                   uint32_t *status_word, cudaStream_t stream) {
   BwdPlan plan;
   if (!make_bwd_plan(p, plan)) return HT_ERR_UNSUPPORTED;
   if (forward_tiled_workspace_bytes(p) == 0) return HT_ERR_UNSUPPORTED;  // the workspace holds no records otherwise
   if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(gx)) & 15u) != 0)
     return HT_ERR_UNSUPPORTED;
+  if (eval_records == nullptr && (p->flags & HT_DETERMINISTIC) != 0) return HT_ERR_UNSUPPORTED;
   const int64_t N = threshold_count(p->kind, p->depth);
   const int64_t L = ((int64_t)1) << p->depth;
   const int64_t elements = p->T * (N + L);
@@ -340,6 +500,13 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
   a.gx = gx;
   a.gthr = gthr;
   a.gw = gw;
+  a.evals = EvalRecords{nullptr, nullptr, nullptr};
+  if (eval_records != nullptr) {
+    const size_t stride = record_array_bytes(p);
+    unsigned char *base = static_cast<unsigned char *>(eval_records);
+    a.evals = EvalRecords{reinterpret_cast<float *>(base), reinterpret_cast<float *>(base + stride),
+                          reinterpret_cast<uint32_t *>(base + 2 * stride)};
+  }
   a.status_word = status_word;
   a.B = p->B;
   a.T = p->T;
@@ -348,8 +515,34 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
   a.G = plan.G;
   a.per_warp = plan.per_warp;
   const unsigned grid = (unsigned)((p->B + plan.S - 1) / plan.S);
-  return p->kind == TREE ? launch_kind<TREE>(p->depth, plan, a, grid, stream)
-                         : launch_kind<FERN>(p->depth, plan, a, grid, stream);
+  const int rc = p->kind == TREE ? launch_kind<TREE>(p->depth, plan, a, grid, stream)
+                                 : launch_kind<FERN>(p->depth, plan, a, grid, stream);
+  if (rc != HT_OK || eval_records == nullptr) return rc;
+
+  if (gthr != nullptr || gw != nullptr) {
+    // fixed-order mode: one warp per tree, the reference's sequential sum.  Default mode: as many
+    // warps as help (each needs work and its own bins), summed in warp order.
+    int warps = 1;
+    if ((p->flags & HT_DETERMINISTIC) == 0) {
+      warps = 16;
+      while (warps > 1 && ((size_t)warps * (N + L) * 4 > 64 * 1024 || p->B < (int64_t)warps * 512)) warps >>= 1;
+    }
+    const size_t smem = sizeof(float) * (size_t)(N + L) * warps;
+    HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kSmemBudget));
+    reduce_parameter_records_kernel<<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, p->B, p->T, N, L, gthr, gw);
+    HT_CHECK_LAUNCH();
+  }
+  if (gx != nullptr) {
+    int S = 128;  // 3 CTAs per SM at 128 features: the walk over the trees is latency bound
+    while (S > 32 && (size_t)S * p->C * 4 > 200 * 1024) S >>= 1;
+    const size_t smem = (size_t)S * p->C * 4;
+    if (smem > kSmemBudget) return HT_ERR_UNSUPPORTED;
+    HT_CUDA_TRY(cudaFuncSetAttribute(reduce_x_records_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    reduce_x_records_kernel<<<(unsigned)((p->B + S - 1) / S), S, smem, stream>>>(a.evals, ord, p->B, p->T, N, (int)p->C, S, gx);
+    HT_CHECK_LAUNCH();
+  }
+  return HT_OK;
 }
 
 }  // namespace ht

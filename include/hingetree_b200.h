@@ -51,6 +51,7 @@ typedef enum ht_status {
 
 /* ht_forest_problem.flags */
 #define HT_DETERMINISTIC 1u /* backward: fixed summation order equal to the reference CPU loops */
+#define HT_WORKSPACE_FOR_BACKWARD 2u /* ht_forest_workspace_bytes: include the backward's evaluation records */
 
 typedef struct ht_forest_problem {
   int32_t kind;   /* HT_KIND_TREE or HT_KIND_FERN */
@@ -68,8 +69,12 @@ int ht_version(void);
 const char *ht_status_string(int status);
 int ht_last_cuda_error(void); /* cudaError_t of the last failed runtime call on this thread */
 
-/* Scratch bytes ht_forest_* calls need for this problem (compact ordinals and, for the
- * backward, nothing more).  The workspace must be 256-byte aligned device memory. */
+/* Scratch bytes ht_forest_* calls need for this problem: compact ordinals and the tile kernel's
+ * per-tree records.  With HT_WORKSPACE_FOR_BACKWARD in p->flags the figure also covers 12 bytes
+ * per (sample, tree) of evaluation records, which let ht_forest_backward_f32 run its fastest,
+ * fixed-order path on tabular one-output-per-leaf problems (up to 32 GiB; beyond that, and
+ * whenever the workspace passed is smaller, the backward uses its other paths).  The workspace
+ * must be 256-byte aligned device memory. */
 size_t ht_forest_workspace_bytes(const ht_forest_problem *p);
 
 /* out[i,j,k,m] = |margin(i,j,k)| * w[j, leaf(i,j,k), m]

@@ -228,6 +228,16 @@ def test_tile_kernel_backward(cabi, kind, shape):
     ax, athr, aw = ho.backward_magnitudes(kind, x, thr, ord_, w, g)
     assert grad_close(gx, rx, ax) and grad_close(gthr, rthr, athr) and grad_close(gw, rw, aw)
     assert f.ordinal_flags() == 0
+    # with room for the evaluation records the tile path adds the x gradient in the reference's order in
+    # both modes, and everything in that order in fixed-order mode: exact
+    assert equal(gx, rx)
+    fd = cabi.Forest(kind, dx, dw, deterministic=True)
+    for got, ref in zip(fd.backward(dx, dthr, dord, dw, dg), (rx, rthr, rw)):
+        assert equal(got, ref)
+    # without that room: the scatter variant of the tile kernel (default mode), free summation order
+    small = cabi.Forest(kind, dx, dw, backward_workspace=False)
+    sx, sthr, sw = small.backward(dx, dthr, dord, dw, dg)
+    assert grad_close(sx, rx, ax) and grad_close(sthr, rthr, athr) and grad_close(sw, rw, aw)
     # only some gradients requested
     only_w = f.backward(dx, dthr, dord, dw, dg, need=(False, False, True))
     assert only_w[0] is None and only_w[1] is None and grad_close(only_w[2], rw, aw)
