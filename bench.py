@@ -289,7 +289,7 @@ class ForestRunner:
         self.out = torch.empty(self.forest.out_shape, dtype=torch.float32, device=device)
         self.g = None
         # ordinal pack (+ record repack when the tile kernel runs) + the evaluation kernel
-        self.launches = 3 if wl["M"] in (0, 1) and B * wl["T"] >= 32768 else 2
+        self.launches = 3 if B * wl["T"] >= 32768 else 2
 
     def enable_backward(self):
         torch = self.torch

@@ -31,6 +31,8 @@
 #include "ht_forest_tiled.cuh"
 #include "ht_tile_common.cuh"
 
+#include <algorithm>
+
 namespace ht {
 
 using namespace tile;
@@ -48,11 +50,11 @@ struct TilePlan {
 };
 
 bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
-  if (p->K != 1 || p->M != 1) return false;
+  if (p->K != 1 || p->M < 1 || p->M > 64) return false;
   if (p->C > 65536 || p->depth > 12) return false;
   if (p->B * p->T < 32 * 1024) return false;  // too small to fill the machine with sample tiles
   plan.ord_bytes = p->C <= 256 ? 1 : 2;
-  plan.rec = record_layout(p->kind, p->depth, (uint32_t)plan.ord_bytes);
+  plan.rec = record_layout(p->kind, p->depth, (uint32_t)plan.ord_bytes, p->M == 1);
   for (int S = 256; S >= 32; S >>= 1) {
     const int slots = kWarps / (S / 32);
     for (int per_warp = 4; per_warp >= 1; per_warp >>= 1) {
@@ -60,7 +62,7 @@ bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
       plan.S = S;
       plan.G = G;
       plan.per_warp = per_warp;
-      plan.smem = (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + (size_t)S * (G + 1) * 4 + 64;
+      plan.smem = (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + (size_t)S * (G * p->M + 1) * 4 + 64;
       if (plan.smem <= kSmemBudget) return true;
     }
   }
@@ -70,21 +72,24 @@ bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
 struct TiledArgs {
   const float *x;
   const unsigned char *records;
+  const float *w;  // leaf weights in global memory, read when there are several outputs per leaf
   float *out;
   uint32_t *status_word;
   int64_t B, T;
-  int C, S, G, per_warp;
+  int C, S, G, per_warp, M;
 };
 
 __device__ __forceinline__ uint32_t pick(const uint4 &q, int i) {
   return i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w;
 }
 
-// Walks NT trees (records at rec[0..NT)) for this lane's sample: |min margin| * leaf weight each.
-template <int KIND, int DEPTH, typename OrdT, int NT>
+// Walks NT trees (records at rec[0..NT)) for this lane's sample.  With the leaf weights in the
+// records (WREC) result is |min margin| * leaf weight; otherwise result is |min margin| and
+// path is 2^DEPTH + the path bits, root first.
+template <int KIND, int DEPTH, typename OrdT, int NT, bool WREC>
 __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr, uint32_t x_stride,
-                                     float (&result)[NT]) {
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+                                     float (&result)[NT], uint32_t (&path)[NT]) {
+  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC);
   uint32_t v[NT];
   float best[NT], first[NT];
   if (KIND == FERN) {
@@ -152,21 +157,26 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
   }
 #pragma unroll
   for (int u = 0; u < NT; ++u) {
-    const float wv = lds_f32(rec[u] + 4u * v[u] + (lay.w - 4u * (1u << DEPTH)));
     const float am = (first[u] != first[u]) ? first[u] : best[u];
-    result[u] = am * wv;
+    path[u] = v[u];
+    if (WREC)
+      result[u] = am * lds_f32(rec[u] + 4u * v[u] + (lay.w - 4u * (1u << DEPTH)));
+    else
+      result[u] = am;
   }
 }
 
-template <int KIND, int DEPTH, typename OrdT>
+template <int KIND, int DEPTH, typename OrdT, bool WREC>
 __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(TiledArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC);
   const int S = a.S, G = a.G, C = a.C;
+  const int M = WREC ? 1 : a.M;
+  const int row_floats = G * M + 1;  // staging row of one sample: G trees x M outputs, padded
   float *xs = reinterpret_cast<float *>(smem);
   unsigned char *params = smem + (size_t)C * S * 4;
   float *outs = reinterpret_cast<float *>(params + 2 * (size_t)G * lay.bytes);
-  uint64_t *full = reinterpret_cast<uint64_t *>(outs + (size_t)S * (G + 1));  // [2] copy landed
+  uint64_t *full = reinterpret_cast<uint64_t *>(outs + (size_t)S * row_floats);  // [2] copy landed
   uint32_t *finished = reinterpret_cast<uint32_t *>(full + 2);                 // [2] warps done with a buffer
 
   const int tid = threadIdx.x;
@@ -177,17 +187,21 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
   const int slot = warp / groups_of_samples;
   const int per_warp = a.per_warp;
   const int64_t row0 = (int64_t)blockIdx.x * S;
-  const int num_groups = (int)((a.T + G - 1) / G);
+  // blockIdx.y splits the tree groups among CTAs when there are too few sample tiles to fill the
+  // machine; this CTA walks groups [group0, group0 + num_groups), `it` counts them from 0
+  const int all_groups = (int)((a.T + G - 1) / G);
+  const int groups_per_cta = (all_groups + (int)gridDim.y - 1) / (int)gridDim.y;
+  const int group0 = (int)blockIdx.y * groups_per_cta;
+  const int num_groups = max(0, min(groups_per_cta, all_groups - group0));
   const uint32_t params_addr = smem_addr(params);
 
-  auto issue = [&](int group) {
-    const int64_t first_tree = (int64_t)group * G;
+  auto issue = [&](int it) {
+    const int64_t first_tree = (int64_t)(group0 + it) * G;
     const int64_t count = min((int64_t)G, a.T - first_tree);
     const uint32_t bytes = (uint32_t)(count * lay.bytes);
-    uint64_t *bar = &full[group & 1];
+    uint64_t *bar = &full[it & 1];
     mbar_expect_tx(bar, bytes);
-    bulk_load(params_addr + (uint32_t)(group & 1) * (uint32_t)G * lay.bytes, a.records + first_tree * lay.bytes, bytes,
-              bar);
+    bulk_load(params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes, a.records + first_tree * lay.bytes, bytes, bar);
   };
   if (tid == 0) {
     mbar_init(&full[0], 1);
@@ -195,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
     finished[0] = 0;
     finished[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    issue(0);
+    if (num_groups > 0) issue(0);
     if (num_groups > 1) issue(1);
   }
 
@@ -222,99 +236,121 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
 
   const uint32_t xl_addr = smem_addr(xs + sample_group * 32 + lane);
   const uint32_t x_stride = (uint32_t)S * 4u;
-  float *stage = outs + (size_t)sample_group * 32 * (G + 1);  // this sample group's [32][G + 1] staging rows
+  float *stage = outs + (size_t)sample_group * 32 * row_floats;  // this sample group's [32][G*M + 1] staging rows
   const int group_threads = slots * 32;
   const int tid_in_group = slot * 32 + lane;
+  constexpr uint32_t kL = 1u << DEPTH;
   bool poisoned = false;  // a bounded wait ran out: keep the barriers matched, stop waiting
 
-  for (int group = 0; group < num_groups; ++group) {
-    if (!poisoned && !mbar_wait(&full[group & 1], (uint32_t)((group >> 1) & 1))) {
+  for (int it = 0; it < num_groups; ++it) {
+    const int group = group0 + it;
+    if (!poisoned && !mbar_wait(&full[it & 1], (uint32_t)((it >> 1) & 1))) {
       poisoned = true;
       if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
     }
     const int in_group = (int)min((int64_t)G, a.T - (int64_t)group * G);
-    const uint32_t base_addr = params_addr + (uint32_t)(group & 1) * (uint32_t)G * lay.bytes;
+    const uint32_t base_addr = params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes;
     const int t_first = slot * per_warp;  // this warp's consecutive trees inside the group
     float result[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t path[4] = {kL, kL, kL, kL};
     if (t_first < in_group) {
       // trees beyond the end of a short last group repeat the last valid one (results unused)
       if (per_warp == 4) {
         uint32_t rec[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) rec[u] = base_addr + (uint32_t)min(t_first + u, in_group - 1) * lay.bytes;
-        walk<KIND, DEPTH, OrdT, 4>(rec, xl_addr, x_stride, result);
+        walk<KIND, DEPTH, OrdT, 4, WREC>(rec, xl_addr, x_stride, result, path);
       } else if (per_warp == 2) {
-        uint32_t rec[2];
+        uint32_t rec[2], p2[2];
 #pragma unroll
         for (int u = 0; u < 2; ++u) rec[u] = base_addr + (uint32_t)min(t_first + u, in_group - 1) * lay.bytes;
         float r2[2];
-        walk<KIND, DEPTH, OrdT, 2>(rec, xl_addr, x_stride, r2);
+        walk<KIND, DEPTH, OrdT, 2, WREC>(rec, xl_addr, x_stride, r2, p2);
         result[0] = r2[0];
         result[1] = r2[1];
+        path[0] = p2[0];
+        path[1] = p2[1];
       } else {
-        uint32_t rec[1] = {base_addr + (uint32_t)t_first * lay.bytes};
+        uint32_t rec[1] = {base_addr + (uint32_t)t_first * lay.bytes}, p1[1];
         float r1[1];
-        walk<KIND, DEPTH, OrdT, 1>(rec, xl_addr, x_stride, r1);
+        walk<KIND, DEPTH, OrdT, 1, WREC>(rec, xl_addr, x_stride, r1, p1);
         result[0] = r1[0];
+        path[0] = p1[0];
       }
     }
     // This warp no longer reads the parameter buffer.  The last warp to get here refills it.
     __syncwarp();
     if (lane == 0) {
       __threadfence_block();
-      const uint32_t before = atomicAdd(&finished[group & 1], 1u);
+      const uint32_t before = atomicAdd(&finished[it & 1], 1u);
       if (before == kWarps - 1) {
-        atomicExch(&finished[group & 1], 0u);
+        atomicExch(&finished[it & 1], 0u);
         __threadfence_block();
-        if (group + 2 < num_groups) issue(group + 2);
+        if (it + 2 < num_groups) issue(it + 2);
       }
     }
 
+    const int64_t col0 = (int64_t)group * G;
     named_barrier(1 + sample_group, group_threads);  // previous group's rows have left the staging area
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
-      if (u < per_warp && t_first + u < in_group) stage[lane * (G + 1) + t_first + u] = result[u];
+    for (int u = 0; u < 4; ++u) {
+      if (u < per_warp && t_first + u < in_group) {
+        if (WREC) {
+          stage[lane * row_floats + t_first + u] = result[u];
+        } else {
+          // several outputs per leaf: the leaf's weight row comes from global memory (L2 resident)
+          const uint32_t key = __brev(path[u] - kL) >> (32 - DEPTH);
+          const float *wl = a.w + ((col0 + t_first + u) * (int64_t)kL + key) * M;
+          float *dst = stage + lane * row_floats + (t_first + u) * M;
+          for (int m = 0; m < M; ++m) dst[m] = result[u] * __ldg(wl + m);
+        }
+      }
+    }
     named_barrier(1 + sample_group, group_threads);  // staging area complete
 
-    // the sample group's warps write its [32 x in_group] block of results as row segments
-    const int64_t col0 = (int64_t)group * G;
+    // the sample group's warps write its [32 x in_group*M] block of results as row segments
     const int64_t row_base = row0 + sample_group * 32;
-    if ((a.T & 3) == 0 && (in_group & 3) == 0) {
-      const int quads = in_group >> 2;
+    const int width = in_group * M;
+    const int64_t row_pitch = a.T * M, first_col = col0 * M;
+    if ((row_pitch & 3) == 0 && (first_col & 3) == 0 && (width & 3) == 0) {
+      const int quads = width >> 2;
       for (int idx = tid_in_group; idx < 32 * quads; idx += group_threads) {
         const int s = idx / quads, q = idx - s * quads;
         if (row_base + s < a.B) {
-          const float *src = stage + s * (G + 1) + 4 * q;
-          *reinterpret_cast<float4 *>(a.out + (row_base + s) * a.T + col0 + 4 * q) =
+          const float *src = stage + s * row_floats + 4 * q;
+          *reinterpret_cast<float4 *>(a.out + (row_base + s) * row_pitch + first_col + 4 * q) =
               make_float4(src[0], src[1], src[2], src[3]);
         }
       }
     } else {
-      for (int idx = tid_in_group; idx < 32 * in_group; idx += group_threads) {
-        const int s = idx / in_group, t = idx - s * in_group;
-        if (row_base + s < a.B) a.out[(row_base + s) * a.T + col0 + t] = stage[s * (G + 1) + t];
+      for (int idx = tid_in_group; idx < 32 * width; idx += group_threads) {
+        const int s = idx / width, t = idx - s * width;
+        if (row_base + s < a.B) a.out[(row_base + s) * row_pitch + first_col + t] = stage[s * row_floats + t];
       }
     }
   }
 }
 
-template <int KIND, int DEPTH>
-int launch_depth(const TilePlan &plan, const TiledArgs &a, unsigned grid, cudaStream_t stream) {
-  if (plan.ord_bytes == 1) {
-    auto kernel = forest_forward_tiled_kernel<KIND, DEPTH, uint8_t>;
-    HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-    kernel<<<grid, kThreads, plan.smem, stream>>>(a);
-  } else {
-    auto kernel = forest_forward_tiled_kernel<KIND, DEPTH, uint16_t>;
-    HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-    kernel<<<grid, kThreads, plan.smem, stream>>>(a);
-  }
+template <typename Kernel>
+int launch_one(Kernel kernel, const TilePlan &plan, const TiledArgs &a, dim3 grid, cudaStream_t stream) {
+  HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+  kernel<<<grid, kThreads, plan.smem, stream>>>(a);
   HT_CHECK_LAUNCH();
   return HT_OK;
 }
 
+template <int KIND, int DEPTH>
+int launch_depth(const TilePlan &plan, const TiledArgs &a, dim3 grid, cudaStream_t stream) {
+  const bool wrec = a.M == 1;
+  if (plan.ord_bytes == 1)
+    return wrec ? launch_one(forest_forward_tiled_kernel<KIND, DEPTH, uint8_t, true>, plan, a, grid, stream)
+                : launch_one(forest_forward_tiled_kernel<KIND, DEPTH, uint8_t, false>, plan, a, grid, stream);
+  return wrec ? launch_one(forest_forward_tiled_kernel<KIND, DEPTH, uint16_t, true>, plan, a, grid, stream)
+              : launch_one(forest_forward_tiled_kernel<KIND, DEPTH, uint16_t, false>, plan, a, grid, stream);
+}
+
 template <int KIND>
-int launch_kind(int depth, const TilePlan &plan, const TiledArgs &a, unsigned grid, cudaStream_t stream) {
+int launch_kind(int depth, const TilePlan &plan, const TiledArgs &a, dim3 grid, cudaStream_t stream) {
   switch (depth) {
 #define HT_DEPTH_CASE(D) \
   case D:                \
@@ -365,6 +401,8 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
   TiledArgs a;
   a.x = x;
   a.records = rec;
+  a.w = w;
+  a.M = (int)p->M;
   a.out = out;
   a.status_word = status_word;
   a.B = p->B;
@@ -373,7 +411,13 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
   a.S = plan.S;
   a.G = plan.G;
   a.per_warp = plan.per_warp;
-  const unsigned grid = (unsigned)((p->B + plan.S - 1) / plan.S);
+  // With few sample tiles the tree groups are split among CTAs (grid.y) until the machine is filled
+  // about twice over; every split re-stages the feature tile, which is cheap next to the walk.
+  const int64_t tiles = (p->B + plan.S - 1) / plan.S;
+  const int64_t groups = (p->T + plan.G - 1) / plan.G;
+  int64_t splits = 1;
+  if (tiles < 2 * 148) splits = std::min<int64_t>(groups, (2 * 148 + tiles - 1) / tiles);
+  const dim3 grid((unsigned)tiles, (unsigned)std::max<int64_t>(splits, 1));
   return p->kind == TREE ? launch_kind<TREE>(p->depth, plan, a, grid, stream)
                          : launch_kind<FERN>(p->depth, plan, a, grid, stream);
 }

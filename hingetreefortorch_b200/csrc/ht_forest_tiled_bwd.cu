@@ -15,6 +15,8 @@
 #include "ht_forest_tiled.cuh"
 #include "ht_tile_common.cuh"
 
+#include <algorithm>
+
 namespace ht {
 
 using namespace tile;
@@ -132,16 +134,20 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
   const int slot = warp / groups_of_samples;
   const int per_warp = a.per_warp;
   const int64_t row0 = (int64_t)blockIdx.x * S;
-  const int num_groups = (int)((a.T + G - 1) / G);
+  // the tree groups are split over gridDim.y when the batch alone gives too few tiles
+  const int all_groups = (int)((a.T + G - 1) / G);
+  const int groups_per_cta = (all_groups + (int)gridDim.y - 1) / (int)gridDim.y;
+  const int group0 = (int)blockIdx.y * groups_per_cta;
+  const int num_groups = max(0, min(groups_per_cta, all_groups - group0));
   const uint32_t params_addr = smem_addr(params);
 
-  auto issue = [&](int group) {
-    const int64_t first_tree = (int64_t)group * G;
+  auto issue = [&](int it) {
+    const int64_t first_tree = (int64_t)(group0 + it) * G;
     const int64_t count = min((int64_t)G, a.T - first_tree);
     const uint32_t bytes = (uint32_t)(count * lay.bytes);
-    uint64_t *bar = &full[group & 1];
+    uint64_t *bar = &full[it & 1];
     mbar_expect_tx(bar, bytes);
-    bulk_load(params_addr + (uint32_t)(group & 1) * (uint32_t)G * lay.bytes, a.records + first_tree * lay.bytes, bytes,
+    bulk_load(params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes, a.records + first_tree * lay.bytes, bytes,
               bar);
   };
   if (tid == 0) {
@@ -150,7 +156,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
     finished[0] = 0;
     finished[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    issue(0);
+    if (num_groups > 0) issue(0);
     if (num_groups > 1) issue(1);
   }
 
@@ -181,7 +187,8 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
   const int64_t my_row = row0 + my_sample;
   bool poisoned = false;
 
-  for (int group = 0; group < num_groups; ++group) {
+  for (int it = 0; it < num_groups; ++it) {
+    const int group = group0 + it;
     const int in_group = (int)min((int64_t)G, a.T - (int64_t)group * G);
     const int64_t col0 = (int64_t)group * G;
 
@@ -203,11 +210,11 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
       }
     }
 
-    if (!poisoned && !mbar_wait(&full[group & 1], (uint32_t)((group >> 1) & 1))) {
+    if (!poisoned && !mbar_wait(&full[it & 1], (uint32_t)((it >> 1) & 1))) {
       poisoned = true;
       if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
     }
-    const uint32_t base_addr = params_addr + (uint32_t)(group & 1) * (uint32_t)G * lay.bytes;
+    const uint32_t base_addr = params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes;
     if (t_first < in_group && !poisoned) {
       auto scatter = [&](const Walked &wk, uint32_t rec, int u) {
         const int t = t_first + u;
@@ -262,11 +269,11 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
     __syncwarp();
     if (lane == 0) {
       __threadfence_block();
-      const uint32_t before = atomicAdd(&finished[group & 1], 1u);
+      const uint32_t before = atomicAdd(&finished[it & 1], 1u);
       if (before == kWarps - 1) {
-        atomicExch(&finished[group & 1], 0u);
+        atomicExch(&finished[it & 1], 0u);
         __threadfence_block();
-        if (group + 2 < num_groups) issue(group + 2);
+        if (it + 2 < num_groups) issue(it + 2);
       }
     }
   }
@@ -274,7 +281,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
 }
 
 template <typename Kernel>
-int launch_one(Kernel kernel, const BwdPlan &plan, const BwdArgs &a, unsigned grid, cudaStream_t stream) {
+int launch_one(Kernel kernel, const BwdPlan &plan, const BwdArgs &a, dim3 grid, cudaStream_t stream) {
   HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
   kernel<<<grid, kThreads, plan.smem, stream>>>(a);
   HT_CHECK_LAUNCH();
@@ -282,7 +289,7 @@ int launch_one(Kernel kernel, const BwdPlan &plan, const BwdArgs &a, unsigned gr
 }
 
 template <int KIND, int DEPTH>
-int launch_depth(const BwdPlan &plan, const BwdArgs &a, unsigned grid, cudaStream_t stream) {
+int launch_depth(const BwdPlan &plan, const BwdArgs &a, dim3 grid, cudaStream_t stream) {
   const bool records = a.evals.dx != nullptr;
   if (plan.ord_bytes == 1)
     return records ? launch_one(forest_backward_tiled_kernel<KIND, DEPTH, uint8_t, true>, plan, a, grid, stream)
@@ -442,7 +449,7 @@ __global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, co
 }
 
 template <int KIND>
-int launch_kind(int depth, const BwdPlan &plan, const BwdArgs &a, unsigned grid, cudaStream_t stream) {
+int launch_kind(int depth, const BwdPlan &plan, const BwdArgs &a, dim3 grid, cudaStream_t stream) {
   switch (depth) {
 #define HT_DEPTH_CASE(D) \
   case D:                \
@@ -514,7 +521,12 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
   a.S = plan.S;
   a.G = plan.G;
   a.per_warp = plan.per_warp;
-  const unsigned grid = (unsigned)((p->B + plan.S - 1) / plan.S);
+  // a small batch gives too few sample tiles for 148 SMs: share the tree groups between CTAs
+  const int64_t tiles = (p->B + plan.S - 1) / plan.S;
+  const int64_t groups = (p->T + plan.G - 1) / plan.G;
+  int64_t splits = 1;
+  if (tiles < 2 * 148) splits = std::min<int64_t>(groups, (2 * 148 + tiles - 1) / tiles);
+  const dim3 grid((unsigned)tiles, (unsigned)std::max<int64_t>(splits, 1));
   const int rc = p->kind == TREE ? launch_kind<TREE>(p->depth, plan, a, grid, stream)
                                  : launch_kind<FERN>(p->depth, plan, a, grid, stream);
   if (rc != HT_OK || eval_records == nullptr) return rc;

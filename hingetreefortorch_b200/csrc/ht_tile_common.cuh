@@ -23,12 +23,14 @@ struct RecordLayout {
   uint32_t thr, ord, w, bytes;
 };
 
-__host__ __device__ constexpr RecordLayout record_layout(int kind, int depth, uint32_t ord_size) {
+// with_weights: the record carries the leaf weights (one output per leaf); with several outputs
+// per leaf the weights stay in global memory and the record ends after the feature indices.
+__host__ __device__ constexpr RecordLayout record_layout(int kind, int depth, uint32_t ord_size, bool with_weights = true) {
   const uint32_t n = kind == FERN ? (uint32_t)depth : (1u << depth) - 1u;
   const uint32_t thr = kind == FERN ? 0u : (uint32_t)kHeadBytes;
   const uint32_t ord = thr + round16(4u * n);
   const uint32_t w = ord + round16(ord_size * n);
-  return RecordLayout{thr, ord, w, round16(w + 4u * (1u << depth))};
+  return RecordLayout{thr, ord, w, with_weights ? round16(w + 4u * (1u << depth)) : w};
 }
 
 __device__ __forceinline__ uint32_t bit_reverse(uint32_t v, int bits) { return __brev(v) >> (32 - bits); }
@@ -63,7 +65,7 @@ __global__ void repack_records_kernel(const float *__restrict__ thr, const int32
       rec[13] = rec[14] = 0;
     }
     if (kind == TREE && r == 0) rec[15] = 0;
-  } else {
+  } else if (lay.bytes > lay.w) {  // records that carry the leaf weights
     const int64_t h = r - N;
     reinterpret_cast<float *>(rec + lay.w)[h] = w[j * L + (int64_t)bit_reverse((uint32_t)h, depth)];
   }

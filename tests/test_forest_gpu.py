@@ -243,3 +243,27 @@ def test_tile_kernel_backward(cabi, kind, shape):
     assert only_w[0] is None and only_w[1] is None and grad_close(only_w[2], rw, aw)
     only_x = f.backward(dx, dthr, dord, dw, dg, need=(True, False, False))
     assert grad_close(only_x[0], rx, ax)
+
+
+MULTI_OUTPUT_SHAPES = [
+    # B, C, T, depth, M: tabular input with several outputs per leaf (tile kernel, weights read from global memory)
+    (4096, 256, 20, 10, 10),
+    (700, 64, 50, 6, 3),
+    (513, 300, 66, 5, 8),
+    (300, 128, 130, 8, 2),
+]
+
+
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+@pytest.mark.parametrize("shape", MULTI_OUTPUT_SHAPES, ids=[str(s) for s in MULTI_OUTPUT_SHAPES])
+def test_tile_kernel_several_outputs_per_leaf(cabi, kind, shape):
+    B, C, T, depth, M = shape
+    x, thr, ord_, w = random_forest_inputs(90 + MULTI_OUTPUT_SHAPES.index(shape), kind, B, C, (), T, depth, (M,),
+                                           quantise=True)
+    x.reshape(-1)[::97] = np.nan
+    dx, dthr, dord, dw = dev(x, thr, ord_, w)
+    f = cabi.Forest(kind, dx, dw)
+    got = f.forward(dx, dthr, dord, dw).cpu().numpy()
+    assert got.shape == (B, T, M)
+    assert np.array_equal(got, ho.forward(kind, x, thr, ord_, w), equal_nan=True)
+    assert f.ordinal_flags() == 0
