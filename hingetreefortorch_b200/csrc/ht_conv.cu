@@ -9,6 +9,7 @@
 // walks the input channels itself, adding in the reference's order, so the forward is
 // deterministic and equal to the reference CPU loop bit for bit.
 #include "ht_common.cuh"
+#include "ht_conv_tiled.cuh"
 
 namespace ht {
 
@@ -256,6 +257,35 @@ int check_conv(const ht_conv_problem *p, ConvArgs &a) {
 
 size_t conv_ordinal_bytes(const ConvArgs &a) { return align_up((size_t)(a.Co * a.Ci * a.N) * sizeof(int32_t), 256); }
 
+// The problem as the shared-memory tile kernels see it (1-D and 2-D, one output per leaf).
+bool tile_problem(const ht_conv_problem *p, const ConvArgs &a, ConvTileProblem &t) {
+  if (p->dims > 2 || a.M != 1) return false;
+  const int row = p->dims == 2 ? 0 : -1, col = p->dims - 1;  // a 1-D signal is one image row
+  t.kind = p->kind;
+  t.depth = p->depth;
+  t.B = a.B;
+  t.Ci = a.Ci;
+  t.Co = a.Co;
+  t.H = row < 0 ? 1 : a.size[row];
+  t.W = a.size[col];
+  t.Ho = row < 0 ? 1 : a.osize[row];
+  t.Wo = a.osize[col];
+  t.kh = row < 0 ? 1 : a.kernel[row];
+  t.kw = a.kernel[col];
+  t.sy = row < 0 ? 1 : a.stride[row];
+  t.sx = a.stride[col];
+  t.py = row < 0 ? 0 : a.pad[row];
+  t.px = a.pad[col];
+  t.dy = row < 0 ? 1 : a.dil[row];
+  t.dx = a.dil[col];
+  return true;
+}
+
+size_t conv_records_bytes(const ht_conv_problem *p, const ConvArgs &a) {
+  ConvTileProblem t;
+  return tile_problem(p, a, t) ? conv_tiled_workspace_bytes(t) : 0;
+}
+
 int prepare_conv(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
                  void *workspace, size_t workspace_bytes, uint32_t *status_word, cudaStream_t stream, ConvArgs &a) {
   const int rc = check_conv(p, a);
@@ -334,7 +364,7 @@ int ht_conv_output_size(const ht_conv_problem *p, int64_t *osize) {
 size_t ht_conv_workspace_bytes(const ht_conv_problem *p) {
   ConvArgs a;
   if (check_conv(p, a) != HT_OK) return 0;
-  return conv_ordinal_bytes(a) + 256;
+  return conv_ordinal_bytes(a) + conv_records_bytes(p, a) + 256;
 }
 
 int ht_conv_forward_f32(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
@@ -346,6 +376,15 @@ int ht_conv_forward_f32(const ht_conv_problem *p, const float *x, const float *t
   const int64_t threads = a.B * a.Co * a.out_count;
   if (threads * a.M == 0) return HT_OK;
   if (out == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  ConvTileProblem t;
+  if (tile_problem(p, a, t)) {
+    const size_t records = conv_tiled_workspace_bytes(t);
+    if (records != 0 && workspace_bytes >= conv_ordinal_bytes(a) + records + 256) {
+      const int tiled = conv_forward_tiled(t, x, thr, a.ord, w, out, static_cast<unsigned char *>(workspace) + conv_ordinal_bytes(a),
+                                           status_word, s);
+      if (tiled != HT_ERR_UNSUPPORTED) return tiled;
+    }
+  }
   if (p->kind == TREE)
     conv_forward_kernel<TREE><<<blocks_for(threads), kBlock, 0, s>>>(a, out);
   else

@@ -79,93 +79,6 @@ struct TiledArgs {
   int C, S, G, per_warp, M;
 };
 
-__device__ __forceinline__ uint32_t pick(const uint4 &q, int i) {
-  return i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w;
-}
-
-// Walks NT trees (records at rec[0..NT)) for this lane's sample.  With the leaf weights in the
-// records (WREC) result is |min margin| * leaf weight; otherwise result is |min margin| and
-// path is 2^DEPTH + the path bits, root first.
-template <int KIND, int DEPTH, typename OrdT, int NT, bool WREC>
-__device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr, uint32_t x_stride,
-                                     float (&result)[NT], uint32_t (&path)[NT]) {
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC);
-  uint32_t v[NT];
-  float best[NT], first[NT];
-  if (KIND == FERN) {
-    // every lane tests the same decisions: thresholds and feature indices come in 16-byte broadcasts
-    constexpr int kPerWord = 4 / (int)sizeof(OrdT);   // feature indices per 32-bit word
-    constexpr int kPerQuad = 4 * kPerWord;            // ... per 16-byte load
-    uint4 tq[NT], oq[NT];
-#pragma unroll
-    for (int u = 0; u < NT; ++u) v[u] = 1u;
-#pragma unroll
-    for (int l = 0; l < DEPTH; ++l) {
-#pragma unroll
-      for (int u = 0; u < NT; ++u) {
-        if (l % 4 == 0) tq[u] = lds_b128(rec[u] + lay.thr + 4u * l);
-        if (l % kPerQuad == 0) oq[u] = lds_b128(rec[u] + lay.ord + (uint32_t)sizeof(OrdT) * l);
-        const uint32_t tbits = pick(tq[u], l % 4);
-        const uint32_t obits = pick(oq[u], (l % kPerQuad) / kPerWord);
-        const uint32_t c = (obits >> (8 * (int)sizeof(OrdT) * (l % kPerWord))) & (sizeof(OrdT) == 1 ? 0xffu : 0xffffu);
-        const float nm = __uint_as_float(tbits) - lds_f32(c * x_stride + xl_addr);
-        const float am = fabsf(nm);
-        if (l == 0) {
-          best[u] = am;
-          first[u] = am;
-        } else {
-          best[u] = fminf(best[u], am);
-        }
-        v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
-      }
-    }
-  } else {
-    constexpr bool kHead = sizeof(OrdT) == 1;  // root + children in one 16-byte broadcast
-    uint4 head[NT];
-#pragma unroll
-    for (int u = 0; u < NT; ++u) {
-      v[u] = 1u;
-      if (kHead) head[u] = lds_b128(rec[u]);
-    }
-#pragma unroll
-    for (int l = 0; l < DEPTH; ++l) {
-#pragma unroll
-      for (int u = 0; u < NT; ++u) {
-        float thr;
-        uint32_t c;
-        if (kHead && l == 0) {
-          thr = __uint_as_float(head[u].x);
-          c = head[u].w & 0xffu;
-        } else if (kHead && l == 1) {
-          thr = __uint_as_float((v[u] & 1u) ? head[u].z : head[u].y);
-          c = __byte_perm(head[u].w, 0u, 0x4440u + (v[u] - 1u));
-        } else {
-          thr = lds_f32(rec[u] + 4u * v[u] + (lay.thr - 4u));
-          c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * v[u] + (lay.ord - (uint32_t)sizeof(OrdT)));
-        }
-        const float nm = thr - lds_f32(c * x_stride + xl_addr);
-        const float am = fabsf(nm);
-        if (l == 0) {
-          best[u] = am;
-          first[u] = am;
-        } else {
-          best[u] = fminf(best[u], am);
-        }
-        v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
-      }
-    }
-  }
-#pragma unroll
-  for (int u = 0; u < NT; ++u) {
-    const float am = (first[u] != first[u]) ? first[u] : best[u];
-    path[u] = v[u];
-    if (WREC)
-      result[u] = am * lds_f32(rec[u] + 4u * v[u] + (lay.w - 4u * (1u << DEPTH)));
-    else
-      result[u] = am;
-  }
-}
-
 template <int KIND, int DEPTH, typename OrdT, bool WREC>
 __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(TiledArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];

@@ -35,12 +35,22 @@ __host__ __device__ constexpr RecordLayout record_layout(int kind, int depth, ui
 
 __device__ __forceinline__ uint32_t bit_reverse(uint32_t v, int bits) { return __brev(v) >> (32 - bits); }
 
+// What a record stores for a feature index f: f itself for tabular input; for a 2-D convolution
+// window cell f = (row, column) the offset of that cell inside a staged image patch.
+struct FeatureRemap {
+  int columns = 0;  // cells per window row; 0: identity
+  int row_step = 0, column_step = 0;
+  __host__ __device__ uint32_t operator()(uint32_t f) const {
+    return columns == 0 ? f : (f / (uint32_t)columns) * (uint32_t)row_step + (f % (uint32_t)columns) * (uint32_t)column_step;
+  }
+};
+
 // One thread per record element.  Leaf weights are permuted so that the path bits in the order
 // the traversal collects them (root first, most significant) address them directly.
 template <typename OrdT>
 __global__ void repack_records_kernel(const float *__restrict__ thr, const int32_t *__restrict__ ord,
                                       const float *__restrict__ w, unsigned char *__restrict__ records, int kind,
-                                      int depth, int64_t T, RecordLayout lay) {
+                                      int depth, int64_t T, RecordLayout lay, FeatureRemap remap = FeatureRemap()) {
   const int64_t N = threshold_count(kind, depth);
   const int64_t L = ((int64_t)1) << depth;
   const int64_t per_tree = N + L;
@@ -52,7 +62,7 @@ __global__ void repack_records_kernel(const float *__restrict__ thr, const int32
   if (r < N) {
     float t = thr[j * N + r];
     t = t == 0.0f ? 0.0f : t;  // -0 becomes +0
-    const uint32_t c = (uint32_t)ord[j * N + r];
+    const uint32_t c = remap((uint32_t)ord[j * N + r]);
     reinterpret_cast<float *>(rec + lay.thr)[r] = t;
     reinterpret_cast<OrdT *>(rec + lay.ord)[r] = (OrdT)c;
     if (kind == TREE && r < 3) {  // root and its children again, for one broadcast load
@@ -130,6 +140,92 @@ __device__ __forceinline__ uint32_t lds_ord(uint32_t addr) {
   return v;
 }
 
+__device__ __forceinline__ uint32_t pick(const uint4 &q, int i) {
+  return i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w;
+}
+
+// Walks NT trees (records at rec[0..NT)) for this lane's sample.  With the leaf weights in the
+// records (WREC) result is |min margin| * leaf weight; otherwise result is |min margin| and
+// path is 2^DEPTH + the path bits, root first.
+template <int KIND, int DEPTH, typename OrdT, int NT, bool WREC>
+__device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr, uint32_t x_stride,
+                                     float (&result)[NT], uint32_t (&path)[NT]) {
+  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC);
+  uint32_t v[NT];
+  float best[NT], first[NT];
+  if (KIND == FERN) {
+    // every lane tests the same decisions: thresholds and feature indices come in 16-byte broadcasts
+    constexpr int kPerWord = 4 / (int)sizeof(OrdT);   // feature indices per 32-bit word
+    constexpr int kPerQuad = 4 * kPerWord;            // ... per 16-byte load
+    uint4 tq[NT], oq[NT];
+#pragma unroll
+    for (int u = 0; u < NT; ++u) v[u] = 1u;
+#pragma unroll
+    for (int l = 0; l < DEPTH; ++l) {
+#pragma unroll
+      for (int u = 0; u < NT; ++u) {
+        if (l % 4 == 0) tq[u] = lds_b128(rec[u] + lay.thr + 4u * l);
+        if (l % kPerQuad == 0) oq[u] = lds_b128(rec[u] + lay.ord + (uint32_t)sizeof(OrdT) * l);
+        const uint32_t tbits = pick(tq[u], l % 4);
+        const uint32_t obits = pick(oq[u], (l % kPerQuad) / kPerWord);
+        const uint32_t c = (obits >> (8 * (int)sizeof(OrdT) * (l % kPerWord))) & (sizeof(OrdT) == 1 ? 0xffu : 0xffffu);
+        const float nm = __uint_as_float(tbits) - lds_f32(c * x_stride + xl_addr);
+        const float am = fabsf(nm);
+        if (l == 0) {
+          best[u] = am;
+          first[u] = am;
+        } else {
+          best[u] = fminf(best[u], am);
+        }
+        v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
+      }
+    }
+  } else {
+    constexpr bool kHead = sizeof(OrdT) == 1;  // root + children in one 16-byte broadcast
+    uint4 head[NT];
+#pragma unroll
+    for (int u = 0; u < NT; ++u) {
+      v[u] = 1u;
+      if (kHead) head[u] = lds_b128(rec[u]);
+    }
+#pragma unroll
+    for (int l = 0; l < DEPTH; ++l) {
+#pragma unroll
+      for (int u = 0; u < NT; ++u) {
+        float thr;
+        uint32_t c;
+        if (kHead && l == 0) {
+          thr = __uint_as_float(head[u].x);
+          c = head[u].w & 0xffu;
+        } else if (kHead && l == 1) {
+          thr = __uint_as_float((v[u] & 1u) ? head[u].z : head[u].y);
+          c = __byte_perm(head[u].w, 0u, 0x4440u + (v[u] - 1u));
+        } else {
+          thr = lds_f32(rec[u] + 4u * v[u] + (lay.thr - 4u));
+          c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * v[u] + (lay.ord - (uint32_t)sizeof(OrdT)));
+        }
+        const float nm = thr - lds_f32(c * x_stride + xl_addr);
+        const float am = fabsf(nm);
+        if (l == 0) {
+          best[u] = am;
+          first[u] = am;
+        } else {
+          best[u] = fminf(best[u], am);
+        }
+        v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < NT; ++u) {
+    const float am = (first[u] != first[u]) ? first[u] : best[u];
+    path[u] = v[u];
+    if (WREC)
+      result[u] = __fmul_rn(am, lds_f32(rec[u] + 4u * v[u] + (lay.w - 4u * (1u << DEPTH))));
+    else
+      result[u] = am;
+  }
+}
 
 }  // namespace tile
 }  // namespace ht

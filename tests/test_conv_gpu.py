@@ -31,6 +31,15 @@ CONV_CASES = [
     (2, (1, 2, 8, 9), 3, 2, (2,), (2, 3), (2, 1), (1, 2), (2, 1)),
     (2, (3, 4, 12, 12), 6, 4, (9,), (3, 3), (2, 2), (0, 0), (1, 1)),
     (3, (1, 2, 5, 6, 4), 2, 2, (), (2, 3, 2), (1, 2, 1), (1, 0, 1), (1, 1, 2)),
+    # large enough for the shared-memory tile kernel (one output per leaf, >= 2^20 tree evaluations):
+    # ragged channel chunks and output-channel blocks, few tiles (output channels split over CTAs)
+    (2, (2, 20, 48, 70), 8, 5, (), (3, 3), (1, 1), (1, 1), (1, 1)),
+    # stride, dilation, padding wider than the window overhang, non-square window, odd channel counts
+    (2, (1, 7, 67, 90), 50, 4, (), (3, 5), (2, 1), (2, 3), (2, 1)),
+    # window offsets beyond one byte
+    (2, (1, 4, 60, 64), 80, 3, (), (3, 3), (1, 1), (6, 6), (6, 6)),
+    # 1-D: one tile row
+    (1, (4, 6, 3000), 16, 6, (), (7,), (1,), (3,), (1,)),
 ]
 
 
