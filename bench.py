@@ -304,7 +304,12 @@ class ForestRunner:
             self.forest.backward(self.x, self.thr, self.ord, self.w, self.g, outs=self.grads)
 
     def launches_per_step(self, backward):
-        return self.launches + (2 if backward else 0)
+        if not backward:
+            return self.launches
+        # one output per leaf on the tile path: ordinal pack, record repack, traversal, two ordered reductions;
+        # otherwise ordinal pack + the scatter kernel
+        tiled = self.launches == 3 and self.wl["M"] <= 1
+        return self.launches + (5 if tiled else 2)
 
     def check(self):
         if self.forest.ordinal_flags() != 0:
@@ -410,8 +415,9 @@ class ModuleRunner:
         self._train_step(self.x)
 
     def launches_per_step(self, backward):
-        # this library's kernels only: ordinal pack + forward, ordinal pack + backward (torch's GEMM / BN not counted)
-        return 4
+        # this library's kernels only (torch's GEMM / BN not counted): ordinal pack, record repack and the tile
+        # kernel in each direction; the forest backward adds its two ordered reductions
+        return 6 if self.wl["op"] == "conv" else 8
 
     def check(self):
         pass

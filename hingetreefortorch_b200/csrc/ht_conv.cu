@@ -11,6 +11,8 @@
 #include "ht_common.cuh"
 #include "ht_conv_tiled.cuh"
 
+#include <algorithm>
+
 namespace ht {
 
 namespace {
@@ -283,7 +285,8 @@ bool tile_problem(const ht_conv_problem *p, const ConvArgs &a, ConvTileProblem &
 
 size_t conv_records_bytes(const ht_conv_problem *p, const ConvArgs &a) {
   ConvTileProblem t;
-  return tile_problem(p, a, t) ? conv_tiled_workspace_bytes(t) : 0;
+  if (!tile_problem(p, a, t)) return 0;
+  return std::max(conv_tiled_workspace_bytes(t), conv_backward_tiled_workspace_bytes(t));
 }
 
 int prepare_conv(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
@@ -409,6 +412,15 @@ int ht_conv_backward_f32(const ht_conv_problem *p, const float *x, const float *
   const int64_t threads = a.B * a.Co * a.out_count;
   if (threads * a.M == 0 || (gx == nullptr && gthr == nullptr && gw == nullptr)) return HT_OK;
   if (g == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  ConvTileProblem t;
+  if (tile_problem(p, a, t)) {
+    const size_t records = conv_backward_tiled_workspace_bytes(t);
+    if (records != 0 && workspace_bytes >= conv_ordinal_bytes(a) + records + 256) {
+      const int tiled = conv_backward_tiled(t, x, thr, a.ord, w, g, gx, gthr, gw,
+                                            static_cast<unsigned char *>(workspace) + conv_ordinal_bytes(a), status_word, s);
+      if (tiled != HT_ERR_UNSUPPORTED) return tiled;
+    }
+  }
   if (p->kind == TREE)
     conv_backward_kernel<TREE><<<blocks_for(threads), kBlock, 0, s>>>(a, g, gx, gthr, gw);
   else

@@ -24,10 +24,9 @@
 namespace ht {
 
 using namespace tile;
+using namespace conv_tile;
 
 namespace {
-
-constexpr int kTileColumns = 32;
 
 struct ConvTilePlan {
   int TY;              // tile rows; slots = kWarps / TY
@@ -44,11 +43,11 @@ bool make_plan(const ConvTileProblem &p, ConvTilePlan &plan) {
   for (int TY = 8; TY >= 1; TY >>= 1) {
     if (TY > 1 && TY / 2 >= p.Ho) continue;  // no taller than the output needs
     plan.TY = TY;
-    plan.patch_h = (TY - 1) * p.sy + (p.kh - 1) * p.dy + 1;
-    plan.patch_w = (kTileColumns - 1) * p.sx + (p.kw - 1) * p.dx + 1;
-    const int64_t far = (int64_t)(p.kh - 1) * p.dy * plan.patch_w + (int64_t)(p.kw - 1) * p.dx;
-    if (far > 65535) continue;
-    plan.ord_bytes = far <= 255 ? 1 : 2;
+    const PatchShape shape = patch_shape(p, TY);
+    plan.patch_h = shape.h;
+    plan.patch_w = shape.w;
+    if (shape.far > 65535) continue;
+    plan.ord_bytes = shape.far <= 255 ? 1 : 2;
     plan.rec = record_layout(p.kind, p.depth, (uint32_t)plan.ord_bytes);
     const size_t patches = (size_t)p.Ci * plan.patch_h * plan.patch_w * 4;
     const int JB = (kWarps / TY) * 4;
@@ -126,21 +125,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_forward_tiled_kernel(ConvTil
     if (num_groups > 1) issue(1);
   }
 
-  // the patches of all input channels under this tile; cells outside the image read as 0
-  // (the reference's padding value, ImageToMatrix.h:138)
-  {
-    const int iy0 = oy0 * a.sy - a.py, ix0 = ox0 * a.sx - a.px;
-    const float *image = a.x + b * a.Ci * (int64_t)a.H * a.W;
-    const int total = a.Ci * patch_elems;
-    for (int idx = tid; idx < total; idx += kThreads) {
-      const int c = idx / patch_elems, r = idx - c * patch_elems;
-      const int yy = r / a.patch_w, xx = r - yy * a.patch_w;
-      const int iy = iy0 + yy, ix = ix0 + xx;
-      float v = 0.0f;
-      if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W) v = __ldg(image + ((int64_t)c * a.H + iy) * a.W + ix);
-      patches[idx] = v;
-    }
-  }
+  stage_patches(patches, a.x + b * a.Ci * (int64_t)a.H * a.W, a.Ci, a.H, a.W, oy0 * a.sy - a.py, ox0 * a.sx - a.px,
+                a.patch_h, a.patch_w);
   __syncthreads();  // patches staged; barrier initialisation visible
 
   // this lane's window origin inside a patch; a window cell is origin + the offset held in the record
@@ -261,14 +247,14 @@ int conv_forward_tiled(const ConvTileProblem &p, const float *x, const float *th
   const int64_t L = ((int64_t)1) << p.depth;
   const unsigned pack_grid = (unsigned)((trees * (N + L) + 255) / 256);
   unsigned char *rec = static_cast<unsigned char *>(records);
-  FeatureRemap remap;
-  remap.columns = p.kw;
-  remap.row_step = p.dy * plan.patch_w;
-  remap.column_step = p.dx;
+  RecordMap map;
+  map.columns = p.kw;
+  map.row_step = p.dy * plan.patch_w;
+  map.column_step = p.dx;
   if (plan.ord_bytes == 1)
-    repack_records_kernel<uint8_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p.kind, p.depth, trees, plan.rec, remap);
+    repack_records_kernel<uint8_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p.kind, p.depth, trees, plan.rec, map);
   else
-    repack_records_kernel<uint16_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p.kind, p.depth, trees, plan.rec, remap);
+    repack_records_kernel<uint16_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p.kind, p.depth, trees, plan.rec, map);
   HT_CHECK_LAUNCH();
 
   ConvTileArgs a;

@@ -82,38 +82,6 @@ struct BwdArgs {
   int C, S, G, per_warp;
 };
 
-struct Walked {
-  float nm;      // threshold - feature at the deciding vertex (the negated signed margin)
-  uint32_t v;    // 1-based index of the deciding vertex (ferns: level + 1)
-  uint32_t path; // 2^DEPTH + path bits, root first (most significant)
-};
-
-template <int KIND, int DEPTH, typename OrdT, int NT>
-__device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], uint32_t xl_addr, uint32_t x_stride,
-                                          Walked (&out)[NT]) {
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
-  uint32_t v[NT];
-#pragma unroll
-  for (int u = 0; u < NT; ++u) v[u] = 1u;
-#pragma unroll
-  for (int l = 0; l < DEPTH; ++l) {
-#pragma unroll
-    for (int u = 0; u < NT; ++u) {
-      const uint32_t at = KIND == FERN ? (uint32_t)(l + 1) : v[u];
-      const float thr = lds_f32(rec[u] + 4u * at + (lay.thr - 4u));
-      const uint32_t c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * at + (lay.ord - (uint32_t)sizeof(OrdT)));
-      const float nm = thr - lds_f32(c * x_stride + xl_addr);
-      if (l == 0 || fabsf(nm) < fabsf(out[u].nm)) {
-        out[u].nm = nm;
-        out[u].v = at;
-      }
-      v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
-    }
-  }
-#pragma unroll
-  for (int u = 0; u < NT; ++u) out[u].path = v[u];
-}
-
 template <int KIND, int DEPTH, typename OrdT, bool RECORDS>
 __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];

@@ -35,14 +35,18 @@ __host__ __device__ constexpr RecordLayout record_layout(int kind, int depth, ui
 
 __device__ __forceinline__ uint32_t bit_reverse(uint32_t v, int bits) { return __brev(v) >> (32 - bits); }
 
-// What a record stores for a feature index f: f itself for tabular input; for a 2-D convolution
-// window cell f = (row, column) the offset of that cell inside a staged image patch.
-struct FeatureRemap {
-  int columns = 0;  // cells per window row; 0: identity
+// How the repack kernel places things.  Feature index f: stored as is for tabular input; for a
+// 2-D convolution window cell f = (row, column) the record holds the offset of that cell inside a
+// staged image patch.  Tree t: record t, or, for trees numbered (outer, inner) = t / inner, t % inner,
+// record inner * outer_count + outer (the transposed order) when `inner` is set.
+struct RecordMap {
+  int columns = 0;  // cells per window row; 0: features stored as they are
   int row_step = 0, column_step = 0;
-  __host__ __device__ uint32_t operator()(uint32_t f) const {
+  int64_t inner = 0, outer_count = 0;
+  __host__ __device__ uint32_t feature(uint32_t f) const {
     return columns == 0 ? f : (f / (uint32_t)columns) * (uint32_t)row_step + (f % (uint32_t)columns) * (uint32_t)column_step;
   }
+  __host__ __device__ int64_t slot(int64_t t) const { return inner == 0 ? t : (t % inner) * outer_count + t / inner; }
 };
 
 // One thread per record element.  Leaf weights are permuted so that the path bits in the order
@@ -50,7 +54,7 @@ struct FeatureRemap {
 template <typename OrdT>
 __global__ void repack_records_kernel(const float *__restrict__ thr, const int32_t *__restrict__ ord,
                                       const float *__restrict__ w, unsigned char *__restrict__ records, int kind,
-                                      int depth, int64_t T, RecordLayout lay, FeatureRemap remap = FeatureRemap()) {
+                                      int depth, int64_t T, RecordLayout lay, RecordMap map = RecordMap()) {
   const int64_t N = threshold_count(kind, depth);
   const int64_t L = ((int64_t)1) << depth;
   const int64_t per_tree = N + L;
@@ -58,11 +62,11 @@ __global__ void repack_records_kernel(const float *__restrict__ thr, const int32
   if (e >= T * per_tree) return;
   const int64_t j = e / per_tree;
   const int64_t r = e - j * per_tree;
-  unsigned char *rec = records + j * lay.bytes;
+  unsigned char *rec = records + map.slot(j) * lay.bytes;
   if (r < N) {
     float t = thr[j * N + r];
     t = t == 0.0f ? 0.0f : t;  // -0 becomes +0
-    const uint32_t c = remap((uint32_t)ord[j * N + r]);
+    const uint32_t c = map.feature((uint32_t)ord[j * N + r]);
     reinterpret_cast<float *>(rec + lay.thr)[r] = t;
     reinterpret_cast<OrdT *>(rec + lay.ord)[r] = (OrdT)c;
     if (kind == TREE && r < 3) {  // root and its children again, for one broadcast load
@@ -225,6 +229,51 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
     else
       result[u] = am;
   }
+}
+
+// The traversal as the backward needs it: the signed margin and the deciding vertex, with the
+// reference's strict `<` so that the shallowest minimum wins.
+struct Walked {
+  float nm;      // threshold - feature at the deciding vertex (the negated signed margin)
+  uint32_t v;    // 1-based index of the deciding vertex (ferns: level + 1)
+  uint32_t path; // 2^DEPTH + path bits, root first (most significant)
+};
+
+// rec[u] and x_addr[u]: record and feature base (shared-memory addresses) of the u-th walk in flight.
+template <int KIND, int DEPTH, typename OrdT, int NT>
+__device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], const uint32_t (&x_addr)[NT], uint32_t x_stride,
+                                          Walked (&out)[NT]) {
+  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+  uint32_t v[NT];
+#pragma unroll
+  for (int u = 0; u < NT; ++u) v[u] = 1u;
+#pragma unroll
+  for (int l = 0; l < DEPTH; ++l) {
+#pragma unroll
+    for (int u = 0; u < NT; ++u) {
+      const uint32_t at = KIND == FERN ? (uint32_t)(l + 1) : v[u];
+      const float thr = lds_f32(rec[u] + 4u * at + (lay.thr - 4u));
+      const uint32_t c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * at + (lay.ord - (uint32_t)sizeof(OrdT)));
+      const float nm = thr - lds_f32(c * x_stride + x_addr[u]);
+      if (l == 0 || fabsf(nm) < fabsf(out[u].nm)) {
+        out[u].nm = nm;
+        out[u].v = at;
+      }
+      v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < NT; ++u) out[u].path = v[u];
+}
+
+// The same with one feature base for all walks (several trees on one sample or position).
+template <int KIND, int DEPTH, typename OrdT, int NT>
+__device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], uint32_t xl_addr, uint32_t x_stride,
+                                          Walked (&out)[NT]) {
+  uint32_t x_addr[NT];
+#pragma unroll
+  for (int u = 0; u < NT; ++u) x_addr[u] = xl_addr;
+  walk_full<KIND, DEPTH, OrdT, NT>(rec, x_addr, x_stride, out);
 }
 
 }  // namespace tile
