@@ -99,24 +99,6 @@ __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
   asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
-// Sum of `val` over the lanes of the warp whose `key` equals this lane's, delivered in the lowest
-// of those lanes (`leader`).  All 32 lanes call it.  The leaders then hold distinct keys, so their
-// shared-memory atomics do not collide inside the warp (a float atomic on shared memory is a
-// compare-and-swap loop, which collisions make many times slower).
-__device__ __forceinline__ float sum_by_key(uint32_t key, float val, int lane, bool &leader) {
-  const uint32_t mask = __match_any_sync(0xffffffffu, key);
-  leader = (mask & ((1u << lane) - 1u)) == 0u;
-  uint32_t rest = leader ? (mask & ~(1u << lane)) : 0u;
-  float sum = val;
-  while (__any_sync(0xffffffffu, rest != 0u)) {
-    const int src = rest != 0u ? __ffs((int)rest) - 1 : lane;
-    const float v = __shfl_sync(0xffffffffu, val, src);
-    if (rest != 0u) sum = __fadd_rn(sum, v);
-    rest &= rest - 1u;
-  }
-  return sum;
-}
-
 template <int KIND, int DEPTH, typename OrdT>
 __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];

@@ -291,6 +291,11 @@ __device__ __forceinline__ void lanes_in_order_per_key(bool valid, uint32_t key,
 // memory (lanes that meet in a bin add in lane order); the warps' bins are then summed in warp
 // order.  With one warp (fixed-order mode) that is exactly the reference's sequential sum over
 // the samples; with several (default mode) it is a reproducible sum with another association.
+// ORDERED = false (default mode only): the lanes that meet in a bin first add their terms together
+// with shuffles in a logarithmic number of rounds, and the lowest lane of each bin updates it once;
+// the ordered form pays one dependent round per lane of the fullest bin, and a few bins (the root
+// threshold, the likeliest leaves) collect a third of the lanes of a typical chunk.
+template <bool ORDERED>
 __global__ void __launch_bounds__(512) reduce_parameter_records_kernel(EvalRecords r, int64_t B, int64_t T, int64_t N,
                                                                        int64_t L, float *gthr, float *gw) {
   extern __shared__ float all_bins[];
@@ -325,10 +330,23 @@ __global__ void __launch_bounds__(512) reduce_parameter_records_kernel(EvalRecor
     for (int u = 0; u < kAhead; ++u) {
       const bool valid = i0 + 32 * u + lane < B;
       const uint32_t v = (wh[u] & 0xffffu) - 1u, key = wh[u] >> 16;
-      if (gthr != nullptr)
-        lanes_in_order_per_key(valid, v, [&]() { thr_bins[v] = __fadd_rn(thr_bins[v], -a[u]); });
-      if (gw != nullptr)
-        lanes_in_order_per_key(valid, key, [&]() { w_bins[key] = __fadd_rn(w_bins[key], b[u]); });
+      if (ORDERED) {
+        if (gthr != nullptr)
+          lanes_in_order_per_key(valid, v, [&]() { thr_bins[v] = __fadd_rn(thr_bins[v], -a[u]); });
+        if (gw != nullptr)
+          lanes_in_order_per_key(valid, key, [&]() { w_bins[key] = __fadd_rn(w_bins[key], b[u]); });
+      } else {
+        bool leader;
+        if (gthr != nullptr) {
+          const float sum = sum_by_key(valid ? v : (0x80000000u | lane), valid ? -a[u] : 0.0f, (int)lane, leader);
+          if (leader && valid) thr_bins[v] = __fadd_rn(thr_bins[v], sum);
+        }
+        if (gw != nullptr) {
+          const float sum = sum_by_key(valid ? key : (0x80000000u | lane), valid ? b[u] : 0.0f, (int)lane, leader);
+          if (leader && valid) w_bins[key] = __fadd_rn(w_bins[key], sum);
+        }
+        __syncwarp();
+      }
     }
 #pragma unroll
     for (int u = 0; u < kAhead; ++u) {
@@ -508,9 +526,15 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
       while (warps > 1 && ((size_t)warps * (N + L) * 4 > 64 * 1024 || p->B < (int64_t)warps * 512)) warps >>= 1;
     }
     const size_t smem = sizeof(float) * (size_t)(N + L) * warps;
-    HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)kSmemBudget));
-    reduce_parameter_records_kernel<<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, p->B, p->T, N, L, gthr, gw);
+    if ((p->flags & HT_DETERMINISTIC) != 0) {
+      HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)kSmemBudget));
+      reduce_parameter_records_kernel<true><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, p->B, p->T, N, L, gthr, gw);
+    } else {
+      HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)kSmemBudget));
+      reduce_parameter_records_kernel<false><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, p->B, p->T, N, L, gthr, gw);
+    }
     HT_CHECK_LAUNCH();
   }
   if (gx != nullptr) {

@@ -276,5 +276,29 @@ __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], uint32_t xl
   walk_full<KIND, DEPTH, OrdT, NT>(rec, x_addr, x_stride, out);
 }
 
+// Sum of `val` over the lanes of the warp whose `key` equals this lane's, delivered in the lowest
+// of those lanes (`leader`).  All 32 lanes call it.  The lanes of a key form a list (each points to
+// the next higher one); pointer jumping doubles the span a lane has summed in every round, so the
+// cost grows with the logarithm of the longest list, not its length.  The leaders hold distinct
+// keys, so their updates of shared-memory bins do not collide inside the warp.
+__device__ __forceinline__ float sum_by_key(uint32_t key, float val, int lane, bool &leader) {
+  const uint32_t mask = __match_any_sync(0xffffffffu, key);
+  leader = (mask & ((1u << lane) - 1u)) == 0u;
+  const uint32_t above = mask & ~((2u << lane) - 1u);
+  int next = above != 0u ? __ffs((int)above) - 1 : 32;
+  float sum = val;
+  const int longest = __reduce_max_sync(0xffffffffu, __popc(mask));
+  for (int span = 1; span < longest; span <<= 1) {
+    const int src = next < 32 ? next : lane;
+    const float v = __shfl_sync(0xffffffffu, sum, src);
+    const int after = __shfl_sync(0xffffffffu, next, src);
+    if (next < 32) {
+      sum = __fadd_rn(sum, v);
+      next = after;
+    }
+  }
+  return sum;
+}
+
 }  // namespace tile
 }  // namespace ht
