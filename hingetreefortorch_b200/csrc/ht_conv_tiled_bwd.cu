@@ -16,6 +16,13 @@
 // contiguous; they arrive by bulk async copies on mbarriers, double buffered, like the forward's.
 // One traversal serves all three gradients (the reference runs three kernels per (sample, input
 // channel), each repeating it, hingetree_conv_gpu.cu:545-606).
+//
+// For trees of depth <= 7 the shared bins are the slow part (a few bins collect most terms, and a
+// float atomic on shared memory is a compare-and-swap loop), so there the parameter gradients come
+// from a second kernel further down (one tree per warp, bin columns owned by lanes) and this
+// kernel is launched for the image gradient only.  A fused form of the two with 16 warps per CTA
+// (both kinds of lane-owned arrays need the shared memory of a whole SM) was measured slower than
+// the pair: half the warps hide too little of the traversal's latency.
 #include "ht_conv_tiled.cuh"
 #include "ht_tile_common.cuh"
 

@@ -324,13 +324,11 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
   a.S = plan.S;
   a.G = plan.G;
   a.per_warp = plan.per_warp;
-  // With few sample tiles the tree groups are split among CTAs (grid.y) until the machine is filled
-  // about twice over; every split re-stages the feature tile, which is cheap next to the walk.
+  // With few sample tiles the tree groups are split among CTAs (grid.y) so that the SMs are busy in
+  // every round; every split re-stages the feature tile, which is cheap next to the walk.
   const int64_t tiles = (p->B + plan.S - 1) / plan.S;
   const int64_t groups = (p->T + plan.G - 1) / plan.G;
-  int64_t splits = 1;
-  if (tiles < 2 * 148) splits = std::min<int64_t>(groups, (2 * 148 + tiles - 1) / tiles);
-  const dim3 grid((unsigned)tiles, (unsigned)std::max<int64_t>(splits, 1));
+  const dim3 grid((unsigned)tiles, (unsigned)choose_splits(tiles, groups));
   return p->kind == TREE ? launch_kind<TREE>(p->depth, plan, a, grid, stream)
                          : launch_kind<FERN>(p->depth, plan, a, grid, stream);
 }

@@ -510,9 +510,7 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
   // a small batch gives too few sample tiles for 148 SMs: share the tree groups between CTAs
   const int64_t tiles = (p->B + plan.S - 1) / plan.S;
   const int64_t groups = (p->T + plan.G - 1) / plan.G;
-  int64_t splits = 1;
-  if (tiles < 2 * 148) splits = std::min<int64_t>(groups, (2 * 148 + tiles - 1) / tiles);
-  const dim3 grid((unsigned)tiles, (unsigned)std::max<int64_t>(splits, 1));
+  const dim3 grid((unsigned)tiles, (unsigned)choose_splits(tiles, groups));
   const int rc = p->kind == TREE ? launch_kind<TREE>(p->depth, plan, a, grid, stream)
                                  : launch_kind<FERN>(p->depth, plan, a, grid, stream);
   if (rc != HT_OK || eval_records == nullptr) return rc;

@@ -18,6 +18,25 @@ constexpr uint32_t kMaxSpins = 1u << 22;
 
 __host__ __device__ constexpr uint32_t round16(uint32_t v) { return (v + 15u) & ~15u; }
 
+// Into how many CTAs to split the tree groups of one sample tile (each split stages the tile's
+// features again, charged here at 3 % of a CTA's work): the count that minimises the number of
+// rounds the 148 SMs need, in units of a whole tile's work.  One split when the tiles alone fill
+// the machine evenly enough.
+inline int choose_splits(int64_t tiles, int64_t max_splits) {
+  constexpr int64_t kSMs = 148;
+  int best = 1;
+  double best_cost = 0.0;
+  for (int64_t s = 1; s <= max_splits && s <= 16; ++s) {
+    const double rounds = (double)((tiles * s + kSMs - 1) / kSMs);
+    const double cost = rounds / (double)s * (1.0 + 0.03 * (double)(s - 1));
+    if (s == 1 || cost < best_cost * 0.999) {
+      best = (int)s;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
 // Byte layout of one tree record; the same arithmetic runs on the host (plan) and in the kernel.
 struct RecordLayout {
   uint32_t thr, ord, w, bytes;
