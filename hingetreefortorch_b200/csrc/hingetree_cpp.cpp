@@ -448,7 +448,7 @@ torch::Tensor forest_speedtest(int kind, torch::Tensor x, bool deterministic) {
 
 [[noreturn]] void not_in_this_build(const char *what) {
   bad_runtime(std::string("Error: ") + what +
-              " is a one-time CPU initialisation outside the evaluation path and is not part of this build.");
+              " (randomised tree learning on the CPU, run once before training) is not part of this build.");
 }
 
 }  // namespace
@@ -484,8 +484,8 @@ using namespace htx;
     return forest_marginmap(KIND, x, t, o, w);                                                                      \
   });                                                                                                               \
   m.def(prefix "_speedtest", [](torch::Tensor x, bool det) { return forest_speedtest(KIND, x, det); });             \
-  m.def(prefix "_init_medians", [](torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor) -> bool {            \
-    not_in_this_build(prefix "_init_medians");                                                                      \
+  m.def(prefix "_init_medians", [](torch::Tensor x, torch::Tensor t, torch::Tensor o, torch::Tensor w) {            \
+    return init_medians(KIND == HT_KIND_FERN ? InitFamily::Fern : InitFamily::Tree, x, t, o, w);                    \
   });
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

@@ -12,10 +12,6 @@ namespace htx {
 
 namespace {
 
-[[noreturn]] void pending(const char *name) {
-  bad_runtime(std::string("Error: ") + name + " is not implemented in this build yet.");
-}
-
 // Shared validation of the fusion / fused-linear families (reference: hingetree_fusion.cpp:41-75,
 // 306-366; hingetree_fused_linear.cpp:75-100, 414-440, 769-860, 956-1050).
 struct FamilyCall {
@@ -617,8 +613,8 @@ void bind_more_ops(pybind11::module_ &m) {
         });
   m.def("trie_forward", &trie_forward, "Hinge trie forward.");
   m.def("trie_backward", &trie_backward, "Hinge trie backward.");
-  m.def("trie_init_medians", [](torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor) -> bool {
-    pending("trie_init_medians (a one-time CPU initialisation outside the evaluation path)");
+  m.def("trie_init_medians", [](torch::Tensor x, torch::Tensor t, torch::Tensor o, torch::Tensor w) {
+    return init_medians(InitFamily::Trie, x, t, o, w);
   });
 }
 

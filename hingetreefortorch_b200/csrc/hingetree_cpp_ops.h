@@ -49,4 +49,9 @@ struct ForestCall {
 // Registers the convolution, fused-linear, fusion, sparse, trie and contract/expand operators.
 void bind_more_ops(pybind11::module_ &m);
 
+// Median initialisation of the thresholds (CPU tensors, in place); false when the shapes or the
+// feature indices do not describe a forest over the data.
+enum class InitFamily { Tree, Fern, Trie };
+bool init_medians(InitFamily family, torch::Tensor x, torch::Tensor thr, torch::Tensor ord, torch::Tensor w);
+
 }  // namespace htx

@@ -100,6 +100,7 @@ def main():
     np.savez_compressed(os.path.join(HERE, "forest.npz"), **out)
     print("wrote forest.npz with", len(out), "arrays")
     families(ref)
+    init_vectors(ref)
 
 
 LINEAR_CASES = [
@@ -207,6 +208,45 @@ def families(ref):
     out["trie_count"] = np.array(2)
     np.savez_compressed(os.path.join(HERE, "families.npz"), **out)
     print("wrote families.npz with", len(out), "arrays")
+
+
+INIT_CASES = [
+    # family, B, C, inner, T, depth, quantised (ties), dtype
+    ("tree", 37, 5, (), 4, 3, False, torch.float32),
+    ("tree", 6, 4, (3,), 3, 4, False, torch.float32),   # fewer samples than vertices: some are never reached
+    ("tree", 40, 3, (), 3, 3, True, torch.float32),     # many equal values
+    ("tree", 1, 3, (), 2, 2, False, torch.float32),
+    ("tree", 2, 3, (), 2, 2, False, torch.float32),
+    ("tree", 19, 4, (2,), 2, 3, False, torch.float64),
+    ("fern", 21, 6, (), 5, 4, False, torch.float32),
+    ("fern", 8, 3, (2, 2), 3, 3, True, torch.float32),
+    ("trie", 25, 5, (), 3, 3, False, torch.float32),
+    ("trie", 12, 4, (2,), 2, 2, True, torch.float32),
+]
+
+
+def init_vectors(ref):
+    """Median initialisation of thresholds (tree, fern, trie) -> init.npz."""
+    out = {}
+    for idx, (family, B, C, inner, T, depth, quantised, dtype) in enumerate(INIT_CASES):
+        gen = torch.Generator().manual_seed(700 + idx)
+        N = depth if family == "fern" else 2 ** depth - 1
+        x = torch.randn((B, C) + inner, generator=gen).to(dtype)
+        if quantised:
+            x = torch.round(x * 2) / 2
+        thr = (torch.rand((T, N), generator=gen) * 6 - 3).to(dtype)
+        ord_ = torch.randint(0, C, (T, N), generator=gen)
+        w = torch.zeros((T, N if family == "trie" else 2 ** depth), dtype=dtype)
+        after = thr.clone()
+        ok = getattr(ref, family + "_init_medians")(x, after, ord_, w)
+        p = "init%02d_" % idx
+        out[p + "family"] = np.array(family)
+        for name, t in [("x", x), ("thr", thr), ("ord", ord_), ("w", w), ("after", after)]:
+            out[p + name] = t.numpy()
+        out[p + "ok"] = np.array(bool(ok))
+    out["count"] = np.array(len(INIT_CASES))
+    np.savez_compressed(os.path.join(HERE, "init.npz"), **out)
+    print("wrote init.npz with", len(out), "arrays")
 
 
 if __name__ == "__main__":

@@ -98,3 +98,37 @@ def test_function_layer_names():
                  "HingeTrie", "contract", "expand", "Contract", "Expand"]:
         assert hasattr(F, name), name
     assert issubclass(F.SparseHingeTree, F.HingeTree) and issubclass(F.HingeTreeFusedLinear, F.HingeTree)
+
+
+def test_median_initialisation_matches_reference():
+    """init_medians (CPU tensors, in place) against thresholds produced by the unmodified reference, bit for bit."""
+    import os
+    golden = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "init.npz"))
+    for idx in range(int(golden["count"])):
+        p = "init%02d_" % idx
+        family = str(golden[p + "family"])
+        x, thr, ord_, w = [torch.from_numpy(golden[p + k].copy()) for k in ("x", "thr", "ord", "w")]
+        ok = getattr(hingetree_cpp, family + "_init_medians")(x, thr, ord_, w)
+        assert ok == bool(golden[p + "ok"])
+        assert np.array_equal(thr.numpy(), golden[p + "after"]), (idx, family)
+
+
+def test_median_initialisation_screens_like_the_reference():
+    x = torch.randn(9, 4)
+    thr, ord_, w = torch.zeros(2, 7), torch.randint(0, 4, (2, 7)), torch.zeros(2, 8)
+    before = thr.clone()
+    bad = ord_.clone()
+    bad[1, 3] = 4                                    # feature index beyond the data: False, nothing written
+    assert hingetree_cpp.tree_init_medians(x, thr, bad, w) is False and torch.equal(thr, before)
+    assert hingetree_cpp.tree_init_medians(x, torch.zeros(2, 6), ord_[:, :6].contiguous(), w) is False
+    with pytest.raises(ValueError):
+        hingetree_cpp.tree_init_medians(x.double(), thr, ord_, w)
+    with pytest.raises(ValueError):
+        hingetree_cpp.fern_init_medians(x, thr, ord_.int(), w)
+    forest = R.RandomHingeForest(4, 3, 3)
+    assert forest.init_medians(x) is True
+    root = forest.ordinals[:, 0]
+    medians = torch.stack([x[:, c].sort(descending=True).values[9 // 2] for c in root.tolist()])
+    assert torch.equal(forest.thresholds.data[:, 0], medians)
+    with pytest.raises(RuntimeError):                  # randomised tree learning is not part of this build
+        hingetree_cpp.tree_init_greedy(x, torch.zeros(9), thr, ord_, w)
