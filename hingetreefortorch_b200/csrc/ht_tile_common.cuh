@@ -19,16 +19,17 @@ constexpr uint32_t kMaxSpins = 1u << 22;
 __host__ __device__ constexpr uint32_t round16(uint32_t v) { return (v + 15u) & ~15u; }
 
 // Into how many CTAs to split the tree groups of one sample tile (each split stages the tile's
-// features again, charged here at 3 % of a CTA's work): the count that minimises the number of
-// rounds the 148 SMs need, in units of a whole tile's work.  One split when the tiles alone fill
-// the machine evenly enough.
+// features again, charged here at 6 % of a whole tile's work — 256 tiles of the 1024-tree benchmark
+// forest ran 368 us unsplit, 390 us in 2 and 384 us in 4 splits): the count that minimises the
+// number of rounds the 148 SMs need, in units of a whole tile's work.  One split when the tiles
+// alone fill the machine evenly enough.
 inline int choose_splits(int64_t tiles, int64_t max_splits) {
   constexpr int64_t kSMs = 148;
   int best = 1;
   double best_cost = 0.0;
   for (int64_t s = 1; s <= max_splits && s <= 16; ++s) {
     const double rounds = (double)((tiles * s + kSMs - 1) / kSMs);
-    const double cost = rounds / (double)s * (1.0 + 0.03 * (double)(s - 1));
+    const double cost = rounds * (1.0 / (double)s + 0.06);  // a CTA: its share of the walk + staging
     if (s == 1 || cost < best_cost * 0.999) {
       best = (int)s;
       best_cost = cost;
