@@ -102,10 +102,6 @@ struct ConvBwdArgs {
   RecordMap map;
 };
 
-__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
-  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-
 template <int KIND, int DEPTH, typename OrdT>
 __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];

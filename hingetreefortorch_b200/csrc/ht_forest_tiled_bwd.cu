@@ -367,6 +367,82 @@ __global__ void __launch_bounds__(512) reduce_parameter_records_kernel(EvalRecor
   }
 }
 
+// Default mode, when the bins fit several times into shared memory: every warp keeps `columns`
+// copies of the tree's bins, [bin][column]; a lane adds its terms into column (lane % columns) with
+// plain loads and stores, the 32 / columns lanes that share a column taking turns.  No lane has to
+// find out which other lanes hit the same bin (a match.any per gradient per chunk bounds the kernel
+// above), and the chains of dependent updates of the hot bins are `columns` times shorter.  The
+// warps' columns are summed in a fixed order at the end: reproducible, another association.
+template <int CHUNKS>
+__global__ void __launch_bounds__(512, 1) reduce_parameter_records_columns_kernel(EvalRecords r, int64_t B, int64_t T,
+                                                                                  int64_t N, int64_t L, int columns,
+                                                                                  float *gthr, float *gw) {
+  extern __shared__ float all_bins[];  // [warp][bin][column]
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5;
+  const unsigned lane = threadIdx.x & 31u;
+  const int bins_per_tree = (int)(N + L);
+  const int64_t j = blockIdx.x;
+  for (int t = threadIdx.x; t < warps * bins_per_tree * columns; t += blockDim.x) all_bins[t] = 0.0f;
+  __syncthreads();
+  const uint32_t my_column = smem_addr(all_bins) + (uint32_t)(warp * bins_per_tree * columns + (int)(lane % columns)) * 4u;
+  const uint32_t bin_bytes = (uint32_t)columns * 4u;
+  const int turns = 32 / columns, my_turn = (int)lane / columns;
+
+  const int64_t stride = (int64_t)warps * 32 * CHUNKS;
+  float a[CHUNKS], b[CHUNKS], na[CHUNKS], nb[CHUNKS];
+  uint32_t wh[CHUNKS], nwh[CHUNKS];
+  auto fetch = [&](int64_t i0, float (&fa)[CHUNKS], float (&fb)[CHUNKS], uint32_t (&fw)[CHUNKS]) {
+    const int64_t first = record_index(i0, j, T) + lane;  // i0 is a multiple of 32 * CHUNKS, which divides 256
+#pragma unroll
+    for (int u = 0; u < CHUNKS; ++u) {
+      const bool valid = i0 + 32 * u + lane < B;
+      fa[u] = valid ? __ldcs(r.dx + first + 32 * u) : 0.0f;  // an absent sample adds zeros to bin 0
+      fb[u] = valid ? __ldcs(r.dw + first + 32 * u) : 0.0f;
+      fw[u] = valid ? __ldcs(r.where + first + 32 * u) : 1u;
+    }
+  };
+  int64_t i0 = (int64_t)warp * 32 * CHUNKS;
+  if (i0 < B) fetch(i0, a, b, wh);
+  for (; i0 < B; i0 += stride) {
+    if (i0 + stride < B) fetch(i0 + stride, na, nb, nwh);
+    uint32_t at_thr[CHUNKS], at_w[CHUNKS];
+#pragma unroll
+    for (int u = 0; u < CHUNKS; ++u) {
+      at_thr[u] = my_column + ((wh[u] & 0xffffu) - 1u) * bin_bytes;
+      at_w[u] = my_column + ((uint32_t)N + (wh[u] >> 16)) * bin_bytes;
+    }
+    for (int turn = 0; turn < turns; ++turn) {
+      if (turn == my_turn) {
+#pragma unroll
+        for (int u = 0; u < CHUNKS; ++u) {
+          // the two bins are different words: both updates are in flight together
+          const float old_thr = lds_f32(at_thr[u]), old_w = lds_f32(at_w[u]);
+          if (gthr != nullptr) sts_f32(at_thr[u], __fadd_rn(old_thr, -a[u]));
+          if (gw != nullptr) sts_f32(at_w[u], __fadd_rn(old_w, b[u]));
+        }
+      }
+      __syncwarp();
+    }
+#pragma unroll
+    for (int u = 0; u < CHUNKS; ++u) {
+      a[u] = na[u];
+      b[u] = nb[u];
+      wh[u] = nwh[u];
+    }
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < bins_per_tree; t += blockDim.x) {
+    float sum = 0.0f;
+    for (int wi = 0; wi < warps; ++wi)
+      for (int c = 0; c < columns; ++c) sum = __fadd_rn(sum, all_bins[((size_t)wi * bins_per_tree + t) * columns + c]);
+    if (t < N) {
+      if (gthr != nullptr) gthr[j * N + t] = sum;
+    } else if (gw != nullptr) {
+      gw[j * L + (t - N)] = sum;
+    }
+  }
+}
+
 // x gradient: one thread per sample walks the trees in ascending order and adds into its private
 // column of a shared-memory tile gx[c][s]; the tile leaves with plain stores.
 __global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, const int32_t *__restrict__ ord, int64_t B,
@@ -529,9 +605,21 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
                                        (int)kSmemBudget));
       reduce_parameter_records_kernel<true><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, p->B, p->T, N, L, gthr, gw);
     } else {
-      HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)kSmemBudget));
-      reduce_parameter_records_kernel<false><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, p->B, p->T, N, L, gthr, gw);
+      // copies of the bins per warp (a power of two, at most one per lane) that 16 warps can hold
+      int columns = 32;
+      while (columns > 1 && (size_t)16 * (N + L) * columns * 4 > 200 * 1024) columns >>= 1;
+      if (warps == 16 && columns >= 4) {
+        const size_t column_smem = (size_t)16 * (N + L) * columns * 4;
+        HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_columns_kernel<8>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+        reduce_parameter_records_columns_kernel<8><<<(unsigned)p->T, 512, column_smem, stream>>>(a.evals, p->B, p->T, N, L,
+                                                                                                 columns, gthr, gw);
+      } else {
+        HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+        reduce_parameter_records_kernel<false><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, p->B, p->T, N, L, gthr,
+                                                                                            gw);
+      }
     }
     HT_CHECK_LAUNCH();
   }
