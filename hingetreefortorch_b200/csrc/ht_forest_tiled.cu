@@ -154,6 +154,17 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
   const int tid_in_group = slot * 32 + lane;
   constexpr uint32_t kL = 1u << DEPTH;
   bool poisoned = false;  // a bounded wait ran out: keep the barriers matched, stop waiting
+  // Output of a full group when its 32 x (G*M/4) 16-byte pieces are one per thread of the sample
+  // group (the usual case): which piece is this thread's, worked out once
+  const int full_groups = (int)(a.T / G), tail_trees = (int)(a.T - (int64_t)full_groups * G);  // a.T < 2^31 * G
+  const int full_quads = (G * M) >> 2;
+  const int64_t row_pitch = a.T * M;
+  const bool one_piece = ((G * M) & 3) == 0 && (row_pitch & 3) == 0 && 32 * full_quads == group_threads;
+  const int piece_row = one_piece ? tid_in_group / full_quads : 0;
+  const int piece_quad = one_piece ? tid_in_group - piece_row * full_quads : 0;
+  const int64_t piece_sample = row0 + sample_group * 32 + piece_row;
+  float *piece_dst = a.out + piece_sample * row_pitch + 4 * piece_quad;
+  const float *piece_src = stage + piece_row * row_floats + 4 * piece_quad;
 
   for (int it = 0; it < num_groups; ++it) {
     const int group = group0 + it;
@@ -161,7 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
       poisoned = true;
       if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
     }
-    const int in_group = (int)min((int64_t)G, a.T - (int64_t)group * G);
+    const int in_group = group < full_groups ? G : tail_trees;
     const uint32_t base_addr = params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes;
     const int t_first = slot * per_warp;  // this warp's consecutive trees inside the group
     float result[4] = {0.f, 0.f, 0.f, 0.f};
@@ -171,7 +182,8 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
       if (per_warp == 4) {
         uint32_t rec[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) rec[u] = base_addr + (uint32_t)min(t_first + u, in_group - 1) * lay.bytes;
+        for (int u = 0; u < 4; ++u)
+          rec[u] = base_addr + (uint32_t)(in_group == G ? t_first + u : min(t_first + u, in_group - 1)) * lay.bytes;
         walk<KIND, DEPTH, OrdT, 4, WREC>(rec, xl_addr, x_stride, result, path);
       } else if (per_warp == 2) {
         uint32_t rec[2], p2[2];
@@ -224,8 +236,11 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
     // the sample group's warps write its [32 x in_group*M] block of results as row segments
     const int64_t row_base = row0 + sample_group * 32;
     const int width = in_group * M;
-    const int64_t row_pitch = a.T * M, first_col = col0 * M;
-    if ((row_pitch & 3) == 0 && (first_col & 3) == 0 && (width & 3) == 0) {
+    const int64_t first_col = col0 * M;
+    if (one_piece && in_group == G) {
+      if (piece_sample < a.B)
+        *reinterpret_cast<float4 *>(piece_dst + first_col) = make_float4(piece_src[0], piece_src[1], piece_src[2], piece_src[3]);
+    } else if ((row_pitch & 3) == 0 && (first_col & 3) == 0 && (width & 3) == 0) {
       const int quads = width >> 2;
       for (int idx = tid_in_group; idx < 32 * quads; idx += group_threads) {
         const int s = idx / quads, q = idx - s * quads;
