@@ -165,6 +165,25 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
   const int64_t piece_sample = row0 + sample_group * 32 + piece_row;
   float *piece_dst = a.out + piece_sample * row_pitch + 4 * piece_quad;
   const float *piece_src = stage + piece_row * row_floats + 4 * piece_quad;
+  // Full groups with 4 trees per warp and the weights in the records take a body without the
+  // bookkeeping of short groups, other tree counts and several outputs per leaf.
+  const bool streamlined = WREC && one_piece && per_warp == 4;
+  const uint32_t warp_records = (uint32_t)(slot * per_warp) * lay.bytes;
+  float *stage_mine = stage + lane * row_floats + slot * per_warp;
+
+  // This warp no longer reads parameter buffer (it & 1).  The last warp to say so refills it.
+  auto done_with_buffer = [&](int it) {
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      const uint32_t before = atomicAdd(&finished[it & 1], 1u);
+      if (before == kWarps - 1) {
+        atomicExch(&finished[it & 1], 0u);
+        __threadfence_block();
+        if (it + 2 < num_groups) issue(it + 2);
+      }
+    }
+  };
 
   for (int it = 0; it < num_groups; ++it) {
     const int group = group0 + it;
@@ -174,6 +193,22 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
     }
     const int in_group = group < full_groups ? G : tail_trees;
     const uint32_t base_addr = params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes;
+    if (streamlined && in_group == G) {
+      uint32_t rec[4], unused[4];
+      float result[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) rec[u] = base_addr + warp_records + (uint32_t)u * lay.bytes;
+      walk<KIND, DEPTH, OrdT, 4, WREC>(rec, xl_addr, x_stride, result, unused);
+      done_with_buffer(it);
+      named_barrier(1 + sample_group, group_threads);  // previous group's rows have left the staging area
+#pragma unroll
+      for (int u = 0; u < 4; ++u) stage_mine[u] = result[u];
+      named_barrier(1 + sample_group, group_threads);  // staging area complete
+      if (piece_sample < a.B)
+        *reinterpret_cast<float4 *>(piece_dst + (int64_t)group * G) =
+            make_float4(piece_src[0], piece_src[1], piece_src[2], piece_src[3]);
+      continue;
+    }
     const int t_first = slot * per_warp;  // this warp's consecutive trees inside the group
     float result[4] = {0.f, 0.f, 0.f, 0.f};
     uint32_t path[4] = {kL, kL, kL, kL};
@@ -203,17 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
         path[0] = p1[0];
       }
     }
-    // This warp no longer reads the parameter buffer.  The last warp to get here refills it.
-    __syncwarp();
-    if (lane == 0) {
-      __threadfence_block();
-      const uint32_t before = atomicAdd(&finished[it & 1], 1u);
-      if (before == kWarps - 1) {
-        atomicExch(&finished[it & 1], 0u);
-        __threadfence_block();
-        if (it + 2 < num_groups) issue(it + 2);
-      }
-    }
+    done_with_buffer(it);
 
     const int64_t col0 = (int64_t)group * G;
     named_barrier(1 + sample_group, group_threads);  // previous group's rows have left the staging area
