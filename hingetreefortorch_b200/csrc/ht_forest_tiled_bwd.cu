@@ -153,11 +153,13 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
   const uint32_t xl_addr = smem_addr(xs + my_sample);
   const uint32_t x_stride = (uint32_t)S * 4u;
   const int64_t my_row = row0 + my_sample;
+  const int64_t my_records = record_index(my_row, 0, a.T);  // tree j's record of this sample: + j * kRecordBlock
+  const int full_groups = (int)(a.T / G), tail_trees = (int)(a.T - (int64_t)full_groups * G);
   bool poisoned = false;
 
   for (int it = 0; it < num_groups; ++it) {
     const int group = group0 + it;
-    const int in_group = (int)min((int64_t)G, a.T - (int64_t)group * G);
+    const int in_group = group < full_groups ? G : tail_trees;
     const int64_t col0 = (int64_t)group * G;
 
     // upstream gradients of this lane's sample for the warp's trees, requested before the walk
@@ -195,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
         const float dx = wk.nm < 0.0f ? wg : (wk.nm > 0.0f ? -wg : __fmul_rn(0.0f, wg));
         if (RECORDS) {
           const uint32_t key = __brev(wk.path - kL) >> (32 - DEPTH);
-          const int64_t at = record_index(my_row, j, a.T);
+          const int64_t at = my_records + j * kRecordBlock;
           a.evals.dx[at] = dx;
           a.evals.dw[at] = __fmul_rn(fabsf(wk.nm), gv);
           a.evals.where[at] = wk.v | (key << 16);
