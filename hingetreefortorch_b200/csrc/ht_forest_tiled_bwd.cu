@@ -156,11 +156,62 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
   const int64_t my_records = record_index(my_row, 0, a.T);  // tree j's record of this sample: + j * kRecordBlock
   const int full_groups = (int)(a.T / G), tail_trees = (int)(a.T - (int64_t)full_groups * G);
   bool poisoned = false;
+  // Full groups with 4 trees per warp on the record path take a body without the bookkeeping of
+  // short groups and other tree counts.
+  const bool streamlined = RECORDS && per_warp == 4 && (a.T & 3) == 0;
+  const uint32_t warp_records = (uint32_t)(slot * per_warp) * lay.bytes;
+  const float *g_mine = a.g + my_row * a.T + slot * per_warp;
+  const int64_t records_mine = my_records + (int64_t)(slot * per_warp) * kRecordBlock;
+
+  // This warp no longer reads parameter buffer (it & 1).  The last warp to say so refills it.
+  auto done_with_buffer = [&](int it) {
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      const uint32_t before = atomicAdd(&finished[it & 1], 1u);
+      if (before == kWarps - 1) {
+        atomicExch(&finished[it & 1], 0u);
+        __threadfence_block();
+        if (it + 2 < num_groups) issue(it + 2);
+      }
+    }
+  };
 
   for (int it = 0; it < num_groups; ++it) {
     const int group = group0 + it;
     const int in_group = group < full_groups ? G : tail_trees;
     const int64_t col0 = (int64_t)group * G;
+    if (streamlined && in_group == G) {
+      float4 gq = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row_valid) gq = __ldg(reinterpret_cast<const float4 *>(g_mine + col0));  // requested before the walk
+      if (!poisoned && !mbar_wait(&full[it & 1], (uint32_t)((it >> 1) & 1))) {
+        poisoned = true;
+        if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
+      }
+      if (!poisoned) {
+        const uint32_t base_addr = params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes + warp_records;
+        uint32_t rec[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) rec[u] = base_addr + (uint32_t)u * lay.bytes;
+        Walked wk[4];
+        walk_full<KIND, DEPTH, OrdT, 4>(rec, xl_addr, x_stride, wk);
+        const float gval[4] = {gq.x, gq.y, gq.z, gq.w};
+        const int64_t at = records_mine + col0 * kRecordBlock;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float wg = __fmul_rn(lds_f32(rec[u] + 4u * wk[u].path + (lay.w - 4u * kL)), gval[u]);
+          const float dx = wk[u].nm < 0.0f ? wg : (wk[u].nm > 0.0f ? -wg : __fmul_rn(0.0f, wg));
+          const uint32_t key = __brev(wk[u].path - kL) >> (32 - DEPTH);
+          if (row_valid) {
+            __stcs(a.evals.dx + at + u * kRecordBlock, dx);
+            __stcs(a.evals.dw + at + u * kRecordBlock, __fmul_rn(fabsf(wk[u].nm), gval[u]));
+            __stcs(a.evals.where + at + u * kRecordBlock, wk[u].v | (key << 16));
+          }
+        }
+      }
+      done_with_buffer(it);
+      continue;
+    }
 
     // upstream gradients of this lane's sample for the warp's trees, requested before the walk
     const int t_first = slot * per_warp;
@@ -236,18 +287,8 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
         scatter(wk[0], rec[0], 0);
       }
     }
-    __syncwarp();
-    if (lane == 0) {
-      __threadfence_block();
-      const uint32_t before = atomicAdd(&finished[it & 1], 1u);
-      if (before == kWarps - 1) {
-        atomicExch(&finished[it & 1], 0u);
-        __threadfence_block();
-        if (it + 2 < num_groups) issue(it + 2);
-      }
-    }
+    done_with_buffer(it);
   }
-
 }
 
 template <typename Kernel>
