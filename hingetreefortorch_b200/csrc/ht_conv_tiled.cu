@@ -48,7 +48,8 @@ bool make_plan(const ConvTileProblem &p, ConvTilePlan &plan) {
     plan.patch_w = shape.w;
     if (shape.far > 65535) continue;
     plan.ord_bytes = shape.far <= 255 ? 1 : 2;
-    plan.rec = record_layout(p.kind, p.depth, (uint32_t)plan.ord_bytes);
+    plan.rec = record_layout(p.kind, p.depth, (uint32_t)plan.ord_bytes, true,
+                             paired_ordinals(p.kind, p.depth, (uint32_t)plan.ord_bytes));
     const size_t patches = (size_t)p.Ci * plan.patch_h * plan.patch_w * 4;
     const int JB = (kWarps / TY) * 4;
     for (int CC = 16; CC >= 1; CC >>= 1) {
@@ -73,7 +74,8 @@ struct ConvTileArgs {
 template <int KIND, int DEPTH, typename OrdT>
 __global__ void __launch_bounds__(kThreads, 1) conv_forward_tiled_kernel(ConvTileArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+  constexpr RecordLayout lay =
+      record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), true, paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT)));
   const int TY = a.TY, CC = a.CC;
   const int slots = kWarps / TY;
   const int JB = slots * 4;  // output channels per parameter group

@@ -54,7 +54,8 @@ bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
   if (p->C > 65536 || p->depth > 12) return false;
   if (p->B * p->T < 32 * 1024) return false;  // too small to fill the machine with sample tiles
   plan.ord_bytes = p->C <= 256 ? 1 : 2;
-  plan.rec = record_layout(p->kind, p->depth, (uint32_t)plan.ord_bytes, p->M == 1);
+  plan.rec = record_layout(p->kind, p->depth, (uint32_t)plan.ord_bytes, p->M == 1,
+                           paired_ordinals(p->kind, p->depth, (uint32_t)plan.ord_bytes));
   for (int S = 256; S >= 32; S >>= 1) {
     const int slots = kWarps / (S / 32);
     for (int per_warp = 4; per_warp >= 1; per_warp >>= 1) {
@@ -82,7 +83,8 @@ struct TiledArgs {
 template <int KIND, int DEPTH, typename OrdT, bool WREC>
 __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(TiledArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC);
+  constexpr RecordLayout lay =
+      record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC, paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT)));
   const int S = a.S, G = a.G, C = a.C;
   const int M = WREC ? 1 : a.M;
   const int row_floats = G * M + 1;  // staging row of one sample: G trees x M outputs, padded

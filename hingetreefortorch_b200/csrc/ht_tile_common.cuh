@@ -41,16 +41,30 @@ inline int choose_splits(int64_t tiles, int64_t max_splits) {
 // Byte layout of one tree record; the same arithmetic runs on the host (plan) and in the kernel.
 struct RecordLayout {
   uint32_t thr, ord, w, bytes;
+  bool paired;  // feature indices stored as words {own, left child's, right child's} of the even-level vertices
 };
+
+// Trees with one-byte feature indices can store them so that one 4-byte load serves two levels: a
+// word per vertex of every even level >= 2 holding its own index and its two children's (levels 0
+// and 1 come from the record's head).  Word of vertex v (1-based) of even level l: paired_first(l) + v - 2^l.
+__host__ __device__ constexpr bool paired_ordinals(int kind, int depth, uint32_t ord_size) {
+  return kind == TREE && ord_size == 1 && depth >= 3;
+}
+__host__ __device__ constexpr uint32_t paired_first(int level) { return ((1u << level) - 4u) / 3u; }
+__host__ __device__ constexpr uint32_t paired_words(int depth) {
+  const int top = ((depth - 1) / 2) * 2;  // the deepest even level
+  return paired_first(top) + (1u << top);
+}
 
 // with_weights: the record carries the leaf weights (one output per leaf); with several outputs
 // per leaf the weights stay in global memory and the record ends after the feature indices.
-__host__ __device__ constexpr RecordLayout record_layout(int kind, int depth, uint32_t ord_size, bool with_weights = true) {
+__host__ __device__ constexpr RecordLayout record_layout(int kind, int depth, uint32_t ord_size, bool with_weights = true,
+                                                        bool paired = false) {
   const uint32_t n = kind == FERN ? (uint32_t)depth : (1u << depth) - 1u;
   const uint32_t thr = kind == FERN ? 0u : (uint32_t)kHeadBytes;
   const uint32_t ord = thr + round16(4u * n);
-  const uint32_t w = ord + round16(ord_size * n);
-  return RecordLayout{thr, ord, w, with_weights ? round16(w + 4u * (1u << depth)) : w};
+  const uint32_t w = ord + round16(paired ? 4u * paired_words(depth) : ord_size * n);
+  return RecordLayout{thr, ord, w, with_weights ? round16(w + 4u * (1u << depth)) : w, paired};
 }
 
 __device__ __forceinline__ uint32_t bit_reverse(uint32_t v, int bits) { return __brev(v) >> (32 - bits); }
@@ -88,7 +102,16 @@ __global__ void repack_records_kernel(const float *__restrict__ thr, const int32
     t = t == 0.0f ? 0.0f : t;  // -0 becomes +0
     const uint32_t c = map.feature((uint32_t)ord[j * N + r]);
     reinterpret_cast<float *>(rec + lay.thr)[r] = t;
-    reinterpret_cast<OrdT *>(rec + lay.ord)[r] = (OrdT)c;
+    if (!lay.paired) {
+      reinterpret_cast<OrdT *>(rec + lay.ord)[r] = (OrdT)c;
+    } else if (r >= 3) {  // vertex v = r + 1 of level >= 2: byte 0 of its own word, or byte 1 / 2 of its parent's
+      const uint32_t v = (uint32_t)r + 1u;
+      const int level = 31 - __clz((int)v);
+      const uint32_t owner = (level & 1) ? v >> 1 : v;
+      const int owner_level = level & ~1;
+      const uint32_t word = paired_first(owner_level) + owner - (1u << owner_level);
+      rec[lay.ord + 4u * word + ((level & 1) ? 1u + (v & 1u) : 0u)] = (unsigned char)c;
+    }
     if (kind == TREE && r < 3) {  // root and its children again, for one broadcast load
       reinterpret_cast<float *>(rec)[r] = t;
       if (sizeof(OrdT) == 1) rec[12 + r] = (unsigned char)c;
@@ -152,6 +175,12 @@ __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
   asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
+__device__ __forceinline__ uint32_t lds_b32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
 __device__ __forceinline__ uint4 lds_b128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -178,7 +207,8 @@ __device__ __forceinline__ uint32_t pick(const uint4 &q, int i) {
 template <int KIND, int DEPTH, typename OrdT, int NT, bool WREC>
 __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr, uint32_t x_stride,
                                      float (&result)[NT], uint32_t (&path)[NT]) {
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC);
+  constexpr bool kPaired = paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC, kPaired);
   uint32_t v[NT];
   float best[NT], first[NT];
   if (KIND == FERN) {
@@ -211,9 +241,11 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
   } else {
     constexpr bool kHead = sizeof(OrdT) == 1;  // root + children in one 16-byte broadcast
     uint4 head[NT];
+    uint32_t family[NT];  // paired form: feature indices of an even-level vertex and its children
 #pragma unroll
     for (int u = 0; u < NT; ++u) {
       v[u] = 1u;
+      family[u] = 0u;
       if (kHead) head[u] = lds_b128(rec[u]);
     }
 #pragma unroll
@@ -228,6 +260,14 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
         } else if (kHead && l == 1) {
           thr = __uint_as_float((v[u] & 1u) ? head[u].z : head[u].y);
           c = __byte_perm(head[u].w, 0u, 0x4440u + (v[u] - 1u));
+        } else if (kPaired) {
+          thr = lds_f32(rec[u] + 4u * v[u] + (lay.thr - 4u));
+          if (l % 2 == 0) {
+            family[u] = lds_b32(rec[u] + 4u * v[u] + (lay.ord + 4u * paired_first(l) - 4u * (1u << l)));
+            c = family[u] & 0xffu;
+          } else {
+            c = __byte_perm(family[u], 0u, 0x4441u + (v[u] & 1u));  // byte 1 (left child) or 2 (right child)
+          }
         } else {
           thr = lds_f32(rec[u] + 4u * v[u] + (lay.thr - 4u));
           c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * v[u] + (lay.ord - (uint32_t)sizeof(OrdT)));
