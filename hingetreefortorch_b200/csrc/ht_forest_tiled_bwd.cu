@@ -29,12 +29,14 @@ struct BwdPlan {
   size_t smem;
 };
 
-bool make_bwd_plan(const ht_forest_problem *p, BwdPlan &plan) {
+// paired: the record path, whose kernels never look a feature index up by vertex, takes the paired form
+bool make_bwd_plan(const ht_forest_problem *p, BwdPlan &plan, bool paired = false) {
   if (p->K != 1 || p->M != 1) return false;
   if (p->C > 65536 || p->depth > 12) return false;
   if (p->B * p->T < 32 * 1024) return false;
   plan.ord_bytes = p->C <= 256 ? 1 : 2;
-  plan.rec = record_layout(p->kind, p->depth, (uint32_t)plan.ord_bytes);
+  plan.rec = record_layout(p->kind, p->depth, (uint32_t)plan.ord_bytes, true,
+                           paired && paired_ordinals(p->kind, p->depth, (uint32_t)plan.ord_bytes));
   for (int S = 256; S >= 32; S >>= 1) {
     const int slots = kWarps / (S / 32);
     for (int per_warp = 4; per_warp >= 1; per_warp >>= 1) {
@@ -85,7 +87,8 @@ struct BwdArgs {
 template <int KIND, int DEPTH, typename OrdT, bool RECORDS>
 __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+  constexpr bool kPaired = RECORDS && paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), true, kPaired);
   constexpr uint32_t kN = KIND == FERN ? DEPTH : (1u << DEPTH) - 1u;
   constexpr uint32_t kL = 1u << DEPTH;
   const int S = a.S, G = a.G, C = a.C;
@@ -194,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
 #pragma unroll
         for (int u = 0; u < 4; ++u) rec[u] = base_addr + (uint32_t)u * lay.bytes;
         Walked wk[4];
-        walk_full<KIND, DEPTH, OrdT, 4>(rec, xl_addr, x_stride, wk);
+        walk_full<KIND, DEPTH, OrdT, 4, kPaired>(rec, xl_addr, x_stride, wk);
         const float gval[4] = {gq.x, gq.y, gq.z, gq.w};
         const int64_t at = records_mine + col0 * kRecordBlock;
 #pragma unroll
@@ -269,7 +272,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
 #pragma unroll
         for (int u = 0; u < 4; ++u) rec[u] = base_addr + (uint32_t)min(t_first + u, in_group - 1) * lay.bytes;
         Walked wk[4];
-        walk_full<KIND, DEPTH, OrdT, 4>(rec, xl_addr, x_stride, wk);
+        walk_full<KIND, DEPTH, OrdT, 4, kPaired>(rec, xl_addr, x_stride, wk);
 #pragma unroll
         for (int u = 0; u < 4; ++u) scatter(wk[u], rec[u], u);
       } else if (per_warp == 2) {
@@ -277,13 +280,13 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
 #pragma unroll
         for (int u = 0; u < 2; ++u) rec[u] = base_addr + (uint32_t)min(t_first + u, in_group - 1) * lay.bytes;
         Walked wk[2];
-        walk_full<KIND, DEPTH, OrdT, 2>(rec, xl_addr, x_stride, wk);
+        walk_full<KIND, DEPTH, OrdT, 2, kPaired>(rec, xl_addr, x_stride, wk);
 #pragma unroll
         for (int u = 0; u < 2; ++u) scatter(wk[u], rec[u], u);
       } else {
         uint32_t rec[1] = {base_addr + (uint32_t)t_first * lay.bytes};
         Walked wk[1];
-        walk_full<KIND, DEPTH, OrdT, 1>(rec, xl_addr, x_stride, wk);
+        walk_full<KIND, DEPTH, OrdT, 1, kPaired>(rec, xl_addr, x_stride, wk);
         scatter(wk[0], rec[0], 0);
       }
     }
@@ -590,7 +593,7 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
                    const float *g, float *gx, float *gthr, float *gw, void *records, void *eval_records,
                    uint32_t *status_word, cudaStream_t stream) {
   BwdPlan plan;
-  if (!make_bwd_plan(p, plan)) return HT_ERR_UNSUPPORTED;
+  if (!make_bwd_plan(p, plan, eval_records != nullptr)) return HT_ERR_UNSUPPORTED;
   if (forward_tiled_workspace_bytes(p) == 0) return HT_ERR_UNSUPPORTED;  // the workspace holds no records otherwise
   if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(gx)) & 15u) != 0)
     return HT_ERR_UNSUPPORTED;

@@ -304,20 +304,45 @@ struct Walked {
 };
 
 // rec[u] and x_addr[u]: record and feature base (shared-memory addresses) of the u-th walk in flight.
-template <int KIND, int DEPTH, typename OrdT, int NT>
+// PAIRED: the records hold the feature indices in the paired form (see paired_ordinals).
+template <int KIND, int DEPTH, typename OrdT, int NT, bool PAIRED = false>
 __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], const uint32_t (&x_addr)[NT], uint32_t x_stride,
                                           Walked (&out)[NT]) {
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), true, PAIRED);
   uint32_t v[NT];
+  uint4 head[NT];
+  uint32_t family[NT];
 #pragma unroll
-  for (int u = 0; u < NT; ++u) v[u] = 1u;
+  for (int u = 0; u < NT; ++u) {
+    v[u] = 1u;
+    family[u] = 0u;
+    if (PAIRED) head[u] = lds_b128(rec[u]);
+  }
 #pragma unroll
   for (int l = 0; l < DEPTH; ++l) {
 #pragma unroll
     for (int u = 0; u < NT; ++u) {
       const uint32_t at = KIND == FERN ? (uint32_t)(l + 1) : v[u];
-      const float thr = lds_f32(rec[u] + 4u * at + (lay.thr - 4u));
-      const uint32_t c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * at + (lay.ord - (uint32_t)sizeof(OrdT)));
+      float thr;
+      uint32_t c;
+      if (PAIRED && l == 0) {
+        thr = __uint_as_float(head[u].x);
+        c = head[u].w & 0xffu;
+      } else if (PAIRED && l == 1) {
+        thr = __uint_as_float((at & 1u) ? head[u].z : head[u].y);
+        c = __byte_perm(head[u].w, 0u, 0x4440u + (at - 1u));
+      } else if (PAIRED) {
+        thr = lds_f32(rec[u] + 4u * at + (lay.thr - 4u));
+        if (l % 2 == 0) {
+          family[u] = lds_b32(rec[u] + 4u * at + (lay.ord + 4u * paired_first(l) - 4u * (1u << l)));
+          c = family[u] & 0xffu;
+        } else {
+          c = __byte_perm(family[u], 0u, 0x4441u + (at & 1u));
+        }
+      } else {
+        thr = lds_f32(rec[u] + 4u * at + (lay.thr - 4u));
+        c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * at + (lay.ord - (uint32_t)sizeof(OrdT)));
+      }
       const float nm = thr - lds_f32(c * x_stride + x_addr[u]);
       if (l == 0 || fabsf(nm) < fabsf(out[u].nm)) {
         out[u].nm = nm;
@@ -331,13 +356,13 @@ __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], const uint3
 }
 
 // The same with one feature base for all walks (several trees on one sample or position).
-template <int KIND, int DEPTH, typename OrdT, int NT>
+template <int KIND, int DEPTH, typename OrdT, int NT, bool PAIRED = false>
 __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], uint32_t xl_addr, uint32_t x_stride,
                                           Walked (&out)[NT]) {
   uint32_t x_addr[NT];
 #pragma unroll
   for (int u = 0; u < NT; ++u) x_addr[u] = xl_addr;
-  walk_full<KIND, DEPTH, OrdT, NT>(rec, x_addr, x_stride, out);
+  walk_full<KIND, DEPTH, OrdT, NT, PAIRED>(rec, x_addr, x_stride, out);
 }
 
 // Sum of `val` over the lanes of the warp whose `key` equals this lane's, delivered in the lowest
