@@ -51,10 +51,10 @@ WORKLOADS = {
 
 
 # DRAM bytes (read + write) of the tile kernel per input row of the c3 shape, from the committed
-# capture profiles/forest_forward_tiled_65536rows_ncu.md: (38 291 200 + 215 223 552) B / 65 536 rows.
+# capture profiles/forest_forward_tiled_65536rows_ncu.md: (38 455 040 + 214 589 952) B / 65 536 rows.
 # Traffic grows in proportion to the rows (every CTA handles 256 rows the same way), so the
 # full-size launch is that figure times its rows.
-C3_DRAM_BYTES_PER_ROW = (38291200 + 215223552) / 65536
+C3_DRAM_BYTES_PER_ROW = (38455040 + 214589952) / 65536
 
 
 def decisions(kind, depth):
