@@ -1,17 +1,21 @@
-// Shared-memory tile kernel for the forest backward on tabular input (K == 1, one output per leaf),
-// default (not fixed-order) mode.
+// Shared-memory tile kernels for the forest backward on tabular input (K == 1, one output per leaf).
 //
-// Same tiling as the forward tile kernel (ht_forest_tiled.cu): a CTA owns S consecutive samples,
-// keeps their features feature-major in shared memory and walks ALL trees, whose parameter
-// records stream in through bulk async copies; a warp walks 4 consecutive trees at once for its
-// 32 samples.  Each lane fetches the 4 upstream gradients g[i, j .. j+3] of its sample with one
-// 16-byte load issued before the walk, and scatters the three gradients with fire-and-forget
-// global reductions (red.global.add.f32): the rows of the x gradient are private to the CTA, the
-// threshold and leaf-weight bins are shared by all CTAs.  There is no block-wide barrier after
-// the feature tile has been staged.
-// One traversal serves all three gradients (the reference runs three kernels that each repeat it,
-// hingetree_gpu.cu:699-727).  The traversal keeps the signed margin and the deciding vertex, with
-// the reference's strict `<` so that the shallowest minimum wins.
+// forest_backward_tiled_kernel has the tiling of the forward tile kernel (ht_forest_tiled.cu): a CTA
+// owns S consecutive samples, keeps their features feature-major in shared memory and walks ALL
+// trees, whose parameter records stream in through bulk async copies; a warp walks 4 consecutive
+// trees at once for its 32 samples.  Each lane fetches the 4 upstream gradients g[i, j .. j+3] of its
+// sample with one 16-byte load issued before the walk.  One traversal serves all three gradients
+// (the reference runs three kernels that each repeat it, hingetree_gpu.cu:699-727); it keeps the
+// signed margin and the deciding vertex, with the reference's strict `<` so that the shallowest
+// minimum wins.  What happens to the terms depends on the workspace the caller gave:
+//   * with room for 12 bytes per evaluation (the record path, both modes): the kernel writes one
+//     record per evaluation and two reductions further down add the records in a fixed order —
+//     reduce_x_records_kernel for the x gradient, reduce_parameter_records_* for thresholds and
+//     leaf weights.  No floating-point atomics anywhere; in fixed-order mode the sums are the
+//     reference's sequential CPU sums bit for bit;
+//   * without it (default mode only): fire-and-forget global reductions (red.global.add.f32) from
+//     the traversal kernel itself.
+// There is no block-wide barrier after the feature tile has been staged.
 #include "ht_forest_tiled.cuh"
 #include "ht_tile_common.cuh"
 
@@ -100,7 +104,6 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const int groups_of_samples = S >> 5;
-  const int slots = kWarps / groups_of_samples;
   const int sample_group = warp % groups_of_samples;
   const int slot = warp / groups_of_samples;
   const int per_warp = a.per_warp;
@@ -314,9 +317,10 @@ int launch_depth(const BwdPlan &plan, const BwdArgs &a, dim3 grid, cudaStream_t 
 
 // ---- consumers of the evaluation records -----------------------------------------------------------
 //
-// Both consumers add the terms of every gradient element in exactly the order of the reference
-// CPU loops (samples ascending for the parameter bins, trees ascending for the x gradient), so
-// the record path is deterministic and, with one output per leaf, equal to those loops bit for bit.
+// The x-gradient consumer adds the terms of every element in the order of the reference CPU loop
+// (trees ascending), in both modes.  The parameter consumer does so in fixed-order mode (samples
+// ascending: equal to the reference CPU loops bit for bit); in default mode it adds them in another,
+// fixed association (reproducible from run to run, within rounding of the reference).
 
 // Runs f() on the valid lanes so that lanes sharing `key` execute in lane order.
 template <typename F>
