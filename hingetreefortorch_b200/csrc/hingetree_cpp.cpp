@@ -446,11 +446,6 @@ torch::Tensor forest_speedtest(int kind, torch::Tensor x, bool deterministic) {
   return timings;
 }
 
-[[noreturn]] void not_in_this_build(const char *what) {
-  bad_runtime(std::string("Error: ") + what +
-              " (randomised tree learning on the CPU, run once before training) is not part of this build.");
-}
-
 }  // namespace
 }  // namespace htx
 
@@ -492,9 +487,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a drop-in for HingeTreeForTorch's hingetree_cpp (CUDA tensors only)";
   HT_BIND_KIND("tree", HT_KIND_TREE)
   HT_BIND_KIND("fern", HT_KIND_FERN)
-  m.def("tree_init_greedy", [](torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor) -> bool {
-    not_in_this_build("tree_init_greedy");
-  });
+  m.def("tree_init_greedy", &init_greedy,
+        "Initialize thresholds and ordinals by random decision tree learning on class labels (CPU only).");
+  m.def("seed_init", &seed_init, "Seed the generator tree_init_greedy draws from.");
   m.def("set_ordinal_check", &set_ordinal_check,
         "When to read the ordinal range flag back from the device: 'cached' (default: once per ordinals tensor "
         "version), 'always' (every call, like the reference) or 'never'.");

@@ -54,4 +54,9 @@ void bind_more_ops(pybind11::module_ &m);
 enum class InitFamily { Tree, Fern, Trie };
 bool init_medians(InitFamily family, torch::Tensor x, torch::Tensor thr, torch::Tensor ord, torch::Tensor w);
 
+// Greedy initialisation of a forest's thresholds and feature indices from class labels (CPU tensors, in
+// place), drawing from a process-wide generator that seed_init() resets.
+bool init_greedy(torch::Tensor x, torch::Tensor labels, torch::Tensor thr, torch::Tensor ord, torch::Tensor w);
+void seed_init(uint64_t seed);
+
 }  // namespace htx

@@ -130,5 +130,46 @@ def test_median_initialisation_screens_like_the_reference():
     root = forest.ordinals[:, 0]
     medians = torch.stack([x[:, c].sort(descending=True).values[9 // 2] for c in root.tolist()])
     assert torch.equal(forest.thresholds.data[:, 0], medians)
-    with pytest.raises(RuntimeError):                  # randomised tree learning is not part of this build
-        hingetree_cpp.tree_init_greedy(x, torch.zeros(9), thr, ord_, w)
+
+
+def test_greedy_initialisation_grows_trees_that_separate_the_classes():
+    """tree_init_greedy draws at random (as the reference's does), so the check is on what any correct run
+    must give: valid trees, reproducible after seed_init, unsplittable vertices closed off, purer leaves."""
+    gen = torch.Generator().manual_seed(0)
+    B, C, T = 400, 9, 6
+    x = torch.randn(B, C, generator=gen)
+    y = (x[:, 3] > 0.2).long() + 2 * (x[:, 5] < -0.1).long()          # 4 classes, decided by features 3 and 5
+    thr, ord_, w = torch.zeros(T, 7), torch.randint(0, C, (T, 7), generator=gen), torch.zeros(T, 8)
+    hingetree_cpp.seed_init(7)
+    assert hingetree_cpp.tree_init_greedy(x, y, thr, ord_, w) is True
+    assert int(ord_.min()) >= 0 and int(ord_.max()) < C and not torch.isnan(thr).any()
+    thr2, ord2 = torch.zeros(T, 7), torch.randint(0, C, (T, 7), generator=gen)
+    hingetree_cpp.seed_init(7)
+    assert hingetree_cpp.tree_init_greedy(x, y, thr2, ord2, w) and torch.equal(thr, thr2) and torch.equal(ord_, ord2)
+
+    def leaves(tree):
+        v = torch.zeros(B, dtype=torch.long)
+        for _ in range(3):
+            v = 2 * v + 1 + (x[torch.arange(B), ord_[tree][v]] - thr[tree][v] > 0).long()
+        return v - 7
+
+    purities = []
+    for tree in range(T):
+        leaf = leaves(tree)
+        purities.append(sum(int(torch.bincount(y[leaf == k], minlength=4).max()) for k in range(8)) / B)
+        closed = thr[tree] == torch.finfo(torch.float32).max          # a vertex that could not be split
+        for v in closed.nonzero().flatten().tolist():
+            assert v > 0 and ord_[tree][v] == ord_[tree][(v - 1) // 2]
+        root_values = x[:, ord_[tree][0]].sort().values               # a threshold is a midpoint of two data values
+        assert (((root_values[1:] + root_values[:-1]) / 2 - thr[tree][0]).abs() < 1e-6).any()
+    majority = int(torch.bincount(y).max()) / B
+    assert min(purities) > majority + 0.2 and max(purities) > 0.95
+
+    before = thr.clone()
+    assert hingetree_cpp.tree_init_greedy(x, torch.zeros(B, dtype=torch.long), thr, ord_, w) is False  # one class
+    assert hingetree_cpp.tree_init_greedy(x, -y, thr, ord_, w) is False                                # negative labels
+    assert hingetree_cpp.tree_init_greedy(x, y.float(), thr, ord_, w) is False                         # regression labels
+    assert torch.equal(thr, before)
+    with pytest.raises(ValueError):
+        hingetree_cpp.tree_init_greedy(x, y.int(), thr, ord_, w)
+    assert R.RandomHingeForest(C, 4, 3).init_greedy(x, y) is True
