@@ -114,3 +114,35 @@ def test_kernels_run_on_the_current_stream(ext):
         out = ext.tree_forward(dx, dthr, dord, dw)
     side.synchronize()
     assert np.array_equal(out.cpu().numpy(), ho.forward("tree", x, thr, ord_, w))
+
+
+def test_training_step_is_cuda_graph_capturable():
+    """Once an ordinals tensor has been validated no operator synchronises or reads back, so a whole
+    forward + backward of a module can be captured in a CUDA graph and replayed on new data."""
+    from hingetreefortorch_b200 import RandomHingeForest as R
+    torch.manual_seed(3)
+    m = R.RandomHingeForest(40, 12, 5, extra_outputs=2).cuda()
+    x = torch.rand(64, 40, device="cuda", requires_grad=True)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):  # validates the ordinals, warms the allocator
+            m(x).sum().backward()
+    torch.cuda.current_stream().wait_stream(side)
+    m.zero_grad(set_to_none=True)
+    x.grad = None
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y = m(x)
+        y.sum().backward()
+    with torch.no_grad():
+        x.copy_(torch.rand(64, 40, device="cuda"))  # new data in the captured input
+    graph.replay()
+    torch.cuda.synchronize()
+    got_y, got_gx, got_gw = y.clone(), x.grad.clone(), m.weights.grad.clone()
+    m.zero_grad(set_to_none=True)
+    x.grad = None
+    want = m(x)
+    want.sum().backward()
+    assert torch.equal(got_y, want)
+    assert torch.allclose(got_gx, x.grad, rtol=1e-5, atol=1e-6) and torch.allclose(got_gw, m.weights.grad, rtol=1e-5, atol=1e-6)
