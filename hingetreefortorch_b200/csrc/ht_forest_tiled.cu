@@ -70,13 +70,33 @@ bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
   return false;
 }
 
+// Inputs with inner positions (x [B, C, K], K > 1; one output per leaf): a sample is a (row, position)
+// pair and its features are K elements apart, so consecutive samples of a tile are consecutive
+// positions — contiguous in x and, for a fixed tree, in the output.  No staging of results is needed.
+bool make_inner_plan(const ht_forest_problem *p, TilePlan &plan) {
+  if (p->K <= 1 || p->M != 1) return false;
+  if (p->C > 65536 || p->depth > 12) return false;
+  if (p->B * p->K * p->T < 32 * 1024) return false;
+  plan.ord_bytes = p->C <= 256 ? 1 : 2;
+  plan.rec = record_layout(p->kind, p->depth, (uint32_t)plan.ord_bytes, true,
+                           paired_ordinals(p->kind, p->depth, (uint32_t)plan.ord_bytes));
+  plan.per_warp = 4;
+  for (int S = 256; S >= 32; S >>= 1) {
+    plan.S = S;
+    plan.G = (kWarps / (S / 32)) * plan.per_warp;
+    plan.smem = (size_t)p->C * S * 4 + 2 * (size_t)plan.G * plan.rec.bytes + 64;
+    if (plan.smem <= kSmemBudget) return true;
+  }
+  return false;
+}
+
 struct TiledArgs {
   const float *x;
   const unsigned char *records;
   const float *w;  // leaf weights in global memory, read when there are several outputs per leaf
   float *out;
   uint32_t *status_word;
-  int64_t B, T;
+  int64_t B, T, K;
   int C, S, G, per_warp, M;
 };
 
@@ -286,6 +306,116 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
   }
 }
 
+template <int KIND, int DEPTH, typename OrdT>
+__global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_inner_kernel(TiledArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr RecordLayout lay =
+      record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), true, paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT)));
+  const int S = a.S, G = a.G, C = a.C;
+  float *xs = reinterpret_cast<float *>(smem);
+  unsigned char *params = smem + (size_t)C * S * 4;
+  uint64_t *full = reinterpret_cast<uint64_t *>(params + 2 * (size_t)G * lay.bytes);
+  uint32_t *finished = reinterpret_cast<uint32_t *>(full + 2);
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int groups_of_samples = S >> 5;
+  const int sample_group = warp % groups_of_samples;
+  const int slot = warp / groups_of_samples;
+  const int64_t samples = a.B * a.K;
+  const int64_t sample0 = (int64_t)blockIdx.x * S;
+  const int all_groups = (int)((a.T + G - 1) / G);
+  const int groups_per_cta = (all_groups + (int)gridDim.y - 1) / (int)gridDim.y;
+  const int group0 = (int)blockIdx.y * groups_per_cta;
+  const int num_groups = max(0, min(groups_per_cta, all_groups - group0));
+  const uint32_t params_addr = smem_addr(params);
+
+  auto issue = [&](int it) {
+    const int64_t first_tree = (int64_t)(group0 + it) * G;
+    const int64_t count = min((int64_t)G, a.T - first_tree);
+    const uint32_t bytes = (uint32_t)(count * lay.bytes);
+    uint64_t *bar = &full[it & 1];
+    mbar_expect_tx(bar, bytes);
+    bulk_load(params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes, a.records + first_tree * lay.bytes, bytes, bar);
+  };
+  if (tid == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    finished[0] = 0;
+    finished[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (num_groups > 0) issue(0);
+    if (num_groups > 1) issue(1);
+  }
+
+  // features of the tile's samples, feature-major; consecutive samples are consecutive positions.
+  // A thread stages the features c0, c0 + step, ... of one sample, or of 4 consecutive positions
+  // at a time when the rows allow 16-byte loads (S divides the thread count; a tile starts on a
+  // multiple of S, so 4 positions never straddle a row when 4 divides K)
+  if ((a.K & 3) == 0) {
+    const int quads = S >> 2, t = (tid % quads) * 4, c_step = kThreads / quads;
+    const int64_t sample = sample0 + t;
+    const bool inside = sample < samples;  // then sample + 3 < samples as well
+    const int64_t row = inside ? sample / a.K : 0, k = inside ? sample - row * a.K : 0;
+    const float *src = a.x + row * C * a.K + k;
+    for (int c = tid / quads; c < C; c += c_step) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (inside) v = __ldg(reinterpret_cast<const float4 *>(src + (int64_t)c * a.K));
+      *reinterpret_cast<float4 *>(xs + c * S + t) = v;
+    }
+  } else {
+    const int t = tid % S, c_step = kThreads / S;
+    const int64_t sample = sample0 + t;
+    const bool inside = sample < samples;
+    const int64_t row = inside ? sample / a.K : 0, k = inside ? sample - row * a.K : 0;
+    const float *src = a.x + row * C * a.K + k;
+    for (int c = tid / S; c < C; c += c_step) xs[c * S + t] = inside ? __ldg(src + (int64_t)c * a.K) : 0.0f;
+  }
+  __syncthreads();
+
+  const int64_t my_sample = sample0 + sample_group * 32 + lane;
+  const bool valid = my_sample < samples;
+  const int64_t my_row = valid ? my_sample / a.K : 0, my_k = valid ? my_sample - my_row * a.K : 0;
+  float *my_out = a.out + my_row * a.T * a.K + my_k;  // tree j of this sample: + j * K
+  const uint32_t xl_addr = smem_addr(xs + sample_group * 32 + lane);
+  const uint32_t x_stride = (uint32_t)S * 4u;
+  const int t_first = slot * 4;
+  bool poisoned = false;
+
+  for (int it = 0; it < num_groups; ++it) {
+    const int group = group0 + it;
+    if (!poisoned && !mbar_wait(&full[it & 1], (uint32_t)((it >> 1) & 1))) {
+      poisoned = true;
+      if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
+    }
+    const int in_group = (int)min((int64_t)G, a.T - (int64_t)group * G);
+    const uint32_t base_addr = params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes;
+    float result[4] = {0.f, 0.f, 0.f, 0.f};
+    if (t_first < in_group) {
+      uint32_t rec[4], unused[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) rec[u] = base_addr + (uint32_t)min(t_first + u, in_group - 1) * lay.bytes;
+      walk<KIND, DEPTH, OrdT, 4, true>(rec, xl_addr, x_stride, result, unused);
+    }
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      const uint32_t before = atomicAdd(&finished[it & 1], 1u);
+      if (before == kWarps - 1) {
+        atomicExch(&finished[it & 1], 0u);
+        __threadfence_block();
+        if (it + 2 < num_groups) issue(it + 2);
+      }
+    }
+    if (valid) {
+      float *dst = my_out + ((int64_t)group * G + t_first) * a.K;
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (t_first + u < in_group) dst[(int64_t)u * a.K] = result[u];
+    }
+  }
+}
+
 template <typename Kernel>
 int launch_one(Kernel kernel, const TilePlan &plan, const TiledArgs &a, dim3 grid, cudaStream_t stream) {
   HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
@@ -296,6 +426,10 @@ int launch_one(Kernel kernel, const TilePlan &plan, const TiledArgs &a, dim3 gri
 
 template <int KIND, int DEPTH>
 int launch_depth(const TilePlan &plan, const TiledArgs &a, dim3 grid, cudaStream_t stream) {
+  if (a.K > 1) {
+    if (plan.ord_bytes == 1) return launch_one(forest_forward_tiled_inner_kernel<KIND, DEPTH, uint8_t>, plan, a, grid, stream);
+    return launch_one(forest_forward_tiled_inner_kernel<KIND, DEPTH, uint16_t>, plan, a, grid, stream);
+  }
   const bool wrec = a.M == 1;
   if (plan.ord_bytes == 1)
     return wrec ? launch_one(forest_forward_tiled_kernel<KIND, DEPTH, uint8_t, true>, plan, a, grid, stream)
@@ -332,14 +466,14 @@ int launch_kind(int depth, const TilePlan &plan, const TiledArgs &a, dim3 grid, 
 
 size_t forward_tiled_workspace_bytes(const ht_forest_problem *p) {
   TilePlan plan;
-  if (!make_plan(p, plan)) return 0;
+  if (!(p->K > 1 ? make_inner_plan(p, plan) : make_plan(p, plan))) return 0;
   return align_up((size_t)p->T * plan.rec.bytes, 256);
 }
 
 int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
                   float *out, void *records, uint32_t *status_word, cudaStream_t stream) {
   TilePlan plan;
-  if (!make_plan(p, plan)) return HT_ERR_UNSUPPORTED;
+  if (!(p->K > 1 ? make_inner_plan(p, plan) : make_plan(p, plan))) return HT_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0 || (reinterpret_cast<uintptr_t>(out) & 15u) != 0)
     return HT_ERR_UNSUPPORTED;
   const int64_t N = threshold_count(p->kind, p->depth);
@@ -362,13 +496,15 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
   a.status_word = status_word;
   a.B = p->B;
   a.T = p->T;
+  a.K = p->K;
   a.C = (int)p->C;
   a.S = plan.S;
   a.G = plan.G;
   a.per_warp = plan.per_warp;
   // With few sample tiles the tree groups are split among CTAs (grid.y) so that the SMs are busy in
   // every round; every split re-stages the feature tile, which is cheap next to the walk.
-  const int64_t tiles = (p->B + plan.S - 1) / plan.S;
+  const int64_t tiles = (p->B * p->K + plan.S - 1) / plan.S;
+  if (tiles > 0x7fffffff) return HT_ERR_UNSUPPORTED;
   const int64_t groups = (p->T + plan.G - 1) / plan.G;
   const dim3 grid((unsigned)tiles, (unsigned)choose_splits(tiles, groups));
   return p->kind == TREE ? launch_kind<TREE>(p->depth, plan, a, grid, stream)

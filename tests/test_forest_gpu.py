@@ -267,3 +267,30 @@ def test_tile_kernel_several_outputs_per_leaf(cabi, kind, shape):
     assert got.shape == (B, T, M)
     assert np.array_equal(got, ho.forward(kind, x, thr, ord_, w), equal_nan=True)
     assert f.ordinal_flags() == 0
+
+
+INNER_SHAPES = [
+    # B, C, inner dims, T, depth: x [B, C, *inner] with one output per leaf, large enough for the tile kernel
+    (8, 40, (64, 65), 20, 6),
+    (3, 300, (1000,), 12, 5),      # more than 256 features: 16-bit feature indices
+    (5, 16, (7, 11, 13), 9, 8),    # tiles straddle rows; positions not a multiple of 32
+    (2, 128, (4099,), 33, 3),
+    (700, 8, (3,), 70, 4),         # fewer positions than a warp
+]
+
+
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+@pytest.mark.parametrize("shape", INNER_SHAPES, ids=[str(s) for s in INNER_SHAPES])
+def test_tile_kernel_with_inner_positions(cabi, kind, shape):
+    """Image-shaped inputs: a sample is a (row, position) pair; forward and maps bit-exact, ties and zeros included."""
+    B, C, inner, T, depth = shape
+    x, thr, ord_, w = random_forest_inputs(90 + INNER_SHAPES.index(shape), kind, B, C, inner, T, depth, (), quantise=True)
+    x.reshape(-1)[:3] = [np.inf, -np.inf, np.nan]
+    dx, dthr, dord, dw = dev(x, thr, ord_, w)
+    f = cabi.Forest(kind, dx, dw)
+    out = f.forward(dx, dthr, dord, dw)
+    assert out.shape == (B, T) + tuple(inner)
+    assert equal(out, ho.forward(kind, x, thr, ord_, w))
+    leaf, margin, mord, reach = ho.maps(kind, x, thr, ord_, w)
+    assert equal(f.leafmap(dx, dthr, dord), leaf)
+    assert f.ordinal_flags() == 0
