@@ -35,9 +35,9 @@ struct BwdPlan {
 
 // paired: the record path, whose kernels never look a feature index up by vertex, takes the paired form
 bool make_bwd_plan(const ht_forest_problem *p, BwdPlan &plan, bool paired = false) {
-  if (p->K != 1 || p->M != 1) return false;
+  if (p->K < 1 || p->M != 1) return false;  // a sample is a (row, inner position) pair
   if (p->C > 65536 || p->depth > 12) return false;
-  if (p->B * p->T < 32 * 1024) return false;
+  if (p->B * p->K * p->T < 32 * 1024) return false;
   plan.ord_bytes = p->C <= 256 ? 1 : 2;
   plan.rec = record_layout(p->kind, p->depth, (uint32_t)plan.ord_bytes, true,
                            paired && paired_ordinals(p->kind, p->depth, (uint32_t)plan.ord_bytes));
@@ -73,7 +73,7 @@ __host__ __device__ inline int64_t record_index(int64_t sample, int64_t tree, in
 }
 
 inline size_t record_array_bytes(const ht_forest_problem *p) {
-  const int64_t blocks = (p->B + kRecordBlock - 1) / kRecordBlock;
+  const int64_t blocks = (p->B * p->K + kRecordBlock - 1) / kRecordBlock;
   return align_up((size_t)(blocks * kRecordBlock * p->T) * 4, 256);
 }
 
@@ -84,7 +84,7 @@ struct BwdArgs {
   float *gx, *gthr, *gw;
   EvalRecords evals;
   uint32_t *status_word;
-  int64_t B, T;
+  int64_t B, T, K;  // B: samples = rows x inner positions; K: inner positions per row
   int C, S, G, per_warp;
 };
 
@@ -135,7 +135,15 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
   }
 
   // features in
-  if ((C & 3) == 0) {
+  if (a.K > 1) {
+    // consecutive samples are consecutive positions of a row; a thread stages one sample's features
+    const int t = tid % S, c_step = kThreads / S;
+    const int64_t sample = row0 + t;
+    const bool inside = sample < a.B;
+    const int64_t row = inside ? sample / a.K : 0, k = inside ? sample - row * a.K : 0;
+    const float *src = a.x + row * C * a.K + k;
+    for (int c = tid / S; c < C; c += c_step) xs[c * S + t] = inside ? __ldg(src + (int64_t)c * a.K) : 0.0f;
+  } else if ((C & 3) == 0) {
     const int quads = C >> 2;
     for (int idx = tid; idx < S * quads; idx += kThreads) {
       const int s = idx % S, q = idx / S;
@@ -158,13 +166,17 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
   const bool row_valid = row0 + my_sample < a.B;
   const uint32_t xl_addr = smem_addr(xs + my_sample);
   const uint32_t x_stride = (uint32_t)S * 4u;
-  const int64_t my_row = row0 + my_sample;
+  const int64_t my_row = row0 + my_sample;  // the sample's index; with inner positions (row, position) below
   const int64_t my_records = record_index(my_row, 0, a.T);  // tree j's record of this sample: + j * kRecordBlock
+  const int64_t outer = row_valid ? my_row / a.K : 0, inner = row_valid ? my_row - outer * a.K : 0;
+  // upstream gradient of tree j: g_sample[j * a.K]; x gradient of feature c: gx_sample[c * a.K]
+  const float *g_sample = a.g + outer * a.T * a.K + inner;
+  float *gx_sample = a.gx == nullptr ? nullptr : a.gx + outer * C * a.K + inner;
   const int full_groups = (int)(a.T / G), tail_trees = (int)(a.T - (int64_t)full_groups * G);
   bool poisoned = false;
   // Full groups with 4 trees per warp on the record path take a body without the bookkeeping of
   // short groups and other tree counts.
-  const bool streamlined = RECORDS && per_warp == 4 && (a.T & 3) == 0;
+  const bool streamlined = RECORDS && per_warp == 4 && (a.T & 3) == 0 && a.K == 1;
   const uint32_t warp_records = (uint32_t)(slot * per_warp) * lay.bytes;
   const float *g_mine = a.g + my_row * a.T + slot * per_warp;
   const int64_t records_mine = my_records + (int64_t)(slot * per_warp) * kRecordBlock;
@@ -223,8 +235,12 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
     const int t_first = slot * per_warp;
     float gval[4] = {0.f, 0.f, 0.f, 0.f};
     if (row_valid && t_first < in_group) {
-      const float *gp = a.g + my_row * a.T + col0 + t_first;
-      if (per_warp == 4 && (a.T & 3) == 0 && t_first + 3 < in_group) {
+      const float *gp = g_sample + (col0 + t_first) * a.K;
+      if (a.K > 1) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (u < per_warp && t_first + u < in_group) gval[u] = __ldg(gp + (int64_t)u * a.K);
+      } else if (per_warp == 4 && (a.T & 3) == 0 && t_first + 3 < in_group) {
         const float4 v = __ldg(reinterpret_cast<const float4 *>(gp));
         gval[0] = v.x;
         gval[1] = v.y;
@@ -262,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
         }
         if (a.gx != nullptr) {
           const uint32_t c = lds_ord<OrdT>(rec + (uint32_t)sizeof(OrdT) * wk.v + (lay.ord - (uint32_t)sizeof(OrdT)));
-          atomicAdd(a.gx + my_row * C + c, dx);
+          atomicAdd(gx_sample + (int64_t)c * a.K, dx);
         }
         if (a.gthr != nullptr) atomicAdd(a.gthr + j * kN + (wk.v - 1u), -dx);
         if (a.gw != nullptr) {
@@ -495,8 +511,9 @@ __global__ void __launch_bounds__(512, 1) reduce_parameter_records_columns_kerne
 
 // x gradient: one thread per sample walks the trees in ascending order and adds into its private
 // column of a shared-memory tile gx[c][s]; the tile leaves with plain stores.
+// B: samples (rows x inner positions), K: inner positions per row.
 __global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, const int32_t *__restrict__ ord, int64_t B,
-                                                               int64_t T, int64_t N, int C, int S, float *gx) {
+                                                               int64_t K, int64_t T, int64_t N, int C, int S, float *gx) {
   extern __shared__ float tile[];
   const int s = threadIdx.x;
   const int64_t row0 = (int64_t)blockIdx.x * S;
@@ -543,7 +560,16 @@ __global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, co
     }
   }
   __syncthreads();
-  if ((C & 3) == 0) {
+  if (K > 1) {  // consecutive samples are consecutive positions: each feature's run of the tile is contiguous
+    for (int idx = threadIdx.x; idx < S * C; idx += blockDim.x) {
+      const int ss = idx % S, c = idx / S;
+      const int64_t sample = row0 + ss;
+      if (sample < B) {
+        const int64_t row = sample / K, k = sample - row * K;
+        gx[(row * C + c) * K + k] = tile[c * S + ss];
+      }
+    }
+  } else if ((C & 3) == 0) {
     const int quads = C >> 2;
     for (int idx = threadIdx.x; idx < S * quads; idx += blockDim.x) {
       const int ss = idx % S, q = idx / S;
@@ -627,14 +653,17 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
                           reinterpret_cast<uint32_t *>(base + 2 * stride)};
   }
   a.status_word = status_word;
-  a.B = p->B;
+  a.B = p->B * p->K;
+  a.K = p->K;
   a.T = p->T;
   a.C = (int)p->C;
   a.S = plan.S;
   a.G = plan.G;
   a.per_warp = plan.per_warp;
   // a small batch gives too few sample tiles for 148 SMs: share the tree groups between CTAs
-  const int64_t tiles = (p->B + plan.S - 1) / plan.S;
+  const int64_t samples = p->B * p->K;
+  const int64_t tiles = (samples + plan.S - 1) / plan.S;
+  if (tiles > 0x7fffffff) return HT_ERR_UNSUPPORTED;
   const int64_t groups = (p->T + plan.G - 1) / plan.G;
   const dim3 grid((unsigned)tiles, (unsigned)choose_splits(tiles, groups));
   const int rc = p->kind == TREE ? launch_kind<TREE>(p->depth, plan, a, grid, stream)
@@ -647,13 +676,13 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
     int warps = 1;
     if ((p->flags & HT_DETERMINISTIC) == 0) {
       warps = 16;
-      while (warps > 1 && ((size_t)warps * (N + L) * 4 > 64 * 1024 || p->B < (int64_t)warps * 512)) warps >>= 1;
+      while (warps > 1 && ((size_t)warps * (N + L) * 4 > 64 * 1024 || samples < (int64_t)warps * 512)) warps >>= 1;
     }
     const size_t smem = sizeof(float) * (size_t)(N + L) * warps;
     if ((p->flags & HT_DETERMINISTIC) != 0) {
       HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)kSmemBudget));
-      reduce_parameter_records_kernel<true><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, p->B, p->T, N, L, gthr, gw);
+      reduce_parameter_records_kernel<true><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, samples, p->T, N, L, gthr, gw);
     } else {
       // copies of the bins per warp (a power of two, at most one per lane) that 16 warps can hold
       int columns = 32;
@@ -662,12 +691,12 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
         const size_t column_smem = (size_t)16 * (N + L) * columns * 4;
         HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_columns_kernel<8>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-        reduce_parameter_records_columns_kernel<8><<<(unsigned)p->T, 512, column_smem, stream>>>(a.evals, p->B, p->T, N, L,
+        reduce_parameter_records_columns_kernel<8><<<(unsigned)p->T, 512, column_smem, stream>>>(a.evals, samples, p->T, N, L,
                                                                                                  columns, gthr, gw);
       } else {
         HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-        reduce_parameter_records_kernel<false><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, p->B, p->T, N, L, gthr,
+        reduce_parameter_records_kernel<false><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, samples, p->T, N, L, gthr,
                                                                                             gw);
       }
     }
@@ -679,7 +708,8 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
     const size_t smem = (size_t)S * p->C * 4;
     if (smem > kSmemBudget) return HT_ERR_UNSUPPORTED;
     HT_CUDA_TRY(cudaFuncSetAttribute(reduce_x_records_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-    reduce_x_records_kernel<<<(unsigned)((p->B + S - 1) / S), S, smem, stream>>>(a.evals, ord, p->B, p->T, N, (int)p->C, S, gx);
+    reduce_x_records_kernel<<<(unsigned)((samples + S - 1) / S), S, smem, stream>>>(a.evals, ord, samples, p->K, p->T, N,
+                                                                                    (int)p->C, S, gx);
     HT_CHECK_LAUNCH();
   }
   return HT_OK;

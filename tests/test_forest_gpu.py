@@ -294,3 +294,25 @@ def test_tile_kernel_with_inner_positions(cabi, kind, shape):
     leaf, margin, mord, reach = ho.maps(kind, x, thr, ord_, w)
     assert equal(f.leafmap(dx, dthr, dord), leaf)
     assert f.ordinal_flags() == 0
+
+
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+@pytest.mark.parametrize("shape", INNER_SHAPES, ids=[str(s) for s in INNER_SHAPES])
+def test_tile_kernel_backward_with_inner_positions(cabi, kind, shape):
+    """Record path on image-shaped inputs: default mode within tolerance (x gradient exact), fixed-order mode exact."""
+    B, C, inner, T, depth = shape
+    x, thr, ord_, w = random_forest_inputs(110 + INNER_SHAPES.index(shape), kind, B, C, inner, T, depth, (), quantise=True)
+    g = np.random.default_rng(6).standard_normal((B, T) + tuple(inner)).astype(np.float32)
+    dx, dthr, dord, dw, dg = dev(x, thr, ord_, w, g)
+    rx, rthr, rw = ho.backward(kind, x, thr, ord_, w, g)
+    ax, athr, aw = ho.backward_magnitudes(kind, x, thr, ord_, w, g)
+    f = cabi.Forest(kind, dx, dw)
+    gx, gthr, gw = f.backward(dx, dthr, dord, dw, dg)
+    assert equal(gx, rx) and grad_close(gthr, rthr, athr) and grad_close(gw, rw, aw)
+    fd = cabi.Forest(kind, dx, dw, deterministic=True)
+    for got, ref in zip(fd.backward(dx, dthr, dord, dw, dg), (rx, rthr, rw)):
+        assert equal(got, ref)
+    small = cabi.Forest(kind, dx, dw, backward_workspace=False)  # scatter variant of the tile kernel
+    sx, sthr, sw = small.backward(dx, dthr, dord, dw, dg)
+    assert grad_close(sx, rx, ax) and grad_close(sthr, rthr, athr) and grad_close(sw, rw, aw)
+    assert f.ordinal_flags() == 0
