@@ -1,8 +1,12 @@
-// Shared-memory tile kernel for the forest forward on tabular input (K == 1, one output per leaf).
+// Shared-memory tile kernels for the forest forward.
+//
+// forest_forward_tiled_kernel: tabular input (K == 1), one or several outputs per leaf.
+// forest_forward_tiled_inner_kernel: inputs with inner positions (x [B, C, K...]), one output per leaf.
 //
 // Work decomposition (one CTA of 1024 threads per tile, sized for one CTA per SM):
-//   * a CTA owns S consecutive samples and walks ALL trees, so every input element is read
-//     from HBM exactly once;
+//   * a CTA owns S consecutive samples and walks ALL trees (or, when the batch alone gives too
+//     few tiles for the machine, its share of the tree groups), so every input element is read
+//     from HBM once;
 //   * the samples' features sit in shared memory feature-major, xs[c][s]: lane l of a warp
 //     always reads bank l whatever feature its current vertex tests, so the data gather never
 //     conflicts although the 32 lanes are at 32 different vertices;
@@ -10,13 +14,16 @@
 //     are processed in groups of G; inside a group slot q owns G/slots consecutive trees and
 //     walks them all at once (independent dependent-load chains hide shared-memory latency);
 //   * tree parameters arrive as per-tree records {root and its two children for a single
-//     broadcast load, thresholds, uint8/uint16 feature indices, leaf weights in path order},
-//     written once per call by a small repack kernel, and are streamed into shared memory with
-//     1-D bulk async copies (cp.async.bulk, the TMA engine) completing on an mbarrier.  Two
-//     buffers; the last warp to finish a group issues the copy that refills its buffer, so no
-//     warp ever waits for another in order to keep the pipeline fed;
-//   * results of a group are transposed through a per-sample-group staging area (named
-//     barriers over the 4..32 warps of the sample group only) and leave as row segments.
+//     broadcast load, thresholds, feature indices, leaf weights in path order}, written once per
+//     call by a small repack kernel, and are streamed into shared memory with 1-D bulk async
+//     copies (cp.async.bulk, the TMA engine) completing on an mbarrier.  Two buffers; the last
+//     warp to finish a group issues the copy that refills its buffer, so no warp ever waits for
+//     another in order to keep the pipeline fed.  One-byte feature indices are stored as words
+//     {own, left child's, right child's} of the even-level vertices, one load for two levels;
+//   * tabular results of a group are transposed through a per-sample-group staging area (named
+//     barriers over the 4..32 warps of the sample group only) and leave as row segments; with
+//     inner positions consecutive samples are consecutive positions of the same output row, so
+//     the results leave straight from registers.
 //
 // Only the smallest |margin| matters in the forward, so the minimum is tracked on absolute
 // values.  CUDA's fminf ignores a NaN operand; the reference keeps a NaN only when the root
