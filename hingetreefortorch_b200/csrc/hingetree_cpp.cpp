@@ -135,6 +135,15 @@ void OrdinalGuard::finish() {
   remember_valid(ord_, channels_);
 }
 
+// Most scratch a backward call may take for its per-evaluation records (12 bytes per tree
+// evaluation).  Beyond it the call runs without them: atomic scatters instead of ordered sums.
+static int64_t g_backward_scratch_limit = INT64_MAX;
+
+void set_backward_scratch_limit(int64_t bytes) {
+  if (bytes < 0) bad_argument("Error: the scratch limit is a number of bytes >= 0.");
+  g_backward_scratch_limit = bytes;
+}
+
 void set_ordinal_check(const std::string &mode) {
   if (mode == "cached")
     g_ordinal_check = OrdinalCheck::Cached;
@@ -232,6 +241,8 @@ std::vector<torch::Tensor> forest_backward(int kind, bool deterministic, torch::
   if (!need_x && !need_thr && !need_w) return grads;
   if (deterministic) call.problem.flags |= HT_DETERMINISTIC;
   call.problem.flags |= HT_WORKSPACE_FOR_BACKWARD;
+  if ((int64_t)ht_forest_workspace_bytes(&call.problem) > g_backward_scratch_limit && !deterministic)
+    call.problem.flags &= ~HT_WORKSPACE_FOR_BACKWARD;
   if (need_x) grads[0] = torch::empty_like(x);
   if (need_thr) grads[1] = torch::empty_like(thr);
   if (need_w) grads[3] = torch::empty_like(w);
@@ -490,6 +501,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tree_init_greedy", &init_greedy,
         "Initialize thresholds and ordinals by random decision tree learning on class labels (CPU only).");
   m.def("seed_init", &seed_init, "Seed the generator tree_init_greedy draws from.");
+  m.def("set_backward_scratch_limit", &set_backward_scratch_limit,
+        "Upper bound in bytes on the scratch a default-mode backward call allocates for its per-evaluation records "
+        "(12 bytes per tree evaluation); above it the gradients are scattered with atomics instead. Default: no bound.");
   m.def("set_ordinal_check", &set_ordinal_check,
         "When to read the ordinal range flag back from the device: 'cached' (default: once per ordinals tensor "
         "version), 'always' (every call, like the reference) or 'never'.");

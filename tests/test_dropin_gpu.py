@@ -146,3 +146,25 @@ def test_training_step_is_cuda_graph_capturable():
     want.sum().backward()
     assert torch.equal(got_y, want)
     assert torch.allclose(got_gx, x.grad, rtol=1e-5, atol=1e-6) and torch.allclose(got_gw, m.weights.grad, rtol=1e-5, atol=1e-6)
+
+
+def test_backward_scratch_limit_switches_to_scatters(ext):
+    """With the per-evaluation records ruled out the default-mode backward still matches within tolerance."""
+    rng = np.random.default_rng(8)
+    B, C, T, depth = 1200, 64, 40, 6
+    x = rng.standard_normal((B, C)).astype(np.float32)
+    thr = rng.uniform(-3, 3, (T, 63)).astype(np.float32)
+    ord_ = rng.integers(0, C, (T, 63)).astype(np.int64)
+    w = rng.standard_normal((T, 64)).astype(np.float32)
+    g = rng.standard_normal((B, T)).astype(np.float32)
+    dx, dthr, dord, dw, dg = [torch.from_numpy(a).cuda() for a in (x, thr, ord_, w, g)]
+    with_records = ext.tree_backward(dx, True, dthr, True, dord, False, dw, True, dg)
+    ext.set_backward_scratch_limit(0)
+    try:
+        scattered = ext.tree_backward(dx, True, dthr, True, dord, False, dw, True, dg)
+    finally:
+        ext.set_backward_scratch_limit(2 ** 62)
+    for a, b in zip((with_records[0], with_records[1], with_records[3]), (scattered[0], scattered[1], scattered[3])):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-4 * float(a.abs().max()))
+    with pytest.raises(ValueError):
+        ext.set_backward_scratch_limit(-1)
