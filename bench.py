@@ -454,6 +454,8 @@ def our_arm(a, wl):
         dist.init_process_group("nccl", device_id=device)
 
     B = a.rows or wl["B"]
+    if a.linear == "tf32":
+        torch.backends.cuda.matmul.allow_tf32 = True
     runner = ForestRunner(wl, B, device, rank) if wl["op"] == "forest" else ModuleRunner(wl, B, device, rank, world)
     if wl["bwd"]:
         runner.enable_backward()
@@ -574,7 +576,8 @@ def our_arm(a, wl):
             "value": value, "unit": "tree-evals/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": elapsed_ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl["name"] + ("" if B == wl["B"] else " (rows overridden)"), "rows_per_gpu": B,
+            "config": {"workload": wl["name"] + ("" if B == wl["B"] else " (rows overridden)") +
+                       (" [Linear in tf32]" if a.linear == "tf32" and wl["op"] == "pipeline" else ""), "rows_per_gpu": B,
                        "l2": "inputs and outputs exceed L2 (126 MB)" if bytes_per_step > 4 * 126e6
                        else "working set fits L2; launch-latency regime",
                        "parallelism": "batch-sharded x%d, replicated parameters%s"
@@ -608,6 +611,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--rows", type=int, default=0, help="rows per GPU instead of the workload's (profiler captures)")
+    ap.add_argument("--linear", default="fp32", choices=["fp32", "tf32"],
+                    help="c5 only: arithmetic of torch's Linear (cuBLAS); the forest stage is fp32 either way")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time the device-resident step only (profiler captures): no end-to-end and no CPU leg")
     a = ap.parse_args()
