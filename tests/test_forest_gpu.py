@@ -186,6 +186,8 @@ TILED_SHAPES = [
     (257, 1000, 132, 7),  # wide rows: small sample tiles
     (4096, 16, 9, 10),
     (2048, 32, 17, 1),
+    (600, 32, 70, 11),    # deep trees: one or two trees per warp at a time
+    (3000, 24, 13, 9),
 ]
 
 
