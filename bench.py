@@ -278,11 +278,12 @@ def reference_arm(a, wl):
 class ForestRunner:
     """Plain forest / fern through the C ABI (device resident) and through hingetree_cpp (end to end)."""
 
-    def __init__(self, wl, B, device, rank):
+    def __init__(self, wl, B, device, rank, world=1):
         import torch
         from hingetreefortorch_b200 import _cabi
         from hingetreefortorch_b200._ext import hingetree_cpp
         self.wl, self.B, self.device, self.torch, self.ext = wl, B, device, torch, hingetree_cpp
+        self.world = world
         self.thr, self.ord, self.w = [t.to(device) for t in make_params(wl)]
         self.x_host = make_x(wl, B, rank)
         self.x = self.x_host.to(device)
@@ -297,12 +298,19 @@ class ForestRunner:
         if self.g is None:
             self.g = torch.randn(self.forest.out_shape, generator=torch.Generator(device=self.device).manual_seed(5),
                                  device=self.device)
-            self.grads = (torch.empty_like(self.x), torch.empty_like(self.thr), torch.empty_like(self.w))
+            # threshold and leaf-weight gradients side by side in one buffer: one all-reduce per step at N > 1
+            self.param_grads = torch.empty(self.thr.numel() + self.w.numel(), dtype=torch.float32, device=self.device)
+            n = self.thr.numel()
+            self.grads = (torch.empty_like(self.x), self.param_grads[:n].view_as(self.thr),
+                          self.param_grads[n:].view_as(self.w))
 
     def step(self, backward):
         self.forest.forward(self.x, self.thr, self.ord, self.w, out=self.out)
         if backward:
             self.forest.backward(self.x, self.thr, self.ord, self.w, self.g, outs=self.grads)
+            if self.world > 1 and self.wl["bwd"]:  # a training workload: parameter gradients summed over the ranks
+                import torch.distributed as dist
+                dist.all_reduce(self.param_grads)
 
     def launches_per_step(self, backward):
         if not backward:
@@ -456,7 +464,7 @@ def our_arm(a, wl):
     B = a.rows or wl["B"]
     if a.linear == "tf32":
         torch.backends.cuda.matmul.allow_tf32 = True
-    runner = ForestRunner(wl, B, device, rank) if wl["op"] == "forest" else ModuleRunner(wl, B, device, rank, world)
+    runner = ForestRunner(wl, B, device, rank, world) if wl["op"] == "forest" else ModuleRunner(wl, B, device, rank, world)
     if wl["bwd"]:
         runner.enable_backward()
 
@@ -512,7 +520,7 @@ def our_arm(a, wl):
         fwd_bwd = {"value": evals * world * fb_steps / (fb_ms * 1e-3), "unit": "tree-evals/s",
                    "ms_per_step": fb_ms / fb_steps, "steps": fb_steps, "bytes_per_step": fb_bytes,
                    "achieved_gbs": fb_bytes / (fb_ms / fb_steps * 1e-3) / 1e9}
-        runner.g = runner.grads = None
+        runner.g = runner.grads = runner.param_grads = None
         torch.cuda.empty_cache()
 
     # the launch-latency workloads once more as one CUDA-graph replay per step: the C ABI neither
@@ -582,7 +590,7 @@ def our_arm(a, wl):
                        else "working set fits L2; launch-latency regime",
                        "parallelism": "batch-sharded x%d, replicated parameters%s"
                        % (world, ", one NCCL all-reduce of parameter gradients per step"
-                          if world > 1 and wl["op"] != "forest" else "")},
+                          if world > 1 and wl["bwd"] else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": C3_DRAM_BYTES_PER_ROW * B if a.workload == "c3" else None,
                          "peak_source": peak_src, "bytes_per_launch": bytes_per_step,
