@@ -70,7 +70,9 @@ bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
       plan.S = S;
       plan.G = G;
       plan.per_warp = per_warp;
-      plan.smem = (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + (size_t)S * (G * p->M + 1) * 4 + 64;
+      // results: a staging row per sample (one output per leaf), or the warps' (margin, leaf) pairs
+      const size_t results = p->M == 1 ? (size_t)S * (G + 1) * 4 : (size_t)kWarps * 32 * 4 * 8;
+      plan.smem = (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + results + 64;
       if (plan.smem <= kSmemBudget) return true;
     }
   }
@@ -114,11 +116,11 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
       record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC, paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT)));
   const int S = a.S, G = a.G, C = a.C;
   const int M = WREC ? 1 : a.M;
-  const int row_floats = G * M + 1;  // staging row of one sample: G trees x M outputs, padded
+  const int row_floats = G + 1;  // staging row of one sample (one output per leaf): G trees, padded
   float *xs = reinterpret_cast<float *>(smem);
   unsigned char *params = smem + (size_t)C * S * 4;
   float *outs = reinterpret_cast<float *>(params + 2 * (size_t)G * lay.bytes);
-  uint64_t *full = reinterpret_cast<uint64_t *>(outs + (size_t)S * row_floats);  // [2] copy landed
+  uint64_t *full = reinterpret_cast<uint64_t *>(outs + (WREC ? (size_t)S * row_floats : (size_t)kWarps * 32 * 4 * 2));  // [2] copy landed
   uint32_t *finished = reinterpret_cast<uint32_t *>(full + 2);                 // [2] warps done with a buffer
 
   const int tid = threadIdx.x;
@@ -270,21 +272,56 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
     done_with_buffer(it);
 
     const int64_t col0 = (int64_t)group * G;
-    named_barrier(1 + sample_group, group_threads);  // previous group's rows have left the staging area
+    if (!WREC) {
+      // Several outputs per leaf: out[i, j, :] = |margin| * w[j, leaf, :], and the warp's trees
+      // j .. j + n - 1 of one sample are n * M consecutive outputs.  Every lane leaves its (|margin|, leaf)
+      // pairs in the warp's corner of shared memory; then the warp writes the 32 samples' runs one after
+      // another, lane by lane along a run, reading the weight rows from global memory (L2 resident)
+      // the same way: loads and stores are contiguous whatever leaves the samples reached.
+      const int trees_here = min(per_warp, in_group - t_first);  // <= 0: nothing for this warp in a short group
+      float2 *pairs = reinterpret_cast<float2 *>(outs) + (size_t)warp * 32 * 4;
+      __syncwarp();
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      if (u < per_warp && t_first + u < in_group) {
-        if (WREC) {
-          stage[lane * row_floats + t_first + u] = result[u];
-        } else {
-          // several outputs per leaf: the leaf's weight row comes from global memory (L2 resident)
-          const uint32_t key = __brev(path[u] - kL) >> (32 - DEPTH);
-          const float *wl = a.w + ((col0 + t_first + u) * (int64_t)kL + key) * M;
-          float *dst = stage + lane * row_floats + (t_first + u) * M;
-          for (int m = 0; m < M; ++m) dst[m] = result[u] * __ldg(wl + m);
+      for (int u = 0; u < 4; ++u)
+        pairs[lane * 4 + u] = make_float2(result[u], __uint_as_float(__brev(path[u] - kL) >> (32 - DEPTH)));
+      __syncwarp();
+      if (trees_here > 0) {
+        const int run = trees_here * M;  // outputs of one sample that this warp owns, contiguous
+        const int64_t first_row = row0 + sample_group * 32;
+        const int rows_here = (int)min((int64_t)32, a.B - first_row);
+        const float *w_first = a.w + (col0 + t_first) * (int64_t)kL * M;
+        float *dst = a.out + first_row * row_pitch + (col0 + t_first) * M;
+        // Lane l writes element l, l + 32, ... of every sample's run: which tree and which output
+        // that is does not depend on the sample, so it is worked out once per pass and the loop
+        // over the samples is a pair load, a weight load, a multiply and a store.
+        for (int e = lane; e < run; e += 32) {
+          const int u = (e >= M) + (e >= 2 * M) + (e >= 3 * M), m = e - u * M;  // run <= 4 * M
+          const float *w_tree = w_first + (int64_t)u * kL * M + m;
+          const float2 *pair_of = pairs + u;
+          float *to = dst + e;
+          int sample = 0;
+          for (; sample + 4 <= rows_here; sample += 4) {
+            float2 pr[4];
+            float weight[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) pr[k] = pair_of[(sample + k) * 4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) weight[k] = __ldg(w_tree + (int64_t)__float_as_uint(pr[k].y) * M);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) to[(int64_t)(sample + k) * row_pitch] = pr[k].x * weight[k];
+          }
+          for (; sample < rows_here; ++sample) {
+            const float2 pr = pair_of[sample * 4];
+            to[(int64_t)sample * row_pitch] = pr.x * __ldg(w_tree + (int64_t)__float_as_uint(pr.y) * M);
+          }
         }
       }
+      continue;
     }
+    named_barrier(1 + sample_group, group_threads);  // previous group's rows have left the staging area
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (u < per_warp && t_first + u < in_group) stage[lane * row_floats + t_first + u] = result[u];
     named_barrier(1 + sample_group, group_threads);  // staging area complete
 
     // the sample group's warps write its [32 x in_group*M] block of results as row segments
