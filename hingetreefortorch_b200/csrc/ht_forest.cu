@@ -405,6 +405,9 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
     const int trc = backward_tiled(p, x, thr, a.ord, w, g, gx, gthr, gw, ws + ordinals_bytes(p), eval_records,
                                    status_word, pr.stream);
     if (trc != HT_ERR_UNSUPPORTED) return trc;
+    const int mrc = backward_tiled_multi(p, x, thr, a.ord, w, g, gx, gthr, gw, ws + ordinals_bytes(p),
+                                         forward_tiled_workspace_bytes(p), status_word, pr.stream);
+    if (mrc != HT_ERR_UNSUPPORTED) return mrc;
   }
   if ((p->flags & HT_DETERMINISTIC) == 0) {
     const unsigned grid = blocks_for(pr.evals, kBlock);

@@ -26,4 +26,11 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
                    const float *g, float *gx, float *gthr, float *gw, void *records, void *eval_records,
                    uint32_t *status_word, cudaStream_t stream);
 
+// Backward for several outputs per leaf (default mode, tabular input) with the tile kernel of
+// ht_forest_tiled_bwd_multi.cu; same contract as backward_tiled without evaluation records.
+// `records` is scratch of `records_bytes` bytes (the forward's record area is large enough).
+int backward_tiled_multi(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
+                         const float *g, float *gx, float *gthr, float *gw, void *records, size_t records_bytes,
+                         uint32_t *status_word, cudaStream_t stream);
+
 }  // namespace ht

@@ -318,3 +318,29 @@ def test_tile_kernel_backward_with_inner_positions(cabi, kind, shape):
     sx, sthr, sw = small.backward(dx, dthr, dord, dw, dg)
     assert grad_close(sx, rx, ax) and grad_close(sthr, rthr, athr) and grad_close(sw, rw, aw)
     assert f.ordinal_flags() == 0
+
+
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+@pytest.mark.parametrize("shape", MULTI_OUTPUT_SHAPES + [(257, 40, 130, 4, 33), (2100, 16, 20, 9, 64),
+                                                        # from 4 Mi evaluations on: the tile kernel
+                                                        (40000, 64, 110, 6, 3), (9000, 300, 500, 5, 33), (70001, 16, 64, 9, 64)],
+                         ids=lambda s: str(s))
+def test_tile_kernel_backward_several_outputs_per_leaf(cabi, kind, shape):
+    """Default-mode backward with several outputs per leaf (tile kernel, work along the outputs shared by the warp)."""
+    B, C, T, depth, M = shape
+    x, thr, ord_, w = random_forest_inputs(130 + B % 97, kind, B, C, (), T, depth, (M,), quantise=True)
+    g = np.random.default_rng(7).standard_normal((B, T, M)).astype(np.float32)
+    dx, dthr, dord, dw, dg = dev(x, thr, ord_, w, g)
+    rx, rthr, rw = ho.backward(kind, x, thr, ord_, w, g)
+    ax, athr, aw = ho.backward_magnitudes(kind, x, thr, ord_, w, g)
+    f = cabi.Forest(kind, dx, dw)
+    gx, gthr, gw = f.backward(dx, dthr, dord, dw, dg)
+    assert grad_close(gx, rx, ax) and grad_close(gthr, rthr, athr) and grad_close(gw, rw, aw)
+    only_w = f.backward(dx, dthr, dord, dw, dg, need=(False, False, True))
+    assert only_w[0] is None and grad_close(only_w[2], rw, aw)
+    only_x = f.backward(dx, dthr, dord, dw, dg, need=(True, False, False))
+    assert grad_close(only_x[0], rx, ax) and only_x[2] is None
+    fd = cabi.Forest(kind, dx, dw, deterministic=True)  # fixed-order mode: the ordered kernels, exact
+    for got, ref in zip(fd.backward(dx, dthr, dord, dw, dg), (rx, rthr, rw)):
+        assert equal(got, ref)
+    assert f.ordinal_flags() == 0
