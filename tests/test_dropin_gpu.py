@@ -168,3 +168,15 @@ def test_backward_scratch_limit_switches_to_scatters(ext):
         assert torch.allclose(a, b, rtol=1e-4, atol=1e-4 * float(a.abs().max()))
     with pytest.raises(ValueError):
         ext.set_backward_scratch_limit(-1)
+
+
+def test_speedtest_sweeps_like_the_reference(ext, capfd):
+    """The reference's own benchmark operator: trees 1..512 by powers of two, depth 1..12, rows = trees, depth,
+    forward ms, backward ms (hingetree.cpp:1361-1438)."""
+    x = torch.rand(100, 1000, device="cuda")
+    timings = ext.tree_speedtest(x, False)
+    assert timings.shape == (4, 120) and timings.device.type == "cpu"
+    assert timings[0].tolist() == [float(2 ** s) for s in range(10) for _ in range(12)]
+    assert timings[1].tolist() == [float(d) for _ in range(10) for d in range(1, 13)]
+    assert bool((timings[2:] > 0).all()) and float(timings[2:].max()) < 50.0
+    assert "hingetree_forward: numBatches = 100" in capfd.readouterr().out
