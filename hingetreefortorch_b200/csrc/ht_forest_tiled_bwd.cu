@@ -523,7 +523,7 @@ __global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, co
   if (s < S && i < B) {
     // batches of kAhead trees; the next batch (records and feature indices) is requested before
     // the current one is added
-    constexpr int kAhead = 8;
+    constexpr int kAhead = 16;
     const int64_t first = record_index(i, 0, T);  // tree j of this sample sits at first + j * 256
     // three stages in flight: records of batch n+2, feature indices of batch n+1, additions of batch n
     float a0[kAhead], a1[kAhead], a2[kAhead];
