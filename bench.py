@@ -51,8 +51,9 @@ WORKLOADS = {
 }
 
 
-# DRAM bytes (read + write) of the tile kernel per input row of the c3 shape, from the committed
-# capture profiles/forest_forward_tiled_65536rows_ncu.md: (38 455 040 + 214 589 952) B / 65 536 rows.
+# DRAM bytes (read + write) of the tile kernel per input row of the c3 shape, from an Nsight Compute
+# capture of the kernel on 65 536 rows (dram__bytes_read.sum + dram__bytes_write.sum =
+# 38 455 040 + 214 589 952 B; the summary is kept with the repository's profile summaries).
 # Traffic grows in proportion to the rows (every CTA handles 256 rows the same way), so the
 # full-size launch is that figure times its rows.
 C3_DRAM_BYTES_PER_ROW = (38455040 + 214589952) / 65536
