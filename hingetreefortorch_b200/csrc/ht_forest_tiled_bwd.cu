@@ -27,6 +27,12 @@ using namespace tile;
 
 namespace {
 
+// Warps per CTA of the parameter reduction with bin columns.  Fewer warps leave room for more columns
+// per warp (fewer turns per chunk, and a turn costs a full shared-memory wavefront per load and
+// store) but hide less latency; C3 forward+backward: 16 warps x 4 columns 17.9 ms, 8 x 8 17.4 ms,
+// 4 x 16 18.4 ms.
+constexpr int kColumnWarps = 8;
+
 struct BwdPlan {
   int S, G, per_warp, ord_bytes;
   RecordLayout rec;
@@ -684,15 +690,16 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
                                        (int)kSmemBudget));
       reduce_parameter_records_kernel<true><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, samples, p->T, N, L, gthr, gw);
     } else {
-      // copies of the bins per warp (a power of two, at most one per lane) that 16 warps can hold
+      // copies of the bins per warp (a power of two, at most one per lane) that `column_warps` warps can hold
+      const int column_warps = kColumnWarps;
       int columns = 32;
-      while (columns > 1 && (size_t)16 * (N + L) * columns * 4 > 200 * 1024) columns >>= 1;
+      while (columns > 1 && (size_t)column_warps * (N + L) * columns * 4 > 200 * 1024) columns >>= 1;
       if (warps == 16 && columns >= 4) {
-        const size_t column_smem = (size_t)16 * (N + L) * columns * 4;
+        const size_t column_smem = (size_t)column_warps * (N + L) * columns * 4;
         HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_columns_kernel<8>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-        reduce_parameter_records_columns_kernel<8><<<(unsigned)p->T, 512, column_smem, stream>>>(a.evals, samples, p->T, N, L,
-                                                                                                 columns, gthr, gw);
+        reduce_parameter_records_columns_kernel<8><<<(unsigned)p->T, 32 * column_warps, column_smem, stream>>>(
+            a.evals, samples, p->T, N, L, columns, gthr, gw);
       } else {
         HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
