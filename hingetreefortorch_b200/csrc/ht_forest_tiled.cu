@@ -37,6 +37,7 @@
 // |feature - threshold| bit for bit.
 #include "ht_forest_tiled.cuh"
 #include "ht_tile_common.cuh"
+#include "ht_tma.cuh"
 
 #include <algorithm>
 
@@ -56,6 +57,14 @@ struct TilePlan {
   size_t smem;
 };
 
+// Shared-memory layout of forest_forward_tiled_kernel, from a 1024-byte boundary: the results area (a
+// staging row per sample with one output per leaf — boxes the TMA engine can store —, or the warps'
+// (margin, leaf) pairs), the feature tile, two parameter buffers, the barriers.
+__host__ __device__ inline size_t results_bytes(bool one_output, int S, int G) {
+  const size_t bytes = one_output ? (size_t)S * (G + 1) * 4 : (size_t)kWarps * 32 * 4 * 8;
+  return (bytes + 1023) & ~(size_t)1023;
+}
+
 bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
   if (p->K != 1 || p->M < 1 || p->M > 64) return false;
   if (p->C > 65536 || p->depth > 12) return false;
@@ -71,8 +80,7 @@ bool make_plan(const ht_forest_problem *p, TilePlan &plan) {
       plan.G = G;
       plan.per_warp = per_warp;
       // results: a staging row per sample (one output per leaf), or the warps' (margin, leaf) pairs
-      const size_t results = p->M == 1 ? (size_t)S * (G + 1) * 4 : (size_t)kWarps * 32 * 4 * 8;
-      plan.smem = (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + results + 64;
+      plan.smem = 1024 + results_bytes(p->M == 1, S, G) + (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + 64;
       if (plan.smem <= kSmemBudget) return true;
     }
   }
@@ -100,6 +108,7 @@ bool make_inner_plan(const ht_forest_problem *p, TilePlan &plan) {
 }
 
 struct TiledArgs {
+  CUtensorMap out_map;  // the output [B, T] in boxes of 32 rows x G trees (when tma_store is set)
   const float *x;
   const unsigned char *records;
   const float *w;  // leaf weights in global memory, read when there are several outputs per leaf
@@ -107,21 +116,25 @@ struct TiledArgs {
   uint32_t *status_word;
   int64_t B, T, K;
   int C, S, G, per_warp, M;
+  int tma_store;  // results of full groups leave through the TMA engine (G is 16 or 32)
 };
 
 template <int KIND, int DEPTH, typename OrdT, bool WREC>
-__global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(TiledArgs a) {
-  extern __shared__ __align__(128) unsigned char smem[];
+__global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(const __grid_constant__ TiledArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem[];
   constexpr RecordLayout lay =
       record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC, paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT)));
   const int S = a.S, G = a.G, C = a.C;
   const int M = WREC ? 1 : a.M;
-  const int row_floats = G + 1;  // staging row of one sample (one output per leaf): G trees, padded
-  float *xs = reinterpret_cast<float *>(smem);
-  unsigned char *params = smem + (size_t)C * S * 4;
-  float *outs = reinterpret_cast<float *>(params + 2 * (size_t)G * lay.bytes);
-  uint64_t *full = reinterpret_cast<uint64_t *>(outs + (WREC ? (size_t)S * row_floats : (size_t)kWarps * 32 * 4 * 2));  // [2] copy landed
-  uint32_t *finished = reinterpret_cast<uint32_t *>(full + 2);                 // [2] warps done with a buffer
+  // staging row of one sample (one output per leaf): G trees, padded against bank conflicts; dense when
+  // the area holds the TMA boxes, so that a sample group's rows stay inside its own box
+  const int row_floats = a.tma_store != 0 ? G : G + 1;
+  unsigned char *base = smem + ((1024u - (smem_addr(smem) & 1023u)) & 1023u);
+  float *outs = reinterpret_cast<float *>(base);
+  float *xs = reinterpret_cast<float *>(base + results_bytes(WREC, S, G));
+  unsigned char *params = reinterpret_cast<unsigned char *>(xs + (size_t)C * S);
+  uint64_t *full = reinterpret_cast<uint64_t *>(params + 2 * (size_t)G * lay.bytes);  // [2] copy landed
+  uint32_t *finished = reinterpret_cast<uint32_t *>(full + 2);                         // [2] warps done with a buffer
 
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -201,6 +214,13 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
   const bool streamlined = WREC && one_piece && per_warp == 4;
   const uint32_t warp_records = (uint32_t)(slot * per_warp) * lay.bytes;
   float *stage_mine = stage + lane * row_floats + slot * per_warp;
+  // TMA form of the streamlined body: this sample group's box of 32 rows x G floats, and where this
+  // lane's 4 results (chunk `slot` of row `lane`) sit in it
+  const bool tma_store = streamlined && a.tma_store != 0;
+  const bool store_issuer = tma_store && slot == 0 && lane == 0;
+  const uint32_t box_addr = smem_addr(outs) + (uint32_t)sample_group * 32u * (uint32_t)G * 4u;
+  const uint32_t box_mine = box_addr + (G == 16 ? tma::swizzled_offset<16>((uint32_t)lane, (uint32_t)slot)
+                                                : tma::swizzled_offset<32>((uint32_t)lane, (uint32_t)slot));
 
   // This warp no longer reads parameter buffer (it & 1).  The last warp to say so refills it.
   auto done_with_buffer = [&](int it) {
@@ -226,11 +246,25 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
     const uint32_t base_addr = params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes;
     if (streamlined && in_group == G) {
       uint32_t rec[4], unused[4];
-      float result[4];
+      float result[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int u = 0; u < 4; ++u) rec[u] = base_addr + warp_records + (uint32_t)u * lay.bytes;
-      walk<KIND, DEPTH, OrdT, 4, WREC>(rec, xl_addr, x_stride, result, unused);
+      if (!poisoned) walk<KIND, DEPTH, OrdT, 4, WREC>(rec, xl_addr, x_stride, result, unused);  // a buffer that never arrived is not read
       done_with_buffer(it);
+      if (tma_store) {
+        // The sample group's [32 samples x G trees] block goes to shared memory in the swizzled box layout
+        // (a lane writes the 16 bytes of its own row: conflict free) and leaves as ONE tiled TMA store.
+        if (store_issuer) tma::wait_stores_read();  // the previous box has been read out of the staging area
+        named_barrier(1 + sample_group, group_threads);
+        sts_b128(box_mine, result[0], result[1], result[2], result[3]);
+        tma::fence_async_shared();
+        named_barrier(1 + sample_group, group_threads);  // box complete and visible to the TMA engine
+        if (store_issuer) {
+          tma::store_2d(&a.out_map, box_addr, group * G, (int)(row0 + sample_group * 32));
+          tma::commit_group();
+        }
+        continue;
+      }
       named_barrier(1 + sample_group, group_threads);  // previous group's rows have left the staging area
 #pragma unroll
       for (int u = 0; u < 4; ++u) stage_mine[u] = result[u];
@@ -240,10 +274,11 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
             make_float4(piece_src[0], piece_src[1], piece_src[2], piece_src[3]);
       continue;
     }
+    if (store_issuer) tma::wait_stores_read();  // the body below writes the staging area with plain stores
     const int t_first = slot * per_warp;  // this warp's consecutive trees inside the group
     float result[4] = {0.f, 0.f, 0.f, 0.f};
     uint32_t path[4] = {kL, kL, kL, kL};
-    if (t_first < in_group) {
+    if (t_first < in_group && !poisoned) {  // after a lost copy the buffer is not read: zeros leave instead
       // trees beyond the end of a short last group repeat the last valid one (results unused)
       if (per_warp == 4) {
         uint32_t rec[4];
@@ -348,11 +383,12 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(Tiled
       }
     }
   }
+  if (store_issuer) tma::wait_stores_read();  // shared memory stays valid until the last box has been read
 }
 
 template <int KIND, int DEPTH, typename OrdT>
-__global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_inner_kernel(TiledArgs a) {
-  extern __shared__ __align__(128) unsigned char smem[];
+__global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_inner_kernel(const __grid_constant__ TiledArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem[];
   constexpr RecordLayout lay =
       record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), true, paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT)));
   const int S = a.S, G = a.G, C = a.C;
@@ -435,7 +471,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_inner_kernel
     const int in_group = (int)min((int64_t)G, a.T - (int64_t)group * G);
     const uint32_t base_addr = params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes;
     float result[4] = {0.f, 0.f, 0.f, 0.f};
-    if (t_first < in_group) {
+    if (t_first < in_group && !poisoned) {
       uint32_t rec[4], unused[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) rec[u] = base_addr + (uint32_t)min(t_first + u, in_group - 1) * lay.bytes;
@@ -531,7 +567,7 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
     repack_records_kernel<uint16_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p->kind, p->depth, p->T, plan.rec);
   HT_CHECK_LAUNCH();
 
-  TiledArgs a;
+  TiledArgs a = {};
   a.x = x;
   a.records = rec;
   a.w = w;
@@ -545,6 +581,12 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
   a.S = plan.S;
   a.G = plan.G;
   a.per_warp = plan.per_warp;
+  // Full groups of 16 or 32 trees leave as tiled TMA stores when the output admits a tensor map
+  // (rows of a multiple of 16 bytes); otherwise, and for a short last group, as row segments.
+  a.tma_store = 0;
+  if (tune("HT_TUNE_TMA_STORE", 1) && p->K == 1 && p->M == 1 && plan.per_warp == 4 && (plan.G == 16 || plan.G == 32) && (p->T & 3) == 0 &&
+      p->T >= plan.G && tma::encode_matrix_f32(&a.out_map, out, p->B, p->T, 32, plan.G))
+    a.tma_store = 1;
   // With few sample tiles the tree groups are split among CTAs (grid.y) so that the SMs are busy in
   // every round; every split re-stages the feature tile, which is cheap next to the walk.
   const int64_t tiles = (p->B * p->K + plan.S - 1) / plan.S;

@@ -18,8 +18,10 @@
 // There is no block-wide barrier after the feature tile has been staged.
 #include "ht_forest_tiled.cuh"
 #include "ht_tile_common.cuh"
+#include "ht_tma.cuh"
 
 #include <algorithm>
+#include <type_traits>
 
 namespace ht {
 
@@ -39,6 +41,13 @@ struct BwdPlan {
   size_t smem;
 };
 
+// Shared-memory layout of forest_backward_tiled_kernel, from a 1024-byte boundary: the box of upstream
+// gradients of the current tree group [S samples x G trees] (filled by a tiled TMA load when the
+// gradient admits a tensor map), the feature tile, two parameter buffers, the barriers.
+__host__ __device__ inline size_t gradient_box_bytes(int S, int G) {
+  return ((size_t)S * G * 4 + 1023) & ~(size_t)1023;
+}
+
 // paired: the record path, whose kernels never look a feature index up by vertex, takes the paired form
 bool make_bwd_plan(const ht_forest_problem *p, BwdPlan &plan, bool paired = false) {
   if (p->K < 1 || p->M != 1) return false;  // a sample is a (row, inner position) pair
@@ -54,22 +63,23 @@ bool make_bwd_plan(const ht_forest_problem *p, BwdPlan &plan, bool paired = fals
       plan.S = S;
       plan.G = G;
       plan.per_warp = per_warp;
-      plan.smem = (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + 64;
+      plan.smem = 1024 + gradient_box_bytes(S, G) + (size_t)p->C * S * 4 + 2 * (size_t)G * plan.rec.bytes + 64;
       if (plan.smem <= kSmemBudget) return true;
     }
   }
   return false;
 }
 
-// Per-evaluation results of the traversal kernel, laid out [sample block of 256][tree][256] so that
-// the x-gradient reduction streams each sample block's records sequentially and the parameter
-// reduction reads 1 KB runs: `dx` is the term sign * w * g (the x-gradient term; the threshold term is -dx),
-// `dw` is |margin| * g (the leaf-weight term), `where` packs the deciding vertex (1-based, low 16
-// bits) and the reference leaf key (high 16 bits).
+// Per-evaluation results of the traversal kernel, each array laid out [sample block of 256][tree][256] so
+// that the x-gradient reduction streams each sample block's records sequentially and the parameter
+// reduction reads contiguous runs: `dx` is the term sign * w * g (the x-gradient term; the threshold term
+// is -dx), `dw` is |margin| * g (the leaf-weight term), `where` packs the deciding vertex (1-based) and the
+// reference leaf key — 8 + 8 bits for depths up to 8, 16 + 16 bits beyond.  The reductions move 10 or 12
+// bytes per evaluation through HBM and are bound by it, so every byte saved here is time saved there.
 struct EvalRecords {
   float *dx;
   float *dw;
-  uint32_t *where;
+  void *where;
 };
 
 constexpr int kRecordBlock = 256;
@@ -78,12 +88,49 @@ __host__ __device__ inline int64_t record_index(int64_t sample, int64_t tree, in
   return ((sample / kRecordBlock) * trees + tree) * kRecordBlock + (sample % kRecordBlock);
 }
 
-inline size_t record_array_bytes(const ht_forest_problem *p) {
+inline size_t record_array_bytes(const ht_forest_problem *p, size_t element) {
   const int64_t blocks = (p->B * p->K + kRecordBlock - 1) / kRecordBlock;
-  return align_up((size_t)(blocks * kRecordBlock * p->T) * 4, 256);
+  return align_up((size_t)(blocks * kRecordBlock * p->T) * element, 256);
+}
+inline size_t where_bytes(int depth) { return depth <= 8 ? 2 : 4; }
+
+// `where` as the kernels use it: vertex in the low 16 bits, leaf key in the high 16.
+template <typename WT>
+__device__ __forceinline__ void store_where(void *base, int64_t at, uint32_t vertex, uint32_t key) {
+  if (sizeof(WT) == 2)
+    __stcs(static_cast<unsigned short *>(base) + at, (unsigned short)(vertex | (key << 8)));
+  else
+    __stcs(static_cast<uint32_t *>(base) + at, vertex | (key << 16));
+}
+// Streaming loads as volatile statements: the compiler keeps a batch of them together at the point
+// where the prefetch was written instead of sinking each load to its first use.
+__device__ __forceinline__ float stream_f32(const float *p) {
+  float v;
+  asm volatile("ld.global.cs.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+template <typename WT>
+__device__ __forceinline__ uint32_t stream_raw_where(const void *base, int64_t at) {
+  uint32_t v;
+  if (sizeof(WT) == 2)
+    asm volatile("ld.global.cs.u16 %0, [%1];" : "=r"(v) : "l"(static_cast<const unsigned short *>(base) + at));
+  else
+    asm volatile("ld.global.cs.u32 %0, [%1];" : "=r"(v) : "l"(static_cast<const uint32_t *>(base) + at));
+  return v;
+}
+template <typename WT>
+__device__ __forceinline__ uint32_t unpack_where(uint32_t raw) {
+  return sizeof(WT) == 2 ? (raw & 0xffu) | ((raw >> 8) << 16) : raw;
+}
+template <typename WT>
+__device__ __forceinline__ uint32_t load_where(const void *base, int64_t at) {
+  return unpack_where<WT>(stream_raw_where<WT>(base, at));
 }
 
+
 struct BwdArgs {
+  CUtensorMap g_map;  // the upstream gradient [B, T] in boxes of S rows x G trees (when tma_g is set)
+  int tma_g;
   const float *x;
   const unsigned char *records;
   const float *g;
@@ -95,17 +142,20 @@ struct BwdArgs {
 };
 
 template <int KIND, int DEPTH, typename OrdT, bool RECORDS>
-__global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdArgs a) {
-  extern __shared__ __align__(128) unsigned char smem[];
+__global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(const __grid_constant__ BwdArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem[];
   constexpr bool kPaired = RECORDS && paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT));
   constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), true, kPaired);
   constexpr uint32_t kN = KIND == FERN ? DEPTH : (1u << DEPTH) - 1u;
   constexpr uint32_t kL = 1u << DEPTH;
+  using WhereT = typename std::conditional<(DEPTH <= 8), unsigned short, uint32_t>::type;
   const int S = a.S, G = a.G, C = a.C;
-  float *xs = reinterpret_cast<float *>(smem);
+  unsigned char *base = smem + ((1024u - (smem_addr(smem) & 1023u)) & 1023u);
+  const uint32_t g_box = smem_addr(base);
+  float *xs = reinterpret_cast<float *>(base + gradient_box_bytes(S, G));
   unsigned char *params = reinterpret_cast<unsigned char *>(xs + (size_t)C * S);
-  uint64_t *full = reinterpret_cast<uint64_t *>(params + 2 * (size_t)G * lay.bytes);
-  uint32_t *finished = reinterpret_cast<uint32_t *>(full + 2);
+  uint64_t *full = reinterpret_cast<uint64_t *>(params + 2 * (size_t)G * lay.bytes);  // [2] parameters landed, [1] gradients landed
+  uint32_t *finished = reinterpret_cast<uint32_t *>(full + 3);                        // [2] warps done with a buffer, [1] with the gradients
 
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -130,14 +180,25 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
     bulk_load(params_addr + (uint32_t)(it & 1) * (uint32_t)G * lay.bytes, a.records + first_tree * lay.bytes, bytes,
               bar);
   };
+  // The upstream gradients of a full tree group arrive as one box [S samples x G trees] through the
+  // TMA engine, one group ahead: the last warp to have taken its values out of the box requests the next.
+  const int full_groups_all = (int)(a.T / G);
+  const bool tma_g = RECORDS && a.tma_g != 0;
+  auto issue_gradients = [&](int it) {
+    mbar_expect_tx(&full[2], (uint32_t)(S * G * 4));
+    tma::load_2d(g_box, &a.g_map, (group0 + it) * G, (int)row0, &full[2]);
+  };
   if (tid == 0) {
     mbar_init(&full[0], 1);
     mbar_init(&full[1], 1);
+    mbar_init(&full[2], 1);
     finished[0] = 0;
     finished[1] = 0;
+    finished[2] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (num_groups > 0) issue(0);
     if (num_groups > 1) issue(1);
+    if (tma_g && num_groups > 0 && group0 < full_groups_all) issue_gradients(0);
   }
 
   // features in
@@ -185,6 +246,9 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
   const bool streamlined = RECORDS && per_warp == 4 && (a.T & 3) == 0 && a.K == 1;
   const uint32_t warp_records = (uint32_t)(slot * per_warp) * lay.bytes;
   const float *g_mine = a.g + my_row * a.T + slot * per_warp;
+  // this lane's 4 gradients in the swizzled box: row = sample inside the tile, 16-byte chunk = slot
+  const uint32_t g_mine_box = g_box + (G == 16 ? tma::swizzled_offset<16>((uint32_t)my_sample, (uint32_t)slot)
+                                              : tma::swizzled_offset<32>((uint32_t)my_sample, (uint32_t)slot));
   const int64_t records_mine = my_records + (int64_t)(slot * per_warp) * kRecordBlock;
 
   // This warp no longer reads parameter buffer (it & 1).  The last warp to say so refills it.
@@ -207,7 +271,28 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
     const int64_t col0 = (int64_t)group * G;
     if (streamlined && in_group == G) {
       float4 gq = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row_valid) gq = __ldg(reinterpret_cast<const float4 *>(g_mine + col0));  // requested before the walk
+      if (tma_g) {
+        if (!poisoned && !mbar_wait(&full[2], (uint32_t)(it & 1))) {
+          poisoned = true;
+          if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
+        }
+        if (!poisoned) {
+          const uint4 q = lds_b128(g_mine_box);
+          gq = make_float4(__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w));
+        }
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          const uint32_t before = atomicAdd(&finished[2], 1u);
+          if (before == kWarps - 1) {
+            atomicExch(&finished[2], 0u);
+            __threadfence_block();
+            if (it + 1 < num_groups && group + 1 < full_groups_all && !poisoned) issue_gradients(it + 1);
+          }
+        }
+      } else if (row_valid) {
+        gq = __ldg(reinterpret_cast<const float4 *>(g_mine + col0));  // requested before the walk
+      }
       if (!poisoned && !mbar_wait(&full[it & 1], (uint32_t)((it >> 1) & 1))) {
         poisoned = true;
         if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
@@ -229,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
           if (row_valid) {
             __stcs(a.evals.dx + at + u * kRecordBlock, dx);
             __stcs(a.evals.dw + at + u * kRecordBlock, __fmul_rn(fabsf(wk[u].nm), gval[u]));
-            __stcs(a.evals.where + at + u * kRecordBlock, wk[u].v | (key << 16));
+            store_where<WhereT>(a.evals.where, at + u * kRecordBlock, wk[u].v, key);
           }
         }
       }
@@ -279,7 +364,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(BwdA
           const int64_t at = my_records + j * kRecordBlock;
           a.evals.dx[at] = dx;
           a.evals.dw[at] = __fmul_rn(fabsf(wk.nm), gv);
-          a.evals.where[at] = wk.v | (key << 16);
+          store_where<WhereT>(a.evals.where, at, wk.v, key);
           return;
         }
         if (a.gx != nullptr) {
@@ -367,7 +452,7 @@ __device__ __forceinline__ void lanes_in_order_per_key(bool valid, uint32_t key,
 // with shuffles in a logarithmic number of rounds, and the lowest lane of each bin updates it once;
 // the ordered form pays one dependent round per lane of the fullest bin, and a few bins (the root
 // threshold, the likeliest leaves) collect a third of the lanes of a typical chunk.
-template <bool ORDERED>
+template <bool ORDERED, typename WT>
 __global__ void __launch_bounds__(512) reduce_parameter_records_kernel(EvalRecords r, int64_t B, int64_t T, int64_t N,
                                                                        int64_t L, float *gthr, float *gw) {
   extern __shared__ float all_bins[];
@@ -391,7 +476,7 @@ __global__ void __launch_bounds__(512) reduce_parameter_records_kernel(EvalRecor
       const bool valid = i0 + 32 * u + lane < B;
       fa[u] = valid ? __ldcs(r.dx + first + 32 * u) : 0.0f;
       fb[u] = valid ? __ldcs(r.dw + first + 32 * u) : 0.0f;
-      fw[u] = valid ? __ldcs(r.where + first + 32 * u) : 1u;
+      fw[u] = valid ? load_where<WT>(r.where, first + 32 * u) : 1u;
     }
   };
   int64_t i0 = (int64_t)warp * 32 * kAhead;
@@ -445,7 +530,7 @@ __global__ void __launch_bounds__(512) reduce_parameter_records_kernel(EvalRecor
 // find out which other lanes hit the same bin (a match.any per gradient per chunk bounds the kernel
 // above), and the chains of dependent updates of the hot bins are `columns` times shorter.  The
 // warps' columns are summed in a fixed order at the end: reproducible, another association.
-template <int CHUNKS>
+template <int CHUNKS, typename WT>
 __global__ void __launch_bounds__(512, 1) reduce_parameter_records_columns_kernel(EvalRecords r, int64_t B, int64_t T,
                                                                                   int64_t N, int64_t L, int columns,
                                                                                   float *gthr, float *gw) {
@@ -470,7 +555,7 @@ __global__ void __launch_bounds__(512, 1) reduce_parameter_records_columns_kerne
       const bool valid = i0 + 32 * u + lane < B;
       fa[u] = valid ? __ldcs(r.dx + first + 32 * u) : 0.0f;  // an absent sample adds zeros to bin 0
       fb[u] = valid ? __ldcs(r.dw + first + 32 * u) : 0.0f;
-      fw[u] = valid ? __ldcs(r.where + first + 32 * u) : 1u;
+      fw[u] = valid ? load_where<WT>(r.where, first + 32 * u) : 1u;
     }
   };
   int64_t i0 = (int64_t)warp * 32 * CHUNKS;
@@ -515,9 +600,123 @@ __global__ void __launch_bounds__(512, 1) reduce_parameter_records_columns_kerne
   }
 }
 
+// Default mode, trees whose bins fit 16 or 32 times into a third or a sixth of the shared memory: ONE
+// warp per CTA with COLUMNS copies of the tree's bins, [bin][column].  With 32 columns a lane owns its
+// column outright; with 16, lanes l and l + 16 share one and take two turns.  Either way the lanes that
+// are active together hit distinct banks whatever bins they update, so every load and store is one
+// wavefront for up to 32 terms (the 8-column form above pays a wavefront per 8 terms and a conflict
+// on top).  A lane consumes its records four at a time: the eight bin loads are in flight together,
+// the sums are chained in record order (a later record that hits the bin of an earlier one of the four
+// continues from its sum), and the stores leave in order, so each lane's column holds exactly the
+// sequential sum of its terms.  The samples are split over gridDim.y; a CTA adds its column totals (in a
+// fixed order per bin) to the gradient with one global reduction per bin, or stores them when there is one split.
+template <int COLUMNS, int CHUNKS, typename WT>
+__global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(EvalRecords r, int64_t B, int64_t T, int N,
+                                                                              int L, int64_t blocks_per_split, float *gthr,
+                                                                              float *gw) {
+  extern __shared__ float all_bins[];  // [bin][column]
+  static_assert(CHUNKS % 8 == 0 && kRecordBlock == 256, "a fetch covers whole record blocks");
+  constexpr int kTurns = 32 / COLUMNS;
+  constexpr int kBlocksPerFetch = CHUNKS / 8;
+  const unsigned lane = threadIdx.x;
+  const int bins = N + L;
+  const int64_t j = blockIdx.x;
+  for (int t = (int)lane; t < bins * COLUMNS; t += 32) all_bins[t] = 0.0f;
+  __syncwarp();
+  const uint32_t my_column = smem_addr(all_bins) + (lane % COLUMNS) * 4u;
+  const int my_turn = (int)lane / COLUMNS;
+  const int64_t all_blocks = (B + kRecordBlock - 1) / kRecordBlock;
+  const int64_t block_first = (int64_t)blockIdx.y * blocks_per_split;
+  const int64_t block_last = min(all_blocks, block_first + blocks_per_split);
+
+  float a[CHUNKS], b[CHUNKS], na[CHUNKS], nb[CHUNKS];
+  uint32_t wh[CHUNKS], nwh[CHUNKS];
+  auto fetch = [&](int64_t blk, float (&fa)[CHUNKS], float (&fb)[CHUNKS], uint32_t (&fw)[CHUNKS]) {
+#pragma unroll
+    for (int h = 0; h < kBlocksPerFetch; ++h) {
+      const int64_t first = ((blk + h) * T + j) * kRecordBlock + lane;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool valid = blk + h < block_last && (blk + h) * kRecordBlock + 32 * u + lane < B;
+        fa[8 * h + u] = 0.0f;  // an absent sample adds zeros to bin 0
+        fb[8 * h + u] = 0.0f;
+        fw[8 * h + u] = sizeof(WT) == 2 ? 1u : 1u;  // raw form of vertex 1, leaf 0
+        if (valid) {
+          fa[8 * h + u] = stream_f32(r.dx + first + 32 * u);
+          fb[8 * h + u] = stream_f32(r.dw + first + 32 * u);
+          fw[8 * h + u] = stream_raw_where<WT>(r.where, first + 32 * u);
+        }
+      }
+    }
+  };
+  int64_t blk = block_first;
+  if (blk < block_last) fetch(blk, a, b, wh);
+  for (; blk < block_last; blk += kBlocksPerFetch) {
+    if (blk + kBlocksPerFetch < block_last) fetch(blk + kBlocksPerFetch, na, nb, nwh);
+#pragma unroll
+    for (int q = 0; q < CHUNKS; q += 4) {
+      uint32_t at_thr[4], at_w[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t where = unpack_where<WT>(wh[q + u]);
+        at_thr[u] = my_column + ((where & 0xffffu) - 1u) * (uint32_t)(COLUMNS * 4);
+        at_w[u] = my_column + ((uint32_t)N + (where >> 16)) * (uint32_t)(COLUMNS * 4);
+      }
+#pragma unroll
+      for (int turn = 0; turn < kTurns; ++turn) {
+        if (kTurns == 1 || turn == my_turn) {
+          float st[4], sw[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            st[u] = lds_f32(at_thr[u]);
+            sw[u] = lds_f32(at_w[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+#pragma unroll
+            for (int e = 0; e < u; ++e) {  // the latest earlier record of the four on the same bin, if any
+              st[u] = at_thr[u] == at_thr[e] ? st[e] : st[u];
+              sw[u] = at_w[u] == at_w[e] ? sw[e] : sw[u];
+            }
+            st[u] = __fadd_rn(st[u], -a[q + u]);
+            sw[u] = __fadd_rn(sw[u], b[q + u]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (gthr != nullptr) sts_f32(at_thr[u], st[u]);
+            if (gw != nullptr) sts_f32(at_w[u], sw[u]);
+          }
+        }
+        if (kTurns > 1) __syncwarp();
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < CHUNKS; ++u) {
+      a[u] = na[u];
+      b[u] = nb[u];
+      wh[u] = nwh[u];
+    }
+  }
+  __syncwarp();
+  for (int t = (int)lane; t < bins; t += 32) {
+    float sum = 0.0f;
+#pragma unroll 8
+    for (int c = 0; c < COLUMNS; ++c) sum = __fadd_rn(sum, all_bins[t * COLUMNS + ((c + (int)lane) % COLUMNS)]);
+    float *dst = t < N ? (gthr == nullptr ? nullptr : gthr + j * N + t) : (gw == nullptr ? nullptr : gw + j * L + (t - N));
+    if (dst == nullptr) continue;
+    if (gridDim.y == 1)
+      *dst = sum;
+    else
+      atomicAdd(dst, sum);
+  }
+}
+
 // x gradient: one thread per sample walks the trees in ascending order and adds into its private
-// column of a shared-memory tile gx[c][s]; the tile leaves with plain stores.
+// column of a shared-memory tile gx[c][s]; the tile leaves with plain stores.  Per evaluation it reads
+// the term and the deciding vertex (6 or 8 bytes) and looks the vertex's feature up in the compact
+// ordinal table, which every thread of the CTA walks in the same order (L1 / L2 resident).
 // B: samples (rows x inner positions), K: inner positions per row.
+template <typename WT>
 __global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, const int32_t *__restrict__ ord, int64_t B,
                                                                int64_t K, int64_t T, int64_t N, int C, int S, float *gx) {
   extern __shared__ float tile[];
@@ -527,35 +726,40 @@ __global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, co
   __syncthreads();
   const int64_t i = row0 + s;
   if (s < S && i < B) {
-    // batches of kAhead trees; the next batch (records and feature indices) is requested before
-    // the current one is added
+    // three stages in flight: records of batch n+2, feature indices of batch n+1, additions of batch n
     constexpr int kAhead = 16;
     const int64_t first = record_index(i, 0, T);  // tree j of this sample sits at first + j * 256
-    // three stages in flight: records of batch n+2, feature indices of batch n+1, additions of batch n
     float a0[kAhead], a1[kAhead], a2[kAhead];
     uint32_t wh1[kAhead], wh2[kAhead];
-    int c0[kAhead], c1[kAhead];
+    uint32_t c0[kAhead], c1[kAhead];
     auto fetch_records = [&](int64_t j0, float (&fa)[kAhead], uint32_t (&fw)[kAhead]) {
 #pragma unroll
       for (int u = 0; u < kAhead; ++u) {
-        const bool valid = j0 + u < T;
-        fa[u] = valid ? __ldcs(r.dx + first + (j0 + u) * kRecordBlock) : 0.0f;
-        fw[u] = valid ? __ldcs(r.where + first + (j0 + u) * kRecordBlock) : 1u;
+        fa[u] = 0.0f;
+        fw[u] = 1u;
+        if (j0 + u < T) {
+          fa[u] = stream_f32(r.dx + first + (j0 + u) * kRecordBlock);
+          fw[u] = stream_raw_where<WT>(r.where, first + (j0 + u) * kRecordBlock);
+        }
       }
     };
-    auto fetch_features = [&](int64_t j0, const uint32_t (&fw)[kAhead], int (&fc)[kAhead]) {
+    auto fetch_features = [&](int64_t j0, const uint32_t (&fw)[kAhead], uint32_t (&fc)[kAhead]) {
 #pragma unroll
-      for (int u = 0; u < kAhead; ++u) fc[u] = j0 + u < T ? __ldg(ord + (j0 + u) * N + ((fw[u] & 0xffffu) - 1u)) : 0;
+      for (int u = 0; u < kAhead; ++u)
+        fc[u] = j0 + u < T ? (uint32_t)__ldg(ord + (j0 + u) * N + ((unpack_where<WT>(fw[u]) & 0xffffu) - 1u)) : 0u;
     };
     fetch_records(0, a0, wh1);
     fetch_features(0, wh1, c0);
     fetch_records(kAhead, a1, wh1);
+    const uint32_t column = smem_addr(tile + s), pitch = (uint32_t)S * 4u;
     for (int64_t j0 = 0; j0 < T; j0 += kAhead) {
       fetch_records(j0 + 2 * kAhead, a2, wh2);
       fetch_features(j0 + kAhead, wh1, c1);
 #pragma unroll
-      for (int u = 0; u < kAhead; ++u)
-        if (j0 + u < T) tile[c0[u] * S + s] = __fadd_rn(tile[c0[u] * S + s], a0[u]);
+      for (int u = 0; u < kAhead; ++u) {  // beyond the last tree: zero into feature 0
+        const uint32_t at = column + c0[u] * pitch;
+        sts_f32(at, __fadd_rn(lds_f32(at), a0[u]));
+      }
 #pragma unroll
       for (int u = 0; u < kAhead; ++u) {
         a0[u] = a1[u];
@@ -616,12 +820,67 @@ int launch_kind(int depth, const BwdPlan &plan, const BwdArgs &a, dim3 grid, cud
   }
 }
 
+// Launches the threshold / leaf-weight reduction that fits the mode and the tree size.
+template <typename WT>
+int reduce_parameters(const ht_forest_problem *p, const EvalRecords &evals, int64_t samples, int64_t N, int64_t L,
+                      float *gthr, float *gw, cudaStream_t stream) {
+  // fixed-order mode: one warp per tree, the reference's sequential sum.  Default mode: as many
+  // warps as help (each needs work and its own bins), summed in warp order.
+  int warps = 1;
+  if ((p->flags & HT_DETERMINISTIC) == 0) {
+    warps = 16;
+    while (warps > 1 && ((size_t)warps * (N + L) * 4 > 64 * 1024 || samples < (int64_t)warps * 512)) warps >>= 1;
+  }
+  const size_t smem = sizeof(float) * (size_t)(N + L) * warps;
+  if ((p->flags & HT_DETERMINISTIC) != 0) {
+    HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<true, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kSmemBudget));
+    reduce_parameter_records_kernel<true, WT><<<(unsigned)p->T, 32 * warps, smem, stream>>>(evals, samples, p->T, N, L, gthr, gw);
+    HT_CHECK_LAUNCH();
+    return HT_OK;
+  }
+  // copies of the bins per warp (a power of two, at most one per lane) that `column_warps` warps can hold
+  const int column_warps = kColumnWarps;
+  int columns = 32;
+  while (columns > 1 && (size_t)column_warps * (N + L) * columns * 4 > 200 * 1024) columns >>= 1;
+  // bins that fit 16 times into a sixth of the shared memory: one warp per CTA, each column shared by two
+  // lanes, samples split over gridDim.y so that the machine sees several waves of CTAs
+  const size_t bins = (size_t)(N + L);
+  int private_columns = bins * 16 * 4 <= 36 * 1024 ? 16 : 0;
+  if (tune("HT_TUNE_PRIVATE", 16) != 16) private_columns = tune("HT_TUNE_PRIVATE", 16);
+  if (private_columns != 0 && samples >= 64 * 1024) {
+    const size_t private_smem = bins * private_columns * 4;
+    const int64_t slots = 148 * (int64_t)(kSmemBudget / (private_smem + 1024));
+    const int64_t all_blocks = (samples + kRecordBlock - 1) / kRecordBlock;
+    int64_t splits = std::max<int64_t>(1, std::min<int64_t>((6 * slots + p->T - 1) / p->T, all_blocks / 16));
+    splits = std::min<int64_t>(splits, 65535);
+    const int64_t blocks_per_split = ((all_blocks + splits - 1) / splits + 1) / 2 * 2;  // whole fetches of 2 blocks
+    const dim3 reduce_grid((unsigned)p->T, (unsigned)((all_blocks + blocks_per_split - 1) / blocks_per_split));
+    auto kernel = private_columns == 32 ? reduce_parameter_records_private_kernel<32, 16, WT>
+                                        : reduce_parameter_records_private_kernel<16, 16, WT>;
+    HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    kernel<<<reduce_grid, 32, private_smem, stream>>>(evals, samples, p->T, (int)N, (int)L, blocks_per_split, gthr, gw);
+  } else if (warps == 16 && columns >= 4) {
+    const size_t column_smem = (size_t)column_warps * (N + L) * columns * 4;
+    HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_columns_kernel<8, WT>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    reduce_parameter_records_columns_kernel<8, WT><<<(unsigned)p->T, 32 * column_warps, column_smem, stream>>>(
+        evals, samples, p->T, N, L, columns, gthr, gw);
+  } else {
+    HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<false, WT>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    reduce_parameter_records_kernel<false, WT><<<(unsigned)p->T, 32 * warps, smem, stream>>>(evals, samples, p->T, N, L, gthr, gw);
+  }
+  HT_CHECK_LAUNCH();
+  return HT_OK;
+}
+
 }  // namespace
 
 size_t backward_records_bytes(const ht_forest_problem *p) {
   BwdPlan plan;
   if (!make_bwd_plan(p, plan) || p->depth > 15) return 0;
-  const size_t bytes = 3 * record_array_bytes(p);
+  const size_t bytes = 2 * record_array_bytes(p, 4) + record_array_bytes(p, where_bytes(p->depth));
   return bytes <= ((size_t)32 << 30) ? bytes : 0;
 }
 
@@ -644,7 +903,7 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
   else
     repack_records_kernel<uint16_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p->kind, p->depth, p->T, plan.rec);
   HT_CHECK_LAUNCH();
-  BwdArgs a;
+  BwdArgs a = {};
   a.x = x;
   a.records = rec;
   a.g = g;
@@ -653,10 +912,9 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
   a.gw = gw;
   a.evals = EvalRecords{nullptr, nullptr, nullptr};
   if (eval_records != nullptr) {
-    const size_t stride = record_array_bytes(p);
+    const size_t floats = record_array_bytes(p, 4);
     unsigned char *base = static_cast<unsigned char *>(eval_records);
-    a.evals = EvalRecords{reinterpret_cast<float *>(base), reinterpret_cast<float *>(base + stride),
-                          reinterpret_cast<uint32_t *>(base + 2 * stride)};
+    a.evals = EvalRecords{reinterpret_cast<float *>(base), reinterpret_cast<float *>(base + floats), base + 2 * floats};
   }
   a.status_word = status_word;
   a.B = p->B * p->K;
@@ -666,6 +924,11 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
   a.S = plan.S;
   a.G = plan.G;
   a.per_warp = plan.per_warp;
+  // record path, tabular input, groups of 16 or 32 trees: the upstream gradient comes in by tiled TMA loads
+  a.tma_g = 0;
+  if (tune("HT_TUNE_TMA_G", 1) && eval_records != nullptr && p->K == 1 && plan.per_warp == 4 && (plan.G == 16 || plan.G == 32) && (p->T & 3) == 0 &&
+      p->T >= plan.G && tma::encode_matrix_f32(&a.g_map, g, p->B, p->T, plan.S, plan.G))
+    a.tma_g = 1;
   // a small batch gives too few sample tiles for 148 SMs: share the tree groups between CTAs
   const int64_t samples = p->B * p->K;
   const int64_t tiles = (samples + plan.S - 1) / plan.S;
@@ -677,46 +940,19 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
   if (rc != HT_OK || eval_records == nullptr) return rc;
 
   if (gthr != nullptr || gw != nullptr) {
-    // fixed-order mode: one warp per tree, the reference's sequential sum.  Default mode: as many
-    // warps as help (each needs work and its own bins), summed in warp order.
-    int warps = 1;
-    if ((p->flags & HT_DETERMINISTIC) == 0) {
-      warps = 16;
-      while (warps > 1 && ((size_t)warps * (N + L) * 4 > 64 * 1024 || samples < (int64_t)warps * 512)) warps >>= 1;
-    }
-    const size_t smem = sizeof(float) * (size_t)(N + L) * warps;
-    if ((p->flags & HT_DETERMINISTIC) != 0) {
-      HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)kSmemBudget));
-      reduce_parameter_records_kernel<true><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, samples, p->T, N, L, gthr, gw);
-    } else {
-      // copies of the bins per warp (a power of two, at most one per lane) that `column_warps` warps can hold
-      const int column_warps = kColumnWarps;
-      int columns = 32;
-      while (columns > 1 && (size_t)column_warps * (N + L) * columns * 4 > 200 * 1024) columns >>= 1;
-      if (warps == 16 && columns >= 4) {
-        const size_t column_smem = (size_t)column_warps * (N + L) * columns * 4;
-        HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_columns_kernel<8>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-        reduce_parameter_records_columns_kernel<8><<<(unsigned)p->T, 32 * column_warps, column_smem, stream>>>(
-            a.evals, samples, p->T, N, L, columns, gthr, gw);
-      } else {
-        HT_CUDA_TRY(cudaFuncSetAttribute(reduce_parameter_records_kernel<false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-        reduce_parameter_records_kernel<false><<<(unsigned)p->T, 32 * warps, smem, stream>>>(a.evals, samples, p->T, N, L, gthr,
-                                                                                            gw);
-      }
-    }
-    HT_CHECK_LAUNCH();
+    const int prc = where_bytes(p->depth) == 2
+                        ? reduce_parameters<unsigned short>(p, a.evals, samples, N, L, gthr, gw, stream)
+                        : reduce_parameters<uint32_t>(p, a.evals, samples, N, L, gthr, gw, stream);
+    if (prc != HT_OK) return prc;
   }
   if (gx != nullptr) {
     int S = 128;  // 3 CTAs per SM at 128 features: the walk over the trees is latency bound
     while (S > 32 && (size_t)S * p->C * 4 > 200 * 1024) S >>= 1;
     const size_t smem = (size_t)S * p->C * 4;
     if (smem > kSmemBudget) return HT_ERR_UNSUPPORTED;
-    HT_CUDA_TRY(cudaFuncSetAttribute(reduce_x_records_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
-    reduce_x_records_kernel<<<(unsigned)((samples + S - 1) / S), S, smem, stream>>>(a.evals, ord, samples, p->K, p->T, N,
-                                                                                    (int)p->C, S, gx);
+    auto kernel = where_bytes(p->depth) == 2 ? reduce_x_records_kernel<unsigned short> : reduce_x_records_kernel<uint32_t>;
+    HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+    kernel<<<(unsigned)((samples + S - 1) / S), S, smem, stream>>>(a.evals, ord, samples, p->K, p->T, N, (int)p->C, S, gx);
     HT_CHECK_LAUNCH();
   }
   return HT_OK;

@@ -175,6 +175,10 @@ __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
   asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
+__device__ __forceinline__ void sts_b128(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 __device__ __forceinline__ uint32_t lds_b32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -299,13 +303,14 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
 // reference's strict `<` so that the shallowest minimum wins.
 struct Walked {
   float nm;      // threshold - feature at the deciding vertex (the negated signed margin)
-  uint32_t v;    // 1-based index of the deciding vertex (ferns: level + 1)
+  uint32_t v;    // 1-based index of the deciding vertex (ferns: level + 1); with WITH_FEATURE the feature that
+                 // vertex tests (as stored in the record) rides in the high 16 bits: one register, one select
   uint32_t path; // 2^DEPTH + path bits, root first (most significant)
 };
 
 // rec[u] and x_addr[u]: record and feature base (shared-memory addresses) of the u-th walk in flight.
 // PAIRED: the records hold the feature indices in the paired form (see paired_ordinals).
-template <int KIND, int DEPTH, typename OrdT, int NT, bool PAIRED = false>
+template <int KIND, int DEPTH, typename OrdT, int NT, bool PAIRED = false, bool WITH_FEATURE = false>
 __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], const uint32_t (&x_addr)[NT], uint32_t x_stride,
                                           Walked (&out)[NT]) {
   constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), true, PAIRED);
@@ -346,7 +351,7 @@ __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], const uint3
       const float nm = thr - lds_f32(c * x_stride + x_addr[u]);
       if (l == 0 || fabsf(nm) < fabsf(out[u].nm)) {
         out[u].nm = nm;
-        out[u].v = at;
+        out[u].v = WITH_FEATURE ? (at | (c << 16)) : at;
       }
       v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
     }
@@ -356,13 +361,13 @@ __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], const uint3
 }
 
 // The same with one feature base for all walks (several trees on one sample or position).
-template <int KIND, int DEPTH, typename OrdT, int NT, bool PAIRED = false>
+template <int KIND, int DEPTH, typename OrdT, int NT, bool PAIRED = false, bool WITH_FEATURE = false>
 __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], uint32_t xl_addr, uint32_t x_stride,
                                           Walked (&out)[NT]) {
   uint32_t x_addr[NT];
 #pragma unroll
   for (int u = 0; u < NT; ++u) x_addr[u] = xl_addr;
-  walk_full<KIND, DEPTH, OrdT, NT, PAIRED>(rec, x_addr, x_stride, out);
+  walk_full<KIND, DEPTH, OrdT, NT, PAIRED, WITH_FEATURE>(rec, x_addr, x_stride, out);
 }
 
 // Sum of `val` over the lanes of the warp whose `key` equals this lane's, delivered in the lowest

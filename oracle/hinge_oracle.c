@@ -27,6 +27,11 @@
 #include <string.h>
 #include <math.h>
 
+#include "hinge_oracle_terms.h"
+
+int ho_magnitude_mode = 0;
+void ho_set_magnitude_mode(int on) { ho_magnitude_mode = on; }
+
 #define HO_TREE 0
 #define HO_FERN 1
 
@@ -145,12 +150,12 @@ int ho_backward(int kind, const float *x, const float *vec, int64_t Cv, const fl
         const int64_t c = ord[j * N + p.vertex];
         for (int64_t m = 0; m < M; ++m) {
           if (gx || gvec) {
-            const float t = sign * wl[m] * gl[m];
+            const float t = ho_term(sign * wl[m] * gl[m]);
             if (vec == NULL || c < C) { if (gx) gx[(i * C + c) * K + k] += t; }
             else if (gvec) gvec[i * Cv + (c - C)] += t;
           }
-          if (gthr) gthr[j * N + p.vertex] += -sign * wl[m] * gl[m];
-          if (gw) gw[(j * L + p.key) * M + m] += fabsf(p.margin) * gl[m];
+          if (gthr) gthr[j * N + p.vertex] += ho_term(-sign * wl[m] * gl[m]);
+          if (gw) gw[(j * L + p.key) * M + m] += ho_term(fabsf(p.margin) * gl[m]);
         }
       }
   return 0;
@@ -237,13 +242,13 @@ int ho_linear_backward(int kind, const float *x, const float *vec, int64_t Cv, c
           const float lw = lin[o * T + j];
           for (int64_t m = 0; m < M; ++m) {
             if (gx || gvec) {
-              const float t = (sign * lw) * wl[m] * gl[m];
+              const float t = ho_term((sign * lw) * wl[m] * gl[m]);
               if (vec == NULL || c < C) { if (gx) gx[(i * C + c) * K + k] += t; }
               else if (gvec) gvec[i * Cv + (c - C)] += t;
             }
-            if (gthr) gthr[j * N + p.vertex] += (-sign * lw) * wl[m] * gl[m];
-            if (gw) gw[(j * L + p.key) * M + m] += (am * lw) * gl[m];
-            if (glin) glin[o * T + j] += am * wl[m] * gl[m];
+            if (gthr) gthr[j * N + p.vertex] += ho_term((-sign * lw) * wl[m] * gl[m]);
+            if (gw) gw[(j * L + p.key) * M + m] += ho_term((am * lw) * gl[m]);
+            if (glin) glin[o * T + j] += ho_term(am * wl[m] * gl[m]);
           }
         }
       }
@@ -252,7 +257,7 @@ int ho_linear_backward(int kind, const float *x, const float *vec, int64_t Cv, c
       double s = 0.0;
       for (int64_t i = 0; i < B; ++i)
         for (int64_t k = 0; k < K; ++k)
-          for (int64_t m = 0; m < M; ++m) s += (double)g[((i * O + o) * K + k) * M + m];
+          for (int64_t m = 0; m < M; ++m) s += (double)ho_term(g[((i * O + o) * K + k) * M + m]);
       gbias[o] = (float)s;
     }
   return 0;

@@ -22,7 +22,8 @@ _lib = None
 
 def build(force=False):
     """Compile the C sources with gcc (no FMA contraction, like the reference's x86-64 -O2 build)."""
-    if force or not os.path.exists(LIB) or os.path.getmtime(LIB) < max(os.path.getmtime(s) for s in SOURCES):
+    inputs = SOURCES + [os.path.join(HERE, "hinge_oracle_terms.h")]
+    if force or not os.path.exists(LIB) or os.path.getmtime(LIB) < max(os.path.getmtime(s) for s in inputs):
         subprocess.run(["gcc", "-O2", "-ffp-contract=off", "-fPIC", "-shared", "-std=c11",
                         "-o", LIB] + SOURCES + ["-lm"], check=True)
     return LIB
@@ -116,6 +117,18 @@ def backward_magnitudes(kind, x, thr, ord_, w, g):
     if rc != 0:
         raise ValueError("leaf count is not a power of two")
     return ax, athr, aw
+
+
+def magnitudes(backward_fn, *args, **kwargs):
+    """Runs one of this module's backward functions (backward, linear_backward, conv_backward,
+    trie_backward) with every term replaced by its absolute value: the result has, per gradient
+    element, the sum of |term| over all contributions (float32), which is what a relative
+    tolerance of a sum computed in another order has to be multiplied with."""
+    lib().ho_set_magnitude_mode(1)
+    try:
+        return backward_fn(*args, **kwargs)
+    finally:
+        lib().ho_set_magnitude_mode(0)
 
 
 def linear_forward(kind, x, thr, ord_, w, lin, bias, vec=None):

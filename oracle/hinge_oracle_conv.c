@@ -16,6 +16,8 @@
 #include <string.h>
 #include <math.h>
 
+#include "hinge_oracle_terms.h"
+
 #define HO_FERN 1
 #define HO_MAX_DIMS 3
 
@@ -136,9 +138,9 @@ int ho_conv_backward(int kind, int dims, const float *x, const float *thr, const
           const float *gl = gout + ((i * Co + j) * g.out_count + p) * M;
           const int64_t idx = ho_cell_index(&g, p, ord[tree * N + r.vertex]);
           for (int64_t m = 0; m < M; ++m) {
-            if (gx && idx >= 0) gx[(i * Ci + c) * g.in_count + idx] += sign * wl[m] * gl[m];
-            if (gthr) gthr[tree * N + r.vertex] += -sign * wl[m] * gl[m];
-            if (gw) gw[(tree * L + r.key) * M + m] += am * gl[m];
+            if (gx && idx >= 0) gx[(i * Ci + c) * g.in_count + idx] += ho_term(sign * wl[m] * gl[m]);
+            if (gthr) gthr[tree * N + r.vertex] += ho_term(-sign * wl[m] * gl[m]);
+            if (gw) gw[(tree * L + r.key) * M + m] += ho_term(am * gl[m]);
           }
         }
       }

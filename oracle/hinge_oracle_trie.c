@@ -9,6 +9,8 @@
 #include <stdint.h>
 #include <math.h>
 
+#include "hinge_oracle_terms.h"
+
 static int ho_trie_depth(int64_t N) {
   const int64_t leaves = N + 1; /* HingeTrieCommon.h:51-64 */
   if (leaves <= 0 || (leaves & (leaves - 1)) != 0) return -1;
@@ -62,9 +64,9 @@ int ho_trie_backward(const float *x, const float *thr, const int64_t *ord, const
           for (int d = 0; d < depth; ++d) {
             const float sign = (float)((0.0f < margin[d]) - (margin[d] < 0.0f));
             const float wv = w[(j * N + vertex[d]) * M + m];
-            if (gx) gx[(i * C + ord[j * N + vertex[d]]) * K + k] += sign * wv * gm;
-            if (gthr) gthr[j * N + vertex[d]] += -sign * wv * gm;
-            if (gw) gw[(j * N + vertex[d]) * M + m] += fabsf(margin[d]) * gm;
+            if (gx) gx[(i * C + ord[j * N + vertex[d]]) * K + k] += ho_term(sign * wv * gm);
+            if (gthr) gthr[j * N + vertex[d]] += ho_term(-sign * wv * gm);
+            if (gw) gw[(j * N + vertex[d]) * M + m] += ho_term(fabsf(margin[d]) * gm);
           }
         }
       }
