@@ -82,6 +82,39 @@ def build(reference, jobs=8, force=False):
     return target
 
 
+def trained_forest_path():
+    return os.path.join(OUT, "trained_forests.npz")
+
+
+def extract_trained_forests(reference, limit=2):
+    """Read the hinge forest parameters (thresholds, ordinals, leaf weights) out of the trained
+    checkpoints the reference ships for its renal-cell-carcinoma example (rcc/Models/*/epoch_*.pt:
+    100 trees of depth 7 over 100 channels, 8 x 8 outputs per leaf, rcc/Net.py:64) into
+    ``oracle/_ref/trained_forests.npz`` so that the parity tests can use realistic, trained
+    parameters wherever ``oracle/_ref`` travels.  Like everything under ``oracle/_ref`` the file is
+    git-ignored: nothing of the reference enters the history."""
+    import glob
+
+    import numpy as np
+    import torch
+
+    files = sorted(glob.glob(os.path.join(reference, "rcc", "Models", "*", "epoch_*.pt")))[:limit]
+    if not files:
+        return None
+    target = trained_forest_path()
+    if os.path.exists(target) and os.path.getmtime(target) >= max(os.path.getmtime(f) for f in files):
+        return target
+    os.makedirs(OUT, exist_ok=True)
+    arrays = {"count": np.int64(len(files))}
+    for n, f in enumerate(files):
+        state = torch.load(f, map_location="cpu", weights_only=True)
+        arrays["thr%d" % n] = state["forest.thresholds"].float().numpy()
+        arrays["ord%d" % n] = state["forest.ordinals"].long().numpy()  # old checkpoints store them as float32
+        arrays["w%d" % n] = state["forest.weights"].float().numpy()
+    np.savez(target, **arrays)
+    return target
+
+
 def load():
     """Import the built reference module (raises ImportError if it was never built)."""
     import importlib.util
@@ -97,9 +130,11 @@ def load():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("HINGETREE_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("HINGETREE_REFERENCE"), required="HINGETREE_REFERENCE" not in os.environ,
+                    help="checkout of NIH-MIP/HingeTreeForTorch (or set HINGETREE_REFERENCE)")
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     print(build(a.reference, a.jobs, a.force))
+    print(extract_trained_forests(a.reference))
     sys.exit(0)

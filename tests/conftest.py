@@ -45,3 +45,11 @@ def random_forest_inputs(seed, kind, B, C, inner, T, depth, extra, scale_thr=3.0
         x = np.round(x * 2) / 2
         thr = np.round(thr * 2) / 2
     return x, thr, ord_, w
+
+
+def grad_close(t, ref, scale, rel=1e-5):
+    """The backward bar for sums whose order is free: |t - ref| <= 1e-5 * scale per element, where
+    scale is the sum of |terms| the oracle added into that element (hinge_oracle.magnitudes)."""
+    got = t.detach().cpu().numpy() if hasattr(t, "detach") else np.asarray(t)
+    got = got.astype(np.float64)
+    return bool(np.all(np.abs(got - np.asarray(ref, dtype=np.float64)) <= rel * np.asarray(scale, dtype=np.float64) + 1e-30))

@@ -1,7 +1,7 @@
 """Convolutional hinge trees / ferns and contract / expand on a GPU, against the CPU oracle.
 
 Bars: the convolution forward is bit-exact (input channels are added in the reference's order);
-its gradients (atomic scatters) match within rtol 1e-4 plus a small absolute floor; contract and
+its gradients (summation order is free) match within 1e-5 of the summed term magnitudes; contract and
 expand move bytes and are exact for every element type, and expand(contract(x)) == x whenever the
 windows tile the image without padding.
 """
@@ -9,6 +9,7 @@ import numpy as np
 import pytest
 import torch
 
+from conftest import grad_close
 from oracle import hinge_oracle as ho
 
 pytestmark = pytest.mark.gpu
@@ -16,10 +17,6 @@ pytestmark = pytest.mark.gpu
 
 def dev(*arrays):
     return [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in arrays]
-
-
-def close(t, ref):
-    return np.allclose(t.cpu().numpy(), ref, rtol=1e-4, atol=2e-5 * max(1.0, float(np.abs(ref).max())))
 
 
 CONV_CASES = [
@@ -63,7 +60,8 @@ def test_convolution_matches_oracle(kind, case):
     dg, = dev(g)
     gx, gthr, gw = conv.backward(dx, dthr, dord, dw, dg)
     rx, rthr, rw = ho.conv_backward(kind, x, thr, ord_, w, g, kernel, stride, padding, dilation)
-    assert close(gx, rx) and close(gthr, rthr) and close(gw, rw)
+    ax, athr, aw = ho.magnitudes(ho.conv_backward, kind, x, thr, ord_, w, g, kernel, stride, padding, dilation)
+    assert grad_close(gx, rx, ax) and grad_close(gthr, rthr, athr) and grad_close(gw, rw, aw)
     assert conv.status.item() == 0
 
 

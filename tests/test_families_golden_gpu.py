@@ -1,13 +1,14 @@
 """The CUDA path on the reference's golden vectors for fused linear, fusion, convolution and
-contract/expand (tests/golden/families.npz).  Forwards are bit-exact; atomic-scatter gradients
-within rtol 1e-4 and a small absolute floor."""
+contract/expand (tests/golden/families.npz).  Forwards are bit-exact; gradients whose summation
+order is free within 1e-5 of the summed term magnitudes (computed by the oracle on the same inputs)."""
 import os
 
 import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN
+from conftest import GOLDEN, grad_close
+from oracle import hinge_oracle as ho
 
 pytestmark = pytest.mark.gpu
 
@@ -23,10 +24,6 @@ def dev(a):
     return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def close(t, ref):
-    return np.allclose(t.cpu().numpy(), ref, rtol=1e-4, atol=2e-5 * max(1.0, float(np.abs(ref).max())))
-
-
 @pytest.mark.parametrize("idx", range(int(FAMILIES["linear_count"])))
 def test_fused_linear_and_fusion_golden(idx):
     from hingetreefortorch_b200 import _cabi
@@ -38,14 +35,18 @@ def test_fused_linear_and_fusion_golden(idx):
     out = fam.linear_forward(d["x"], vec, d["thr"], d["ord"], d["w"], d["lin"], d["bias"])
     assert np.array_equal(out.cpu().numpy(), c["out"])
     gx, gvec, gthr, gw, glin = fam.linear_backward(d["x"], vec, d["thr"], d["ord"], d["w"], d["lin"], d["g"])
-    assert close(gx, c["gx"]) and close(gthr, c["gthr"]) and close(gw, c["gw"]) and close(glin, c["glin"])
+    mag = ho.magnitudes(ho.linear_backward, kind, c["x"], c["thr"], c["ord"], c["w"], c["lin"], c["g"], vec=c.get("vec"))
+    ax, athr, aw, alin = mag[0], mag[-4], mag[-3], mag[-2]
+    assert grad_close(gx, c["gx"], ax) and grad_close(gthr, c["gthr"], athr)
+    assert grad_close(gw, c["gw"], aw) and grad_close(glin, c["glin"], alin)
     if vec is not None:
-        assert close(gvec, c["gvec"])
+        assert grad_close(gvec, c["gvec"], mag[1])
         plain = _cabi.ForestFamily(kind, d["x"], d["w"], vec=vec)
         assert np.array_equal(plain.fusion_forward(d["x"], vec, d["thr"], d["ord"], d["w"]).cpu().numpy(), c["fusion_out"])
         gimg, gvec, gthr, gw = plain.fusion_backward(d["x"], vec, d["thr"], d["ord"], d["w"], d["fusion_g"])
-        assert close(gimg, c["fusion_gx"]) and close(gvec, c["fusion_gvec"])
-        assert close(gthr, c["fusion_gthr"]) and close(gw, c["fusion_gw"])
+        aimg, avec, athr, aw = ho.magnitudes(ho.backward, kind, c["x"], c["thr"], c["ord"], c["w"], c["fusion_g"], vec=c["vec"])
+        assert grad_close(gimg, c["fusion_gx"], aimg) and grad_close(gvec, c["fusion_gvec"], avec)
+        assert grad_close(gthr, c["fusion_gthr"], athr) and grad_close(gw, c["fusion_gw"], aw)
 
 
 @pytest.mark.parametrize("idx", range(int(FAMILIES["conv_count"])))
@@ -58,7 +59,8 @@ def test_convolution_golden(idx):
     conv = _cabi.Conv(kind, d["x"], d["w"], *geometry)
     assert np.array_equal(conv.forward(d["x"], d["thr"], d["ord"], d["w"]).cpu().numpy(), c["out"])
     gx, gthr, gw = conv.backward(d["x"], d["thr"], d["ord"], d["w"], d["g"])
-    assert close(gx, c["gx"]) and close(gthr, c["gthr"]) and close(gw, c["gw"])
+    ax, athr, aw = ho.magnitudes(ho.conv_backward, kind, c["x"], c["thr"], c["ord"], c["w"], c["g"], *geometry)
+    assert grad_close(gx, c["gx"], ax) and grad_close(gthr, c["gthr"], athr) and grad_close(gw, c["gw"], aw)
 
 
 @pytest.mark.parametrize("idx", range(int(FAMILIES["patch_count"])))

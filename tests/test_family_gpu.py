@@ -2,13 +2,12 @@
 
 Bars: the fusion forward and the fused-linear forward are bit-exact (the fused-linear forward adds
 its terms in the reference CPU order); gradients match within 1e-5 of the summed term magnitudes
-(these backwards scatter with atomics, so their summation order is free; 1e-4 relative with a
-small absolute floor is used where the magnitudes are not available from the oracle)."""
+(these backwards scatter with atomics, so their summation order is free)."""
 import numpy as np
 import pytest
 import torch
 
-from conftest import random_forest_inputs
+from conftest import grad_close, random_forest_inputs
 from oracle import hinge_oracle as ho
 
 pytestmark = pytest.mark.gpu
@@ -16,10 +15,6 @@ pytestmark = pytest.mark.gpu
 
 def dev(*arrays):
     return [None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in arrays]
-
-
-def close(t, ref):
-    return np.allclose(t.cpu().numpy(), ref, rtol=1e-4, atol=2e-5 * max(1.0, float(np.abs(ref).max())))
 
 
 CASES = [
@@ -53,12 +48,15 @@ def test_fused_linear_and_fusion(case):
     dg, = dev(g)
     gx, gvec, gthr, gw, glin = fam.linear_backward(dx, dvec, dthr, dord, dw, dlin, dg)
     ref = ho.linear_backward(kind, x, thr, ord_, w, lin, g, vec=vec)
+    mag = ho.magnitudes(ho.linear_backward, kind, x, thr, ord_, w, lin, g, vec=vec)
     if Cv:
         rx, rvec, rthr, rw, rlin, _ = ref
-        assert close(gvec, rvec)
+        ax, avec, athr, aw, alin, _ = mag
+        assert grad_close(gvec, rvec, avec)
     else:
         rx, rthr, rw, rlin, _ = ref
-    assert close(gx, rx) and close(gthr, rthr) and close(gw, rw) and close(glin, rlin)
+        ax, athr, aw, alin, _ = mag
+    assert grad_close(gx, rx, ax) and grad_close(gthr, rthr, athr) and grad_close(gw, rw, aw) and grad_close(glin, rlin, alin)
     assert fam.status.item() == 0
 
     if Cv:
@@ -70,7 +68,9 @@ def test_fused_linear_and_fusion(case):
         dg2, = dev(g2)
         gimg, gvec, gthr, gw = plain.fusion_backward(dx, dvec, dthr, dord, dw, dg2)
         rimg, rvec, rthr, rw = ho.backward(kind, x, thr, ord_, w, g2, vec=vec)
-        assert close(gimg, rimg) and close(gvec, rvec) and close(gthr, rthr) and close(gw, rw)
+        aimg, avec, athr, aw = ho.magnitudes(ho.backward, kind, x, thr, ord_, w, g2, vec=vec)
+        assert grad_close(gimg, rimg, aimg) and grad_close(gvec, rvec, avec)
+        assert grad_close(gthr, rthr, athr) and grad_close(gw, rw, aw)
 
 
 def test_modules_fused_linear_and_fusion():
@@ -85,8 +85,9 @@ def test_modules_fused_linear_and_fusion():
     assert np.array_equal(y.detach().cpu().numpy(), ho.linear_forward("tree", *args))
     g = (2 * y).detach().cpu().numpy()
     gx, gthr, gw, glin, gbias = ho.linear_backward("tree", args[0], args[1], args[2], args[3], args[4], g)
-    assert close(x.grad, gx) and close(m.thresholds.grad, gthr) and close(m.weights.grad, gw)
-    assert close(m.linear_weights.grad, glin) and close(m.linear_bias.grad, gbias)
+    ax, athr, aw, alin, abias = ho.magnitudes(ho.linear_backward, "tree", args[0], args[1], args[2], args[3], args[4], g)
+    assert grad_close(x.grad, gx, ax) and grad_close(m.thresholds.grad, gthr, athr) and grad_close(m.weights.grad, gw, aw)
+    assert grad_close(m.linear_weights.grad, glin, alin) and grad_close(m.linear_bias.grad, gbias, abias)
 
     f = R.RandomHingeFernFusion(6, 3, 8, 4).cuda()
     img = torch.randn(5, 6, 4, 4, device="cuda", requires_grad=True)
