@@ -5,7 +5,8 @@ that model code written against it keeps working; the classes themselves are gen
 few templates instead of being spelled out one by one.
 
 Every Function saves its raw inputs and lets the backward operator redo the traversal, as the
-reference does (_HingeTree.py:92-108).  Deterministic mode is read from
+reference does (_HingeTree.py:92-108); the plain tree and fern additionally keep the forward's
+traversal where the library offers it, so that one training step walks the trees once.  Deterministic mode is read from
 torch.are_deterministic_algorithms_enabled() (reference: _HingeTree.py:24-30): the plain tree
 and fern select the fixed-order backward; operators without a fixed-order implementation
 raise RuntimeError, as the reference does for every GPU operator other than the plain ones.
@@ -120,12 +121,28 @@ def _utilities(kind):
 
 def _plain_function(name, kind):
     fwd, bwd, bwd_det = _op(kind + "_forward"), _op(kind + "_backward"), _op(kind + "_backward_deterministic")
+    fwd_saving, bwd_saved = _op(kind + "_forward_saving"), _op(kind + "_backward_saved")
 
     def forward(ctx, inData, inThresholds, inOrdinals, inWeights):
+        # When a gradient will be asked for, the forward keeps its traversal (signed margin, deciding vertex and
+        # leaf of every evaluation) so that the backward does not walk the trees again; the operator returns an
+        # empty `kept` for problems it does not do this for, and the backward then re-walks, as the reference does.
+        kept = None
+        if inData.is_cuda and any(ctx.needs_input_grad):
+            out, kept = fwd_saving(inData, inThresholds, inOrdinals, inWeights)
+            if kept.numel() == 0:
+                kept = None
+        else:
+            out = fwd(inData, inThresholds, inOrdinals, inWeights)
+        ctx.kept = kept
         ctx.save_for_backward(inData, inThresholds, inOrdinals, inWeights)
-        return fwd(inData, inThresholds, inOrdinals, inWeights)
+        return out
 
     def backward(ctx, outDataGrad):
+        kept, ctx.kept = ctx.kept, None  # one backward per forward: the scratch is rewritten by it
+        if kept is not None:
+            return tuple(bwd_saved(*_interleave(ctx.saved_tensors, ctx.needs_input_grad), outDataGrad.contiguous(), kept,
+                                   _is_deterministic()))
         op = bwd_det if _is_deterministic() else bwd
         return tuple(op(*_interleave(ctx.saved_tensors, ctx.needs_input_grad), outDataGrad.contiguous()))
 
@@ -138,6 +155,12 @@ def _sparse_function(name, base, kind, label):
     """Backward returns sparse COO gradients; only the data gradient is densified (as in the reference)."""
     bwd = _op("sparse_%s_backward" % kind)
 
+    fwd = _op(kind + "_forward")
+
+    def forward(ctx, inData, inThresholds, inOrdinals, inWeights):  # the sparse backward has no use for a kept traversal
+        ctx.save_for_backward(inData, inThresholds, inOrdinals, inWeights)
+        return fwd(inData, inThresholds, inOrdinals, inWeights)
+
     def backward(ctx, outDataGrad):
         _refuse_deterministic(ctx.saved_tensors[0], "sparse hinge %s backward" % label)
         grads = list(bwd(*_interleave(ctx.saved_tensors, ctx.needs_input_grad), outDataGrad.contiguous()))
@@ -145,7 +168,7 @@ def _sparse_function(name, base, kind, label):
             grads[0] = grads[0].to_dense()
         return tuple(grads)
 
-    return type(name, (base,), {"backward": staticmethod(backward)})
+    return type(name, (base,), {"forward": staticmethod(forward), "backward": staticmethod(backward)})
 
 
 def _fused_linear_function(name, base, kind, label, sparse):

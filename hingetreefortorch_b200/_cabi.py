@@ -13,11 +13,14 @@ from . import _build
 HT_KIND = {"tree": 0, "fern": 1}
 HT_DETERMINISTIC = 1
 HT_WORKSPACE_FOR_BACKWARD = 2
+HT_SAVE_FOR_BACKWARD = 4
+HT_SAVED_FORWARD = 8
 HT_FLAG_ORDINAL_RANGE = 1
+HT_FLAG_PIPELINE_TIMEOUT = 0x80000000  # a bounded wait inside a kernel ran out: outputs incomplete
 
 # every symbol include/hingetree_b200.h declares (checked by the CPU test-suite)
 SYMBOLS = [
-    "ht_version", "ht_status_string", "ht_last_cuda_error", "ht_forest_workspace_bytes",
+    "ht_version", "ht_status_string", "ht_last_cuda_error", "ht_forest_workspace_bytes", "ht_forest_forward_saves",
     "ht_forest_forward_f32", "ht_forest_leafmap_f32", "ht_forest_marginmap_f32",
     "ht_forest_reachability_f32", "ht_forest_backward_f32",
     "ht_forest_static_scratch_bytes", "ht_forest_forward_static_f32",
@@ -178,11 +181,21 @@ class Forest:
     def _tail(self, x):
         return (_ptr(self.workspace), ctypes.c_size_t(self.workspace.numel()), _ptr(self.status), _stream(x))
 
-    def forward(self, x, thr, ord_, w, out=None):
+    def _with_flags(self, extra):
+        problem = ForestProblem.from_buffer_copy(self.problem)
+        problem.flags |= extra
+        return problem
+
+    def saves_forward(self):
+        """Whether forward(save=True) keeps the traversal for backward(saved=True) on this problem."""
+        return bool(library().ht_forest_forward_saves(ctypes.byref(self.problem)))
+
+    def forward(self, x, thr, ord_, w, out=None, save=False):
         import torch
         if out is None:
             out = torch.empty(self.out_shape, dtype=torch.float32, device=x.device)
-        _check(library().ht_forest_forward_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(w),
+        problem = self._with_flags(HT_SAVE_FOR_BACKWARD) if save else self.problem
+        _check(library().ht_forest_forward_f32(ctypes.byref(problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(w),
                                                _ptr(out), *self._tail(x)))
         return out
 
@@ -217,18 +230,24 @@ class Forest:
                                                     _ptr(counts), *self._tail(x)))
         return counts
 
-    def backward(self, x, thr, ord_, w, g, need=(True, True, True), outs=None):
+    def backward(self, x, thr, ord_, w, g, need=(True, True, True), outs=None, saved=False):
+        """saved=True: the last call on this object was forward(save=True) on the same tensors."""
         import torch
         if outs is None:
             outs = (torch.empty_like(x) if need[0] else None, torch.empty_like(thr) if need[1] else None,
                     torch.empty_like(w) if need[2] else None)
-        _check(library().ht_forest_backward_f32(ctypes.byref(self.problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(w),
+        problem = self._with_flags(HT_SAVED_FORWARD) if saved else self.problem
+        _check(library().ht_forest_backward_f32(ctypes.byref(problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(w),
                                                 _ptr(g), _ptr(outs[0]), _ptr(outs[1]), _ptr(outs[2]), *self._tail(x)))
         return outs
 
     def ordinal_flags(self):
-        """Reads the device status word (blocks until the stream has drained)."""
-        return int(self.status.item())
+        """Reads the device status word (blocks until the stream has drained); raises when a kernel gave up on
+        a bounded wait, returns the other flag bits (HT_FLAG_ORDINAL_RANGE)."""
+        flags = int(self.status.item()) & 0xffffffff
+        if flags & HT_FLAG_PIPELINE_TIMEOUT:
+            raise HingeTreeError(-3, "a bounded wait inside a kernel ran out; outputs are incomplete")
+        return flags
 
 
 class ForestFamily:

@@ -7,6 +7,7 @@
 #include <torch/extension.h>
 
 #include <c10/core/DeviceGuard.h>
+#include <c10/cuda/CUDAFunctions.h>
 #include <c10/cuda/CUDAStream.h>
 
 #include <algorithm>
@@ -120,23 +121,70 @@ void remember_valid(const torch::Tensor &ord, int64_t channels) {
 
 }  // namespace
 
-OrdinalGuard::OrdinalGuard(const torch::Tensor &ord, int64_t channels) : ord_(ord), channels_(channels) {
-  check_ = g_ordinal_check != OrdinalCheck::Never && !seen_valid(ord, channels);
-  if (check_) word_ = torch::zeros({1}, torch::TensorOptions().dtype(torch::kInt32).device(ord.device()));
+// Calls whose ordinals are already known to be valid do not read anything back (no synchronisation), but their
+// kernels still get a status word: one long-lived word per device that collects HT_FLAG_PIPELINE_TIMEOUT (a
+// bounded wait inside a kernel ran out: outputs incomplete).  It is read together with the next call that
+// synchronises anyway, and by pipeline_status().
+namespace {
+std::mutex g_sticky_mutex;
+std::vector<torch::Tensor> g_sticky_words;
+
+torch::Tensor sticky_word(const c10::Device &device, bool create) {
+  std::lock_guard<std::mutex> lock(g_sticky_mutex);
+  const size_t index = device.has_index() ? (size_t)device.index() : (size_t)c10::cuda::current_device();
+  if (g_sticky_words.size() <= index) g_sticky_words.resize(index + 1);
+  if (!g_sticky_words[index].defined() && create)
+    g_sticky_words[index] = torch::zeros({1}, torch::TensorOptions().dtype(torch::kInt32).device(device));
+  return g_sticky_words[index];
 }
 
-uint32_t *OrdinalGuard::word() { return check_ ? reinterpret_cast<uint32_t *>(word_.data_ptr<int32_t>()) : nullptr; }
+[[noreturn]] void raise_pipeline_timeout() {
+  bad_runtime("Error: a bounded wait inside a hinge tree kernel ran out (a parameter or gradient copy never arrived); "
+              "the results of the calls since the last check are incomplete.");
+}
+}  // namespace
+
+OrdinalGuard::OrdinalGuard(const torch::Tensor &ord, int64_t channels) : ord_(ord), channels_(channels) {
+  check_ = g_ordinal_check != OrdinalCheck::Never && !seen_valid(ord, channels);
+  // a checked call synchronises and is never part of a stream capture: the place to create the device's word
+  if (check_) {
+    word_ = torch::zeros({1}, torch::TensorOptions().dtype(torch::kInt32).device(ord.device()));
+    sticky_ = sticky_word(ord.device(), true);
+  } else {
+    sticky_ = sticky_word(ord.device(), false);
+  }
+}
+
+uint32_t *OrdinalGuard::word() {
+  if (check_) return reinterpret_cast<uint32_t *>(word_.data_ptr<int32_t>());
+  return sticky_.defined() ? reinterpret_cast<uint32_t *>(sticky_.data_ptr<int32_t>()) : nullptr;
+}
 
 void OrdinalGuard::finish() {
   if (!check_) return;
-  const int32_t flags = word_.item<int32_t>();
+  const torch::Tensor both = torch::cat({word_, sticky_}).cpu();  // one blocking copy for both words
+  const int32_t flags = both.data_ptr<int32_t>()[0], earlier = both.data_ptr<int32_t>()[1];
+  if (earlier != 0) sticky_.zero_();
+  if (((uint32_t)flags | (uint32_t)earlier) & HT_FLAG_PIPELINE_TIMEOUT) raise_pipeline_timeout();
   if (flags & (int32_t)HT_FLAG_ORDINAL_RANGE)
     bad_runtime("Error: An ordinal value is either negative or larger than or equal to the number of channels.");
   remember_valid(ord_, channels_);
 }
 
+// Reads (and clears) the long-lived status word of the current device; raises when a kernel reported a timeout.
+int64_t pipeline_status() {
+  torch::Tensor word = sticky_word(c10::Device(c10::kCUDA, c10::cuda::current_device()), false);
+  if (!word.defined()) return 0;
+  const int32_t flags = word.item<int32_t>();
+  if (flags != 0) word.zero_();
+  if ((uint32_t)flags & HT_FLAG_PIPELINE_TIMEOUT) raise_pipeline_timeout();
+  return flags;
+}
+
 // Most scratch a backward call may take for its per-evaluation records (12 bytes per tree
 // evaluation).  Beyond it the call runs without them: atomic scatters instead of ordered sums.
+// Default: whatever fits (an allocation that fails falls back to the path without records); a caller may
+// set a smaller figure.
 static int64_t g_backward_scratch_limit = INT64_MAX;
 
 void set_backward_scratch_limit(int64_t bytes) {
@@ -246,13 +294,83 @@ std::vector<torch::Tensor> forest_backward(int kind, bool deterministic, torch::
   if (need_x) grads[0] = torch::empty_like(x);
   if (need_thr) grads[1] = torch::empty_like(thr);
   if (need_w) grads[3] = torch::empty_like(w);
-  torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
+  torch::Tensor ws;
+  try {
+    ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
+  } catch (const c10::OutOfMemoryError &) {
+    // no room for the evaluation records (10 to 12 bytes per tree evaluation): the default mode can do
+    // without them (the reference allocates nothing for its backward either); the fixed-order mode cannot
+    if (deterministic || (call.problem.flags & HT_WORKSPACE_FOR_BACKWARD) == 0) throw;
+    call.problem.flags &= ~HT_WORKSPACE_FOR_BACKWARD;
+    ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
+  }
   OrdinalGuard og(ord, call.problem.C);
   raise_status(
       ht_forest_backward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
                              w.data_ptr<float>(), g.data_ptr<float>(), need_x ? grads[0].data_ptr<float>() : nullptr,
                              need_thr ? grads[1].data_ptr<float>() : nullptr,
                              need_w ? grads[3].data_ptr<float>() : nullptr, ws.data_ptr(), ws.numel(), og.word(),
+                             current_stream(x)),
+      "forest backward");
+  og.finish();
+  return grads;
+}
+
+// ---- forward that keeps its traversal for the backward -----------------------------------------------------
+// Not part of the reference's operator set: the reference's backward walks every tree again (three times).  These
+// two let the autograd layer walk them once per training step.  `saved` is the call's scratch, which holds the
+// traversal; it is empty when the library does not save for this problem (the caller then uses the plain backward).
+static bool g_save_forward = true;
+
+std::vector<torch::Tensor> forest_forward_saving(int kind, torch::Tensor x, torch::Tensor thr, torch::Tensor ord,
+                                                 torch::Tensor w) {
+  ForestCall call(kind, x, thr, ord, w, nullptr);
+  c10::DeviceGuard guard(x.device());
+  const bool saves = g_save_forward && ht_forest_forward_saves(&call.problem) != 0;
+  if (saves) call.problem.flags |= HT_WORKSPACE_FOR_BACKWARD | HT_SAVE_FOR_BACKWARD;
+  if (saves && (int64_t)ht_forest_workspace_bytes(&call.problem) > g_backward_scratch_limit)
+    call.problem.flags &= ~(HT_WORKSPACE_FOR_BACKWARD | HT_SAVE_FOR_BACKWARD);
+  torch::Tensor out = torch::empty(call.out_sizes, x.options());
+  torch::Tensor ws;
+  try {
+    ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
+  } catch (const c10::OutOfMemoryError &) {
+    if ((call.problem.flags & HT_SAVE_FOR_BACKWARD) == 0) throw;
+    call.problem.flags &= ~(HT_WORKSPACE_FOR_BACKWARD | HT_SAVE_FOR_BACKWARD);  // no room: a plain forward
+    ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
+  }
+  OrdinalGuard og(ord, call.problem.C);
+  raise_status(ht_forest_forward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
+                                     w.data_ptr<float>(), out.data_ptr<float>(), ws.data_ptr(), ws.numel(), og.word(),
+                                     current_stream(x)),
+               "forest forward");
+  og.finish();
+  const bool saved = (call.problem.flags & HT_SAVE_FOR_BACKWARD) != 0;
+  return {out, saved ? ws : torch::empty({0}, ws.options())};
+}
+
+std::vector<torch::Tensor> forest_backward_saved(int kind, bool deterministic, torch::Tensor x, bool need_x,
+                                                 torch::Tensor thr, bool need_thr, torch::Tensor ord, bool need_ord,
+                                                 torch::Tensor w, bool need_w, torch::Tensor g, torch::Tensor saved) {
+  if (need_ord) bad_runtime("Error: Gradient on inOrdinals is requested, but inOrdinals never has a gradient.");
+  ForestCall call(kind, x, thr, ord, w, &g);
+  c10::DeviceGuard guard(x.device());
+  std::vector<torch::Tensor> grads(4);
+  if (!need_x && !need_thr && !need_w) return grads;
+  if (deterministic) call.problem.flags |= HT_DETERMINISTIC;
+  call.problem.flags |= HT_WORKSPACE_FOR_BACKWARD | HT_SAVED_FORWARD;
+  if (!saved.defined() || saved.device() != x.device() || saved.scalar_type() != torch::kUInt8 ||
+      (size_t)saved.numel() < ht_forest_workspace_bytes(&call.problem) || ht_forest_forward_saves(&call.problem) == 0)
+    bad_argument("Error: `saved` is not the scratch a saving forward returned for these tensors.");
+  if (need_x) grads[0] = torch::empty_like(x);
+  if (need_thr) grads[1] = torch::empty_like(thr);
+  if (need_w) grads[3] = torch::empty_like(w);
+  OrdinalGuard og(ord, call.problem.C);
+  raise_status(
+      ht_forest_backward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
+                             w.data_ptr<float>(), g.data_ptr<float>(), need_x ? grads[0].data_ptr<float>() : nullptr,
+                             need_thr ? grads[1].data_ptr<float>() : nullptr,
+                             need_w ? grads[3].data_ptr<float>() : nullptr, saved.data_ptr(), saved.numel(), og.word(),
                              current_stream(x)),
       "forest backward");
   og.finish();
@@ -474,6 +592,13 @@ using namespace htx;
                                              bool no, torch::Tensor w, bool nw, torch::Tensor g) {                  \
     return forest_backward(KIND, true, x, nx, t, nt, o, no, w, nw, g);                                              \
   });                                                                                                               \
+  m.def(prefix "_forward_saving", [](torch::Tensor x, torch::Tensor t, torch::Tensor o, torch::Tensor w) {           \
+    return forest_forward_saving(KIND, x, t, o, w);                                                                 \
+  });                                                                                                               \
+  m.def(prefix "_backward_saved", [](torch::Tensor x, bool nx, torch::Tensor t, bool nt, torch::Tensor o, bool no,  \
+                                     torch::Tensor w, bool nw, torch::Tensor g, torch::Tensor saved, bool det) {    \
+    return forest_backward_saved(KIND, det, x, nx, t, nt, o, no, w, nw, g, saved);                                  \
+  });                                                                                                               \
   m.def(prefix "_check_thresholds", [](torch::Tensor t, torch::Tensor o, torch::Tensor w) {                         \
     return thresholds_utility(KIND, false, t, o, w);                                                                \
   });                                                                                                               \
@@ -504,6 +629,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_backward_scratch_limit", &set_backward_scratch_limit,
         "Upper bound in bytes on the scratch a default-mode backward call allocates for its per-evaluation records "
         "(12 bytes per tree evaluation); above it the gradients are scattered with atomics instead. Default: no bound.");
+  m.def("set_save_forward", [](bool on) { g_save_forward = on; },
+        "Whether tree_/fern_forward_saving keep the traversal for the backward (default) or act as the plain forward.");
+  m.def("pipeline_status", &pipeline_status,
+        "Reads and clears the current device's long-lived kernel status word (calls on ordinals already known to be "
+        "valid do not synchronise; a kernel that gave up on a bounded wait leaves its flag there). Raises RuntimeError "
+        "when a timeout was flagged; returns the other flag bits.");
   m.def("set_ordinal_check", &set_ordinal_check,
         "When to read the ordinal range flag back from the device: 'cached' (default: once per ordinals tensor "
         "version), 'always' (every call, like the reference) or 'never'.");

@@ -22,9 +22,11 @@ void require_cuda(const torch::Tensor &t);
 void require_float32(const torch::Tensor &t);
 torch::Tensor make_workspace(size_t bytes, const torch::Tensor &like);
 void set_ordinal_check(const std::string &mode);
+int64_t pipeline_status();
 
 // Owns the device status word of one call and turns a flagged ordinal into the reference's
-// RuntimeError.  word() is null when this ordinals tensor is already known to be valid.
+// RuntimeError.  When this ordinals tensor is already known to be valid nothing is read back and word() is the
+// device's long-lived status word, which keeps a kernel's timeout flag for the next call that synchronises.
 class OrdinalGuard {
  public:
   OrdinalGuard(const torch::Tensor &ord, int64_t channels);
@@ -32,7 +34,7 @@ class OrdinalGuard {
   void finish();
 
  private:
-  torch::Tensor ord_, word_;
+  torch::Tensor ord_, word_, sticky_;
   int64_t channels_;
   bool check_;
 };

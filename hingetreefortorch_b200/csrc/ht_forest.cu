@@ -327,6 +327,10 @@ const char *ht_status_string(int status) {
   }
 }
 
+int ht_forest_forward_saves(const ht_forest_problem *p) {
+  return check_forest_problem(p) == HT_OK && forward_saves(p) ? 1 : 0;
+}
+
 size_t ht_forest_workspace_bytes(const ht_forest_problem *p) {
   if (check_forest_problem(p) != HT_OK) return 0;
   const size_t base = ordinals_bytes(p) + forward_tiled_workspace_bytes(p) + 256;
@@ -341,8 +345,14 @@ int ht_forest_forward_f32(const ht_forest_problem *p, const float *x, const floa
   if (rc != HT_OK) return rc;
   if (pr.evals * p->M == 0) return HT_OK;
   if (out == nullptr) return HT_ERR_INVALID_ARGUMENT;
-  const int trc = forward_tiled(p, x, thr, pr.args.ord, w, out, static_cast<unsigned char *>(workspace) + ordinals_bytes(p),
-                                status_word, pr.stream);
+  // HT_SAVE_FOR_BACKWARD: the traversal goes to the evaluation-record area of the workspace, when it is there
+  unsigned char *ws = static_cast<unsigned char *>(workspace);
+  void *eval_records = nullptr;
+  if ((p->flags & HT_SAVE_FOR_BACKWARD) != 0 && forward_saves(p)) {
+    const size_t records_at = ordinals_bytes(p) + forward_tiled_workspace_bytes(p);
+    if (workspace_bytes >= records_at + backward_records_bytes(p)) eval_records = ws + records_at;
+  }
+  const int trc = forward_tiled(p, x, thr, pr.args.ord, w, out, ws + ordinals_bytes(p), eval_records, status_word, pr.stream);
   if (trc != HT_ERR_UNSUPPORTED) return trc;
   return launch_any<MODE_FORWARD>(p, pr, out, nullptr);
 }
@@ -402,6 +412,11 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
     const size_t records_at = ordinals_bytes(p) + forward_tiled_workspace_bytes(p);
     const size_t eval_bytes = backward_records_bytes(p);
     void *eval_records = eval_bytes > 0 && workspace_bytes >= records_at + eval_bytes ? ws + records_at : nullptr;
+    if ((p->flags & HT_SAVED_FORWARD) != 0 && eval_records != nullptr) {
+      // the records of the forward that ran on these inputs are still there: no tree is walked again
+      const int src = backward_saved(p, a.ord, w, g, gx, gthr, gw, eval_records, pr.stream);
+      if (src != HT_ERR_UNSUPPORTED) return src;
+    }
     const int trc = backward_tiled(p, x, thr, a.ord, w, g, gx, gthr, gw, ws + ordinals_bytes(p), eval_records,
                                    status_word, pr.stream);
     if (trc != HT_ERR_UNSUPPORTED) return trc;

@@ -24,7 +24,8 @@ void *g_scratch_address[kMaxDevices] = {};
 
 // Device address of the scratch array on the current device.  `g_forest_scratch` in host code is
 // only a handle for the runtime, not an address a kernel could use; the address is looked up
-// once per device, with that device current.
+// once per device, with that device current.  The cached address lives as long as the device's
+// primary context: a caller that destroys it (cudaDeviceReset) must not call this entry again.
 int resolve_scratch(void **address) {
   int device = 0;
   HT_CUDA_TRY(cudaGetDevice(&device));
@@ -50,11 +51,14 @@ int ht_forest_forward_static_f32(const ht_forest_problem *p, const float *x, con
                                  const float *w, float *out, uint32_t *status_word, ht_stream_t stream) {
   const int rc = ht::check_forest_problem(p);
   if (rc != HT_OK) return rc;
-  if (ht_forest_workspace_bytes(p) > kStaticScratchBytes) return HT_ERR_WORKSPACE;
+  // the forward needs no backward records: size the request without them, whatever the caller's flags say
+  ht_forest_problem forward_only = *p;
+  forward_only.flags &= ~HT_WORKSPACE_FOR_BACKWARD;
+  if (ht_forest_workspace_bytes(&forward_only) > kStaticScratchBytes) return HT_ERR_WORKSPACE;
   void *scratch = nullptr;
   const int src = resolve_scratch(&scratch);
   if (src != HT_OK) return src;
-  return ht_forest_forward_f32(p, x, thr, ord, w, out, scratch, kStaticScratchBytes, status_word, stream);
+  return ht_forest_forward_f32(&forward_only, x, thr, ord, w, out, scratch, kStaticScratchBytes, status_word, stream);
 }
 
 }  // extern "C"

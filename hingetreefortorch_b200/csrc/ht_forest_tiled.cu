@@ -35,11 +35,13 @@
 // threshold and that an add producing NaN produces the canonical positive NaN (so NaN margins
 // go left, as `margin > 0` does in the reference).  |threshold - feature| equals
 // |feature - threshold| bit for bit.
+#include "ht_eval_records.cuh"
 #include "ht_forest_tiled.cuh"
 #include "ht_tile_common.cuh"
 #include "ht_tma.cuh"
 
 #include <algorithm>
+#include <type_traits>
 
 namespace ht {
 
@@ -117,9 +119,13 @@ struct TiledArgs {
   int64_t B, T, K;
   int C, S, G, per_warp, M;
   int tma_store;  // results of full groups leave through the TMA engine (G is 16 or 32)
+  // a forward that saves its traversal for the backward (SAVE kernels): threshold - feature at the deciding
+  // vertex, and the packed vertex / leaf key, in the evaluation-record layout
+  float *save_margin;
+  void *save_where;
 };
 
-template <int KIND, int DEPTH, typename OrdT, bool WREC>
+template <int KIND, int DEPTH, typename OrdT, bool WREC, bool SAVE = false>
 __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(const __grid_constant__ TiledArgs a) {
   extern __shared__ __align__(1024) unsigned char smem[];
   constexpr RecordLayout lay =
@@ -249,7 +255,33 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(const
       float result[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int u = 0; u < 4; ++u) rec[u] = base_addr + warp_records + (uint32_t)u * lay.bytes;
-      if (!poisoned) walk<KIND, DEPTH, OrdT, 4, WREC>(rec, xl_addr, x_stride, result, unused);  // a buffer that never arrived is not read
+      if (SAVE) {
+        // the walk of the backward (signed margin, deciding vertex, path): the same |margin| * leaf weight
+        // leaves as the result, and the traversal itself goes to the evaluation records, from registers
+        // (consecutive lanes are consecutive samples: 128 and 64 contiguous bytes per tree)
+        using WhereT = typename std::conditional<(DEPTH <= 8), unsigned short, uint32_t>::type;
+        const int64_t sample = row0 + sample_group * 32 + lane;
+        const int64_t at = record_index(sample, (int64_t)group * G + slot * 4, a.T);
+        Walked wk[4];
+        if (!poisoned) {
+          walk_full<KIND, DEPTH, OrdT, 4, lay.paired>(rec, xl_addr, x_stride, wk);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            result[u] = __fmul_rn(fabsf(wk[u].nm), lds_f32(rec[u] + 4u * wk[u].path + (lay.w - 4u * (1u << DEPTH))));
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) wk[u] = Walked{0.0f, 1u, 1u << DEPTH};
+        }
+        if (sample < a.B) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            __stcs(a.save_margin + at + u * kRecordBlock, wk[u].nm);
+            store_where<WhereT>(a.save_where, at + u * kRecordBlock, wk[u].v, __brev(wk[u].path - (1u << DEPTH)) >> (32 - DEPTH));
+          }
+        }
+      } else if (!poisoned) {
+        walk<KIND, DEPTH, OrdT, 4, WREC>(rec, xl_addr, x_stride, result, unused);  // a buffer that never arrived is not read
+      }
       done_with_buffer(it);
       if (tma_store) {
         // The sample group's [32 samples x G trees] block goes to shared memory in the swizzled box layout
@@ -511,6 +543,11 @@ int launch_depth(const TilePlan &plan, const TiledArgs &a, dim3 grid, cudaStream
     return launch_one(forest_forward_tiled_inner_kernel<KIND, DEPTH, uint16_t>, plan, a, grid, stream);
   }
   const bool wrec = a.M == 1;
+  if (a.save_margin != nullptr) {
+    if (plan.ord_bytes == 1)
+      return launch_one(forest_forward_tiled_kernel<KIND, DEPTH, uint8_t, true, true>, plan, a, grid, stream);
+    return launch_one(forest_forward_tiled_kernel<KIND, DEPTH, uint16_t, true, true>, plan, a, grid, stream);
+  }
   if (plan.ord_bytes == 1)
     return wrec ? launch_one(forest_forward_tiled_kernel<KIND, DEPTH, uint8_t, true>, plan, a, grid, stream)
                 : launch_one(forest_forward_tiled_kernel<KIND, DEPTH, uint8_t, false>, plan, a, grid, stream);
@@ -550,8 +587,17 @@ size_t forward_tiled_workspace_bytes(const ht_forest_problem *p) {
   return align_up((size_t)p->T * plan.rec.bytes, 256);
 }
 
+bool forward_saves(const ht_forest_problem *p) {
+  TilePlan plan;
+  if (p->K != 1 || p->M != 1 || !make_plan(p, plan)) return false;
+  // every tree group takes the kernel's streamlined body: 4 trees per warp, no short last group
+  // ... and the kernel that expands the records fits its tables into shared memory
+  return plan.per_warp == 4 && p->T % plan.G == 0 && p->B <= 0x7fffffff && backward_records_bytes(p) > 0 &&
+         saved_samples_per_cta(p) != 0;
+}
+
 int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, const int32_t *ord, const float *w,
-                  float *out, void *records, uint32_t *status_word, cudaStream_t stream) {
+                  float *out, void *records, void *eval_records, uint32_t *status_word, cudaStream_t stream) {
   TilePlan plan;
   if (!(p->K > 1 ? make_inner_plan(p, plan) : make_plan(p, plan))) return HT_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0 || (reinterpret_cast<uintptr_t>(out) & 15u) != 0)
@@ -581,6 +627,13 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
   a.S = plan.S;
   a.G = plan.G;
   a.per_warp = plan.per_warp;
+  a.save_margin = nullptr;
+  a.save_where = nullptr;
+  if (eval_records != nullptr && forward_saves(p)) {
+    const EvalRecords saved = eval_record_arrays(p, eval_records);
+    a.save_margin = saved.dx;
+    a.save_where = saved.where;
+  }
   // Full groups of 16 or 32 trees leave as tiled TMA stores when the output admits a tensor map
   // (rows of a multiple of 16 bytes); otherwise, and for a short last group, as row segments.
   a.tma_store = 0;

@@ -17,6 +17,7 @@
 //     the traversal kernel itself.
 // There is no block-wide barrier after the feature tile has been staged.
 #include "ht_forest_tiled.cuh"
+#include "ht_eval_records.cuh"
 #include "ht_tile_common.cuh"
 #include "ht_tma.cuh"
 
@@ -69,64 +70,6 @@ bool make_bwd_plan(const ht_forest_problem *p, BwdPlan &plan, bool paired = fals
   }
   return false;
 }
-
-// Per-evaluation results of the traversal kernel, each array laid out [sample block of 256][tree][256] so
-// that the x-gradient reduction streams each sample block's records sequentially and the parameter
-// reduction reads contiguous runs: `dx` is the term sign * w * g (the x-gradient term; the threshold term
-// is -dx), `dw` is |margin| * g (the leaf-weight term), `where` packs the deciding vertex (1-based) and the
-// reference leaf key — 8 + 8 bits for depths up to 8, 16 + 16 bits beyond.  The reductions move 10 or 12
-// bytes per evaluation through HBM and are bound by it, so every byte saved here is time saved there.
-struct EvalRecords {
-  float *dx;
-  float *dw;
-  void *where;
-};
-
-constexpr int kRecordBlock = 256;
-
-__host__ __device__ inline int64_t record_index(int64_t sample, int64_t tree, int64_t trees) {
-  return ((sample / kRecordBlock) * trees + tree) * kRecordBlock + (sample % kRecordBlock);
-}
-
-inline size_t record_array_bytes(const ht_forest_problem *p, size_t element) {
-  const int64_t blocks = (p->B * p->K + kRecordBlock - 1) / kRecordBlock;
-  return align_up((size_t)(blocks * kRecordBlock * p->T) * element, 256);
-}
-inline size_t where_bytes(int depth) { return depth <= 8 ? 2 : 4; }
-
-// `where` as the kernels use it: vertex in the low 16 bits, leaf key in the high 16.
-template <typename WT>
-__device__ __forceinline__ void store_where(void *base, int64_t at, uint32_t vertex, uint32_t key) {
-  if (sizeof(WT) == 2)
-    __stcs(static_cast<unsigned short *>(base) + at, (unsigned short)(vertex | (key << 8)));
-  else
-    __stcs(static_cast<uint32_t *>(base) + at, vertex | (key << 16));
-}
-// Streaming loads as volatile statements: the compiler keeps a batch of them together at the point
-// where the prefetch was written instead of sinking each load to its first use.
-__device__ __forceinline__ float stream_f32(const float *p) {
-  float v;
-  asm volatile("ld.global.cs.f32 %0, [%1];" : "=f"(v) : "l"(p));
-  return v;
-}
-template <typename WT>
-__device__ __forceinline__ uint32_t stream_raw_where(const void *base, int64_t at) {
-  uint32_t v;
-  if (sizeof(WT) == 2)
-    asm volatile("ld.global.cs.u16 %0, [%1];" : "=r"(v) : "l"(static_cast<const unsigned short *>(base) + at));
-  else
-    asm volatile("ld.global.cs.u32 %0, [%1];" : "=r"(v) : "l"(static_cast<const uint32_t *>(base) + at));
-  return v;
-}
-template <typename WT>
-__device__ __forceinline__ uint32_t unpack_where(uint32_t raw) {
-  return sizeof(WT) == 2 ? (raw & 0xffu) | ((raw >> 8) << 16) : raw;
-}
-template <typename WT>
-__device__ __forceinline__ uint32_t load_where(const void *base, int64_t at) {
-  return unpack_where<WT>(stream_raw_where<WT>(base, at));
-}
-
 
 struct BwdArgs {
   CUtensorMap g_map;  // the upstream gradient [B, T] in boxes of S rows x G trees (when tma_g is set)
@@ -486,7 +429,8 @@ __global__ void __launch_bounds__(512) reduce_parameter_records_kernel(EvalRecor
 #pragma unroll
     for (int u = 0; u < kAhead; ++u) {
       const bool valid = i0 + 32 * u + lane < B;
-      const uint32_t v = (wh[u] & 0xffffu) - 1u, key = wh[u] >> 16;
+      // (clamped: a traversal that gave up on a lost copy, and said so in the status word, leaves records unwritten)
+      const uint32_t v = min((wh[u] & 0xffffu) - 1u, (uint32_t)N - 1u), key = min(wh[u] >> 16, (uint32_t)L - 1u);
       if (ORDERED) {
         if (gthr != nullptr)
           lanes_in_order_per_key(valid, v, [&]() { thr_bins[v] = __fadd_rn(thr_bins[v], -a[u]); });
@@ -565,8 +509,8 @@ __global__ void __launch_bounds__(512, 1) reduce_parameter_records_columns_kerne
     uint32_t at_thr[CHUNKS], at_w[CHUNKS];
 #pragma unroll
     for (int u = 0; u < CHUNKS; ++u) {
-      at_thr[u] = my_column + ((wh[u] & 0xffffu) - 1u) * bin_bytes;
-      at_w[u] = my_column + ((uint32_t)N + (wh[u] >> 16)) * bin_bytes;
+      at_thr[u] = my_column + min((wh[u] & 0xffffu) - 1u, (uint32_t)N - 1u) * bin_bytes;  // clamped: see above
+      at_w[u] = my_column + ((uint32_t)N + min(wh[u] >> 16, (uint32_t)L - 1u)) * bin_bytes;
     }
     for (int turn = 0; turn < turns; ++turn) {
       if (turn == my_turn) {
@@ -635,18 +579,20 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
 #pragma unroll
     for (int h = 0; h < kBlocksPerFetch; ++h) {
       const int64_t first = ((blk + h) * T + j) * kRecordBlock + lane;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      const float *dxs = r.dx + first, *dws = r.dw + first;
+      const WT *wheres = static_cast<const WT *>(r.where) + first;
+      static_for<0, 8>([&](auto uu) {
+        constexpr int u = decltype(uu)::value;
         const bool valid = blk + h < block_last && (blk + h) * kRecordBlock + 32 * u + lane < B;
         fa[8 * h + u] = 0.0f;  // an absent sample adds zeros to bin 0
         fb[8 * h + u] = 0.0f;
-        fw[8 * h + u] = sizeof(WT) == 2 ? 1u : 1u;  // raw form of vertex 1, leaf 0
+        fw[8 * h + u] = 1u;  // raw form of vertex 1, leaf 0
         if (valid) {
-          fa[8 * h + u] = stream_f32(r.dx + first + 32 * u);
-          fb[8 * h + u] = stream_f32(r.dw + first + 32 * u);
-          fw[8 * h + u] = stream_raw_where<WT>(r.where, first + 32 * u);
+          fa[8 * h + u] = stream_f32_at<32 * u * 4>(dxs);
+          fb[8 * h + u] = stream_f32_at<32 * u * 4>(dws);
+          fw[8 * h + u] = stream_raw_where_at<WT, 32 * u>(wheres);
         }
-      }
+      });
     }
   };
   int64_t blk = block_first;
@@ -659,8 +605,8 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const uint32_t where = unpack_where<WT>(wh[q + u]);
-        at_thr[u] = my_column + ((where & 0xffffu) - 1u) * (uint32_t)(COLUMNS * 4);
-        at_w[u] = my_column + ((uint32_t)N + (where >> 16)) * (uint32_t)(COLUMNS * 4);
+        at_thr[u] = my_column + min((where & 0xffffu) - 1u, (uint32_t)N - 1u) * (uint32_t)(COLUMNS * 4);  // clamped
+        at_w[u] = my_column + ((uint32_t)N + min(where >> 16, (uint32_t)L - 1u)) * (uint32_t)(COLUMNS * 4);
       }
 #pragma unroll
       for (int turn = 0; turn < kTurns; ++turn) {
@@ -733,20 +679,24 @@ __global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, co
     uint32_t wh1[kAhead], wh2[kAhead];
     uint32_t c0[kAhead], c1[kAhead];
     auto fetch_records = [&](int64_t j0, float (&fa)[kAhead], uint32_t (&fw)[kAhead]) {
-#pragma unroll
-      for (int u = 0; u < kAhead; ++u) {
+      const float *dxs = r.dx + first + j0 * kRecordBlock;
+      const WT *wheres = static_cast<const WT *>(r.where) + first + j0 * kRecordBlock;
+      static_for<0, kAhead>([&](auto uu) {
+        constexpr int u = decltype(uu)::value;
         fa[u] = 0.0f;
         fw[u] = 1u;
         if (j0 + u < T) {
-          fa[u] = stream_f32(r.dx + first + (j0 + u) * kRecordBlock);
-          fw[u] = stream_raw_where<WT>(r.where, first + (j0 + u) * kRecordBlock);
+          fa[u] = stream_f32_at<u * kRecordBlock * 4>(dxs);
+          fw[u] = stream_raw_where_at<WT, u * kRecordBlock>(wheres);
         }
-      }
+      });
     };
     auto fetch_features = [&](int64_t j0, const uint32_t (&fw)[kAhead], uint32_t (&fc)[kAhead]) {
 #pragma unroll
       for (int u = 0; u < kAhead; ++u)
-        fc[u] = j0 + u < T ? (uint32_t)__ldg(ord + (j0 + u) * N + ((unpack_where<WT>(fw[u]) & 0xffffu) - 1u)) : 0u;
+        fc[u] = j0 + u < T ? min((uint32_t)__ldg(ord + (j0 + u) * N + min((unpack_where<WT>(fw[u]) & 0xffffu) - 1u, (uint32_t)N - 1u)),
+                                 (uint32_t)C - 1u)
+                           : 0u;  // clamped: see the parameter reductions
     };
     fetch_records(0, a0, wh1);
     fetch_features(0, wh1, c0);
@@ -792,6 +742,170 @@ __global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, co
     for (int idx = threadIdx.x; idx < S * C; idx += blockDim.x) {
       const int ss = idx % S, c = idx / S;
       if (row0 + ss < B) gx[(row0 + ss) * C + c] = tile[c * S + ss];
+    }
+  }
+}
+
+// ---- the backward from a saved forward ---------------------------------------------------------------
+//
+// A forward that ran with room for the evaluation records leaves, per evaluation, nm = threshold - feature at
+// the deciding vertex and the packed (vertex, leaf).  With them no tree is walked again: expand_saved_kernel
+// (sample-stationary, a thread per sample, trees ascending — the reference's order) turns them and the upstream
+// gradient into the terms the traversal kernel of the backward would have written, in place (dx = sign * w * g
+// over nm, dw = |margin| * g), for the parameter reductions above, and adds the x gradient on the way into its
+// column of the shared-memory tile gx[c][s].  Everything it looks up arrives asynchronously, 16 trees at a
+// time, two buffers: the leaf weights and compact feature indices of the trees (both contiguous in global
+// memory: bulk copies) and the box [S samples x 16 trees] of the upstream gradient (a tiled TMA load, 64-byte
+// swizzle: a thread reads the 64 bytes of its own row without bank conflicts).
+constexpr int kSavedBatch = 16;  // trees per batch; the saving forward's tree groups are multiples of it
+
+__host__ __device__ inline size_t saved_table_bytes(int64_t N, int64_t L) { return (size_t)kSavedBatch * (size_t)(N + L) * 4; }
+
+struct ExpandArgs {
+  CUtensorMap g_map;
+  EvalRecords r;
+  const int32_t *ord;
+  const float *w;
+  float *gx;
+  int64_t B, T;
+  int N, L, C;
+  int write_terms;
+};
+
+template <typename WT>
+__global__ void __launch_bounds__(256) expand_saved_kernel(const __grid_constant__ ExpandArgs a) {
+  extern __shared__ __align__(1024) unsigned char saved_smem[];
+  const int S = (int)blockDim.x;
+  const int s = threadIdx.x;
+  const int N = a.N, L = a.L, C = a.C;
+  const int64_t T = a.T;
+  unsigned char *base = saved_smem + ((1024u - (smem_addr(saved_smem) & 1023u)) & 1023u);
+  const uint32_t box_bytes = (uint32_t)S * kSavedBatch * 4u;
+  const uint32_t table_bytes = (uint32_t)saved_table_bytes(N, L);
+  const uint32_t boxes = smem_addr(base);                      // [2] gradient boxes
+  unsigned char *tables = base + 2 * (size_t)box_bytes;        // [2] {leaf weights, feature indices}
+  uint64_t *landed = reinterpret_cast<uint64_t *>(tables + 2 * (size_t)table_bytes);  // [2]
+  float *tile = reinterpret_cast<float *>(landed + 2);         // gx[c][s]
+  const int64_t row0 = (int64_t)blockIdx.x * S;
+  const int batches = (int)(T / kSavedBatch);
+  auto issue = [&](int batch) {  // what the evaluations of trees [16 batch, 16 batch + 16) look up
+    uint64_t *bar = &landed[batch & 1];
+    const uint32_t dst = smem_addr(tables) + (uint32_t)(batch & 1) * table_bytes;
+    const uint32_t w_bytes = (uint32_t)(kSavedBatch * L * 4), o_bytes = (uint32_t)(kSavedBatch * N * 4);
+    mbar_expect_tx(bar, w_bytes + o_bytes + box_bytes);
+    bulk_load(dst, a.w + (int64_t)batch * kSavedBatch * L, w_bytes, bar);
+    bulk_load(dst + w_bytes, a.ord + (int64_t)batch * kSavedBatch * N, o_bytes, bar);
+    tma::load_2d(boxes + (uint32_t)(batch & 1) * box_bytes, &a.g_map, batch * kSavedBatch, (int)row0, bar);
+  };
+  if (s == 0) {
+    mbar_init(&landed[0], 1);
+    mbar_init(&landed[1], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (batches > 0) issue(0);
+    if (batches > 1) issue(1);
+  }
+  if (a.gx != nullptr)
+    for (int idx = s; idx < S * C; idx += S) tile[idx] = 0.0f;
+  __syncthreads();
+  const int64_t i = row0 + s;
+  const bool mine = i < a.B;
+  const int64_t first = record_index(mine ? i : 0, 0, T);  // tree j of this sample sits at first + j * 256
+  // records of the batch after next are requested while the current one is expanded
+  float nm0[kSavedBatch], nm1[kSavedBatch], nm2[kSavedBatch];
+  uint32_t wh0[kSavedBatch], wh1[kSavedBatch], wh2[kSavedBatch];
+  auto fetch = [&](int batch, float (&fn)[kSavedBatch], uint32_t (&fw)[kSavedBatch]) {
+    if (batch >= batches || !mine) return;
+    const int64_t at = first + (int64_t)batch * kSavedBatch * kRecordBlock;
+    const float *margins = a.r.dx + at;
+    const WT *wheres = static_cast<const WT *>(a.r.where) + at;
+    static_for<0, kSavedBatch>([&](auto u) {
+      constexpr int U = decltype(u)::value;
+      fn[U] = stream_f32_at<U * kRecordBlock * 4>(margins);
+      fw[U] = stream_raw_where_at<WT, U * kRecordBlock>(wheres);
+    });
+  };
+#pragma unroll
+  for (int u = 0; u < kSavedBatch; ++u) {
+    nm0[u] = nm1[u] = 0.0f;
+    wh0[u] = wh1[u] = 1u;
+  }
+  fetch(0, nm0, wh0);
+  fetch(1, nm1, wh1);
+  const uint32_t column = smem_addr(tile + s), pitch = (uint32_t)S * 4u;
+  bool gave_up = false;
+  // one batch: its records are in (nm, wh)
+  auto expand = [&](int batch, const float (&nm)[kSavedBatch], const uint32_t (&wh)[kSavedBatch]) {
+    const int64_t j0 = (int64_t)batch * kSavedBatch;
+    if (!gave_up && !mbar_wait(&landed[batch & 1], (uint32_t)((batch >> 1) & 1))) gave_up = true;  // the copies never came
+    if (mine && !gave_up) {
+      const uint32_t w_table = smem_addr(tables) + (uint32_t)(batch & 1) * table_bytes;
+      const uint32_t o_table = w_table + (uint32_t)(kSavedBatch * L * 4);
+      const uint32_t box = boxes + (uint32_t)(batch & 1) * box_bytes;
+      float gv[kSavedBatch], wv[kSavedBatch];
+      uint32_t c[kSavedBatch];
+      float *terms_dx = a.r.dx + first + j0 * kRecordBlock, *terms_dw = a.r.dw + first + j0 * kRecordBlock;
+#pragma unroll
+      for (int q = 0; q < kSavedBatch / 4; ++q) {
+        const uint4 v = lds_b128(box + tma::swizzled_offset<16>((uint32_t)s, (uint32_t)q));
+        gv[4 * q + 0] = __uint_as_float(v.x);
+        gv[4 * q + 1] = __uint_as_float(v.y);
+        gv[4 * q + 2] = __uint_as_float(v.z);
+        gv[4 * q + 3] = __uint_as_float(v.w);
+      }
+#pragma unroll
+      for (int u = 0; u < kSavedBatch; ++u) {  // (clamped: a forward that gave up on a lost copy leaves records unwritten)
+        const uint32_t where = unpack_where<WT>(wh[u]);
+        wv[u] = lds_f32(w_table + 4u * ((uint32_t)(u * L) + min(where >> 16, (uint32_t)L - 1u)));
+        if (a.gx != nullptr)
+          c[u] = min(lds_b32(o_table + 4u * ((uint32_t)(u * N) + min((where & 0xffffu) - 1u, (uint32_t)N - 1u))),
+                     (uint32_t)C - 1u);
+      }
+#pragma unroll
+      for (int u = 0; u < kSavedBatch; ++u) {
+        const float wg = __fmul_rn(wv[u], gv[u]);
+        const float dx = nm[u] < 0.0f ? wg : (nm[u] > 0.0f ? -wg : __fmul_rn(0.0f, wg));
+        if (a.write_terms) {
+          __stcs(terms_dx + u * kRecordBlock, dx);
+          __stcs(terms_dw + u * kRecordBlock, __fmul_rn(fabsf(nm[u]), gv[u]));
+        }
+        if (a.gx != nullptr) {
+          const uint32_t at = column + c[u] * pitch;
+          sts_f32(at, __fadd_rn(lds_f32(at), dx));
+        }
+      }
+    }
+    __syncthreads();  // every thread is done with this buffer
+    if (s == 0 && batch + 2 < batches && !gave_up) issue(batch + 2);
+  };
+  // while one batch is expanded, the records of the two after it are in flight (rotating the register sets costs a
+  // few moves per evaluation; three unrolled copies of the body ran slower: 9.8 against 8.0 ms for the whole backward
+  // of 2^30 evaluations)
+  for (int batch = 0; batch < batches; ++batch) {
+    fetch(batch + 2, nm2, wh2);
+    expand(batch, nm0, wh0);
+#pragma unroll
+    for (int u = 0; u < kSavedBatch; ++u) {
+      nm0[u] = nm1[u];
+      wh0[u] = wh1[u];
+      nm1[u] = nm2[u];
+      wh1[u] = wh2[u];
+    }
+  }
+  if (a.gx == nullptr) return;
+  __syncthreads();
+  if ((C & 3) == 0) {
+    const int quads = C >> 2;
+    for (int idx = s; idx < S * quads; idx += S) {
+      const int ss = idx % S, q = idx / S;
+      if (row0 + ss < a.B)
+        *(reinterpret_cast<float4 *>(a.gx + (row0 + ss) * C) + q) =
+            make_float4(tile[(4 * q + 0) * S + ss], tile[(4 * q + 1) * S + ss], tile[(4 * q + 2) * S + ss],
+                        tile[(4 * q + 3) * S + ss]);
+    }
+  } else {
+    for (int idx = s; idx < S * C; idx += S) {
+      const int ss = idx % S, c = idx / S;
+      if (row0 + ss < a.B) a.gx[(row0 + ss) * C + c] = tile[c * S + ss];
     }
   }
 }
@@ -912,9 +1026,7 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
   a.gw = gw;
   a.evals = EvalRecords{nullptr, nullptr, nullptr};
   if (eval_records != nullptr) {
-    const size_t floats = record_array_bytes(p, 4);
-    unsigned char *base = static_cast<unsigned char *>(eval_records);
-    a.evals = EvalRecords{reinterpret_cast<float *>(base), reinterpret_cast<float *>(base + floats), base + 2 * floats};
+    a.evals = eval_record_arrays(p, eval_records);
   }
   a.status_word = status_word;
   a.B = p->B * p->K;
@@ -956,6 +1068,53 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
     HT_CHECK_LAUNCH();
   }
   return HT_OK;
+}
+
+// Samples per CTA of expand_saved_kernel: 256 when the gradient tile, the gradient boxes and the table buffers
+// fit, else 128; 0 when even that does not fit.
+static size_t expand_smem_bytes(const ht_forest_problem *p, int S, bool with_tile) {
+  const size_t tables = 2 * saved_table_bytes(threshold_count(p->kind, p->depth), ((int64_t)1) << p->depth);
+  return 1024 + 2 * (size_t)S * kSavedBatch * 4 + tables + 64 + (with_tile ? (size_t)S * p->C * 4 : 0);
+}
+
+int saved_samples_per_cta(const ht_forest_problem *p) {
+  for (int S = 256; S >= 128; S >>= 1)
+    if (expand_smem_bytes(p, S, true) <= kSmemBudget) return S;
+  return 0;
+}
+
+int backward_saved(const ht_forest_problem *p, const int32_t *ord, const float *w, const float *g, float *gx, float *gthr,
+                   float *gw, void *eval_records, cudaStream_t stream) {
+  if (!forward_saves(p) || eval_records == nullptr) return HT_ERR_UNSUPPORTED;
+  if (((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(gx) | reinterpret_cast<uintptr_t>(w) |
+        reinterpret_cast<uintptr_t>(ord)) & 15u) != 0)
+    return HT_ERR_UNSUPPORTED;
+  const int S = saved_samples_per_cta(p);
+  if (S == 0) return HT_ERR_UNSUPPORTED;
+  const int64_t N = threshold_count(p->kind, p->depth);
+  const int64_t L = ((int64_t)1) << p->depth;
+  const bool params = gthr != nullptr || gw != nullptr;
+  ExpandArgs a = {};
+  if (!tma::encode_matrix_f32(&a.g_map, g, p->B, p->T, S, kSavedBatch)) return HT_ERR_UNSUPPORTED;
+  a.r = eval_record_arrays(p, eval_records);
+  a.ord = ord;
+  a.w = w;
+  a.gx = gx;
+  a.B = p->B;
+  a.T = p->T;
+  a.N = (int)N;
+  a.L = (int)L;
+  a.C = (int)p->C;
+  a.write_terms = params ? 1 : 0;
+  const bool narrow = where_bytes(p->depth) == 2;
+  auto kernel = narrow ? expand_saved_kernel<unsigned short> : expand_saved_kernel<uint32_t>;
+  HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
+  kernel<<<(unsigned)((p->B + S - 1) / S), S, expand_smem_bytes(p, S, gx != nullptr), stream>>>(a);
+  HT_CHECK_LAUNCH();
+  if (!params) return HT_OK;
+  // the records now hold what the backward's traversal kernel writes: the same reductions, either mode
+  return narrow ? reduce_parameters<unsigned short>(p, a.r, p->B, N, L, gthr, gw, stream)
+                : reduce_parameters<uint32_t>(p, a.r, p->B, N, L, gthr, gw, stream);
 }
 
 }  // namespace ht

@@ -52,6 +52,8 @@ typedef enum ht_status {
 /* ht_forest_problem.flags */
 #define HT_DETERMINISTIC 1u /* backward: fixed summation order equal to the reference CPU loops */
 #define HT_WORKSPACE_FOR_BACKWARD 2u /* ht_forest_workspace_bytes: include the backward's evaluation records */
+#define HT_SAVE_FOR_BACKWARD 4u /* ht_forest_forward_f32: also leave the traversal in the workspace (see below) */
+#define HT_SAVED_FORWARD 8u     /* ht_forest_backward_f32: the workspace still holds that traversal */
 
 typedef struct ht_forest_problem {
   int32_t kind;   /* HT_KIND_TREE or HT_KIND_FERN */
@@ -71,11 +73,22 @@ int ht_last_cuda_error(void); /* cudaError_t of the last failed runtime call on 
 
 /* Scratch bytes ht_forest_* calls need for this problem: compact ordinals and the tile kernel's
  * per-tree records.  With HT_WORKSPACE_FOR_BACKWARD in p->flags the figure also covers 12 bytes
- * per (sample, tree) of evaluation records, which let ht_forest_backward_f32 run its fastest,
+ * per (sample, tree) of evaluation records (10 up to depth 8), which let ht_forest_backward_f32 run its fastest,
  * fixed-order path on tabular one-output-per-leaf problems (up to 32 GiB; beyond that, and
  * whenever the workspace passed is smaller, the backward uses its other paths).  The workspace
  * must be 256-byte aligned device memory. */
 size_t ht_forest_workspace_bytes(const ht_forest_problem *p);
+
+/* Saving the forward's traversal for the backward.  The reference's backward walks every tree again, three
+ * times (hingetree_gpu.cu:699-727); here a training step can walk them once: ht_forest_forward_f32 called with
+ * HT_SAVE_FOR_BACKWARD and a workspace sized with HT_WORKSPACE_FOR_BACKWARD leaves, per (sample, tree), the
+ * signed margin and the deciding vertex / leaf in the workspace (6 or 8 bytes), and ht_forest_backward_f32
+ * called with HT_SAVED_FORWARD on the SAME x, thr, ord, w and workspace — nothing else having used the
+ * workspace in between — computes the gradients from them.  ht_forest_forward_saves() tells whether the
+ * forward does so for a problem (tabular input, one output per leaf, shapes the tile kernel takes with whole
+ * tree groups); where it returns 0 both flags are ignored.  Both modes: with HT_DETERMINISTIC the sums are
+ * the reference's, bit for bit, as without saving. */
+int ht_forest_forward_saves(const ht_forest_problem *p);
 
 /* out[i,j,k,m] = |margin(i,j,k)| * w[j, leaf(i,j,k), m]
  * Replaces hingetree_gpu_forward / ForwardKernel (hingetree_gpu.cu:416-498, 58-87) and the
@@ -95,7 +108,10 @@ int ht_forest_forward_f32(const ht_forest_problem *p, const float *x, const floa
  *   - A problem whose ht_forest_workspace_bytes() exceeds the array is refused with
  *     HT_ERR_WORKSPACE; use ht_forest_forward_f32 with your own workspace for those.
  *   - The first call on a device looks up the array's device address (once per device, with
- *     that device current); make that first call outside any stream capture.
+ *     that device current); make that first call outside any stream capture.  The address is
+ *     kept for the life of the device's primary context: after cudaDeviceReset() this entry
+ *     point must not be used again in the process.
+ *   - HT_WORKSPACE_FOR_BACKWARD in p->flags is ignored: only the forward's scratch counts.
  *   - All calls on a device share the one array, which simply keeps what the last call wrote;
  *     every byte that is read is rewritten first, so nothing needs clearing.  Two calls that
  *     overlap on the GPU (different streams, or different host threads) race on it: serialise

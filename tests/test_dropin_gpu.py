@@ -46,6 +46,50 @@ def test_operators_match_oracle(ext, kind):
     assert getattr(ext, kind + "_backward")(dx, False, dthr, False, dord, False, dw, False, dg) == [None] * 4
 
 
+def test_module_training_step_keeps_the_forward_traversal(ext):
+    """A module large enough for the tile kernel: the autograd Function keeps the forward's traversal and the
+    backward uses it (ext.tree_forward_saving returns a non-empty scratch); results match the oracle at the
+    usual bars, in default and in deterministic mode, and equal those with keeping switched off."""
+    from hingetreefortorch_b200 import RandomHingeForest as R
+    torch.manual_seed(3)
+    m = R.RandomHingeForest(128, 64, 6, extra_outputs=1).cuda()
+    x = torch.randn(1024, 128, device="cuda", requires_grad=True)
+    w2 = m.weights.detach().reshape(64, 64)
+    assert ext.tree_forward_saving(x.detach(), m.thresholds.detach(), m.ordinals, w2)[1].numel() > 0
+    results = {}
+    for keep in (True, False):
+        ext.set_save_forward(keep)
+        try:
+            for p in (x, m.thresholds, m.weights):
+                p.grad = None
+            y = m(x)
+            (y * y).sum().backward()
+            results[keep] = [t.detach().clone() for t in (y, x.grad, m.thresholds.grad, m.weights.grad)]
+        finally:
+            ext.set_save_forward(True)
+    xn, thr, ord_, w = x.detach().cpu().numpy(), m.thresholds.detach().cpu().numpy(), m.ordinals.cpu().numpy(), m.weights.detach().cpu().numpy()
+    want = ho.forward("tree", xn, thr, ord_, w)
+    g = 2 * want
+    ref = ho.backward("tree", xn, thr, ord_, w, g)
+    mags = ho.backward_magnitudes("tree", xn, thr, ord_, w, g)
+    for keep in (True, False):
+        assert np.array_equal(results[keep][0].cpu().numpy(), want)
+        for t, r, mg in zip(results[keep][1:], ref, mags):
+            assert grad_close(t, r, mg)
+    assert torch.equal(results[True][1], results[False][1])  # the x gradient is added in tree order either way
+    prev = torch.are_deterministic_algorithms_enabled()
+    torch.use_deterministic_algorithms(True)
+    try:
+        for p in (x, m.thresholds, m.weights):
+            p.grad = None
+        y = m(x)
+        (y * y).sum().backward()
+    finally:
+        torch.use_deterministic_algorithms(prev)
+    for t, r in zip((x.grad, m.thresholds.grad, m.weights.grad), ref):
+        assert np.array_equal(t.cpu().numpy(), r)
+
+
 def test_error_contract_on_device(ext):
     x, thr, ord_, w = random_forest_inputs(22, "tree", 8, 5, (), 3, 3, ())
     dx, dthr, dord, dw = dev(x, thr, ord_, w)

@@ -344,3 +344,44 @@ def test_tile_kernel_backward_several_outputs_per_leaf(cabi, kind, shape):
     for got, ref in zip(fd.backward(dx, dthr, dord, dw, dg), (rx, rthr, rw)):
         assert equal(got, ref)
     assert f.ordinal_flags() == 0
+
+
+SAVING_SHAPES = [
+    # kind, B, C, T, depth: shapes the tile kernel takes with whole tree groups, and some it does not save for
+    ("tree", 2048, 128, 64, 8, True),
+    ("tree", 1999, 128, 48, 5, True),    # ragged last sample tile
+    ("fern", 4096, 64, 32, 9, True),     # 16 + 16 bit vertex / leaf records
+    ("tree", 700, 300, 128, 6, True),    # two-byte feature indices, smaller sample tiles
+    ("tree", 2048, 128, 72, 8, False),   # short last tree group
+    ("tree", 64, 16, 8, 4, False),       # too small for the tile kernel
+]
+
+
+@pytest.mark.parametrize("case", SAVING_SHAPES, ids=[str(c[:5]) for c in SAVING_SHAPES])
+def test_backward_from_a_saved_forward(cabi, case):
+    """forward(save) followed by backward(saved): the forward is the same bits, and the gradients computed from
+    the kept traversal meet the same bars as those of the backward that walks the trees again (default mode within
+    1e-5 of the summed magnitudes, fixed-order mode bit-exact).  Where the library does not save, the flags are
+    ignored and the results are those of the plain calls."""
+    kind, B, C, T, depth, saves = case
+    x, thr, ord_, w = random_forest_inputs(SAVING_SHAPES.index(case) + 70, kind, B, C, (), T, depth, ())
+    g = np.random.default_rng(9).standard_normal((B, T)).astype(np.float32)
+    dx, dthr, dord, dw, dg = dev(x, thr, ord_, w, g)
+    want = ho.forward(kind, x, thr, ord_, w)
+    ref = ho.backward(kind, x, thr, ord_, w, g)
+    mags = ho.backward_magnitudes(kind, x, thr, ord_, w, g)
+    for deterministic in (False, True):
+        f = cabi.Forest(kind, dx, dw, deterministic=deterministic)
+        assert f.saves_forward() == saves
+        assert equal(f.forward(dx, dthr, dord, dw, save=True), want)
+        got = f.backward(dx, dthr, dord, dw, dg, saved=True)
+        for t, r, m in zip(got, ref, mags):
+            assert equal(t, r) if deterministic else grad_close(t, r, m)
+        # a subset of the gradients, from a fresh saved forward
+        f.forward(dx, dthr, dord, dw, save=True)
+        only_x = f.backward(dx, dthr, dord, dw, dg, need=(True, False, False), saved=True)
+        assert only_x[1] is None and (equal(only_x[0], ref[0]) if deterministic else grad_close(only_x[0], ref[0], mags[0]))
+        f.forward(dx, dthr, dord, dw, save=True)
+        only_w = f.backward(dx, dthr, dord, dw, dg, need=(False, False, True), saved=True)
+        assert only_w[0] is None and (equal(only_w[2], ref[2]) if deterministic else grad_close(only_w[2], ref[2], mags[2]))
+        assert f.ordinal_flags() == 0

@@ -17,6 +17,7 @@ import pytest
 import torch
 
 from conftest import random_forest_inputs
+from oracle import hinge_oracle as ho
 
 pytestmark = pytest.mark.gpu
 
@@ -45,10 +46,15 @@ def test_static_scratch_forward_matches_workspace_forward(kind, shape):
         if memory_before is None:
             forest.forward_static(dx, dthr, dord, dw, out=torch.empty_like(want))  # first call: address look-up
             torch.cuda.synchronize()
+        # nothing allocated, neither through torch's caching allocator nor behind its back (free device
+        # memory as the driver reports it stays where it was)
         memory_before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]
         got = forest.forward_static(dx, dthr, dord, dw, out=out)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == memory_before
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert np.array_equal(got.cpu().numpy(), ho.forward(kind, x, thr, ord_, w))
         assert forest.ordinal_flags() == 0
         assert torch.equal(got, want), "call %d differs from ht_forest_forward_f32" % call
         results.append(got)
