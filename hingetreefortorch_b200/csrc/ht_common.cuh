@@ -4,7 +4,6 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
 
 #include "hingetree_b200.h"
 
@@ -31,12 +30,6 @@ inline int cuda_fail(cudaError_t e) {
 #define HT_CHECK_LAUNCH() HT_CUDA_TRY(cudaPeekAtLastError())
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-
-// EXPERIMENT ONLY (removed before release): integer knob from the environment.
-inline int tune(const char *name, int dflt) {
-  const char *v = getenv(name);
-  return v == nullptr ? dflt : atoi(v);
-}
 
 __host__ __device__ inline int64_t threshold_count(int kind, int depth) {
   return kind == FERN ? (int64_t)depth : (((int64_t)1) << depth) - 1;

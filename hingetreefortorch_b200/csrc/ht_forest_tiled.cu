@@ -637,7 +637,7 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
   // Full groups of 16 or 32 trees leave as tiled TMA stores when the output admits a tensor map
   // (rows of a multiple of 16 bytes); otherwise, and for a short last group, as row segments.
   a.tma_store = 0;
-  if (tune("HT_TUNE_TMA_STORE", 1) && p->K == 1 && p->M == 1 && plan.per_warp == 4 && (plan.G == 16 || plan.G == 32) && (p->T & 3) == 0 &&
+  if (p->K == 1 && p->M == 1 && plan.per_warp == 4 && (plan.G == 16 || plan.G == 32) && (p->T & 3) == 0 &&
       p->T >= plan.G && tma::encode_matrix_f32(&a.out_map, out, p->B, p->T, 32, plan.G))
     a.tma_store = 1;
   // With few sample tiles the tree groups are split among CTAs (grid.y) so that the SMs are busy in

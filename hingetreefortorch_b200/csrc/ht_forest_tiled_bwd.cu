@@ -544,9 +544,9 @@ __global__ void __launch_bounds__(512, 1) reduce_parameter_records_columns_kerne
   }
 }
 
-// Default mode, trees whose bins fit 16 or 32 times into a third or a sixth of the shared memory: ONE
-// warp per CTA with COLUMNS copies of the tree's bins, [bin][column].  With 32 columns a lane owns its
-// column outright; with 16, lanes l and l + 16 share one and take two turns.  Either way the lanes that
+// Default mode, trees whose bins fit 16 times into a sixth of the shared memory: ONE warp per CTA with
+// COLUMNS copies of the tree's bins, [bin][column].  With 32 columns a lane would own its column outright;
+// with 16 (the form launched), lanes l and l + 16 share one and take two turns.  Either way the lanes that
 // are active together hit distinct banks whatever bins they update, so every load and store is one
 // wavefront for up to 32 terms (the 8-column form above pays a wavefront per 8 terms and a conflict
 // on top).  A lane consumes its records four at a time: the eight bin loads are in flight together,
@@ -960,8 +960,7 @@ int reduce_parameters(const ht_forest_problem *p, const EvalRecords &evals, int6
   // bins that fit 16 times into a sixth of the shared memory: one warp per CTA, each column shared by two
   // lanes, samples split over gridDim.y so that the machine sees several waves of CTAs
   const size_t bins = (size_t)(N + L);
-  int private_columns = bins * 16 * 4 <= 36 * 1024 ? 16 : 0;
-  if (tune("HT_TUNE_PRIVATE", 16) != 16) private_columns = tune("HT_TUNE_PRIVATE", 16);
+  const int private_columns = bins * 16 * 4 <= 36 * 1024 ? 16 : 0;
   if (private_columns != 0 && samples >= 64 * 1024) {
     const size_t private_smem = bins * private_columns * 4;
     const int64_t slots = 148 * (int64_t)(kSmemBudget / (private_smem + 1024));
@@ -970,8 +969,8 @@ int reduce_parameters(const ht_forest_problem *p, const EvalRecords &evals, int6
     splits = std::min<int64_t>(splits, 65535);
     const int64_t blocks_per_split = ((all_blocks + splits - 1) / splits + 1) / 2 * 2;  // whole fetches of 2 blocks
     const dim3 reduce_grid((unsigned)p->T, (unsigned)((all_blocks + blocks_per_split - 1) / blocks_per_split));
-    auto kernel = private_columns == 32 ? reduce_parameter_records_private_kernel<32, 16, WT>
-                                        : reduce_parameter_records_private_kernel<16, 16, WT>;
+    // (32 lane-owned columns leave room for 3 warps per SM only and ran slower: 5.3 against 3.2 ms on 2^30 records)
+    auto kernel = reduce_parameter_records_private_kernel<16, 16, WT>;
     HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget));
     kernel<<<reduce_grid, 32, private_smem, stream>>>(evals, samples, p->T, (int)N, (int)L, blocks_per_split, gthr, gw);
   } else if (warps == 16 && columns >= 4) {
@@ -1038,7 +1037,7 @@ int backward_tiled(const ht_forest_problem *p, const float *x, const float *thr,
   a.per_warp = plan.per_warp;
   // record path, tabular input, groups of 16 or 32 trees: the upstream gradient comes in by tiled TMA loads
   a.tma_g = 0;
-  if (tune("HT_TUNE_TMA_G", 1) && eval_records != nullptr && p->K == 1 && plan.per_warp == 4 && (plan.G == 16 || plan.G == 32) && (p->T & 3) == 0 &&
+  if (eval_records != nullptr && p->K == 1 && plan.per_warp == 4 && (plan.G == 16 || plan.G == 32) && (p->T & 3) == 0 &&
       p->T >= plan.G && tma::encode_matrix_f32(&a.g_map, g, p->B, p->T, plan.S, plan.G))
     a.tma_g = 1;
   // a small batch gives too few sample tiles for 148 SMs: share the tree groups between CTAs

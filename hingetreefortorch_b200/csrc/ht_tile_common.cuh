@@ -45,8 +45,9 @@ struct RecordLayout {
 };
 
 // Trees with one-byte feature indices can store them so that one 4-byte load serves two levels: a
-// word per vertex of every even level >= 2 holding its own index and its two children's (levels 0
-// and 1 come from the record's head).  Word of vertex v (1-based) of even level l: paired_first(l) + v - 2^l.
+// word per vertex of every even level >= 2 holding {its own index, 0, its left child's, its right child's}
+// (levels 0 and 1 come from the record's head, whose last word has the same form).  With the children in
+// bytes 2 and 3 the byte-permute selector of a child is its vertex index's low bit OR-ed into a constant.  Word of vertex v (1-based) of even level l: paired_first(l) + v - 2^l.
 __host__ __device__ constexpr bool paired_ordinals(int kind, int depth, uint32_t ord_size) {
   return kind == TREE && ord_size == 1 && depth >= 3;
 }
@@ -110,18 +111,19 @@ __global__ void repack_records_kernel(const float *__restrict__ thr, const int32
       const uint32_t owner = (level & 1) ? v >> 1 : v;
       const int owner_level = level & ~1;
       const uint32_t word = paired_first(owner_level) + owner - (1u << owner_level);
-      rec[lay.ord + 4u * word + ((level & 1) ? 1u + (v & 1u) : 0u)] = (unsigned char)c;
+      rec[lay.ord + 4u * word + ((level & 1) ? 2u + (v & 1u) : 0u)] = (unsigned char)c;
+      if ((level & 1) == 0) rec[lay.ord + 4u * word + 1u] = 0;
     }
     if (kind == TREE && r < 3) {  // root and its children again, for one broadcast load
       reinterpret_cast<float *>(rec)[r] = t;
-      if (sizeof(OrdT) == 1) rec[12 + r] = (unsigned char)c;
+      if (sizeof(OrdT) == 1) rec[12 + (r == 0 ? 0 : r + 1)] = (unsigned char)c;  // {root, 0, left, right}
     }
     if (kind == TREE && r == 0 && N < 3) {  // depth 1: no children; keep the head defined
       reinterpret_cast<float *>(rec)[1] = 0.0f;
       reinterpret_cast<float *>(rec)[2] = 0.0f;
-      rec[13] = rec[14] = 0;
+      rec[14] = rec[15] = 0;
     }
-    if (kind == TREE && r == 0) rec[15] = 0;
+    if (kind == TREE && r == 0) rec[13] = 0;
   } else if (lay.bytes > lay.w) {  // records that carry the leaf weights
     const int64_t h = r - N;
     reinterpret_cast<float *>(rec + lay.w)[h] = w[j * L + (int64_t)bit_reverse((uint32_t)h, depth)];
@@ -201,6 +203,13 @@ __device__ __forceinline__ uint32_t lds_ord(uint32_t addr) {
   return v;
 }
 
+// Minimum of three with one instruction (a NaN operand is ignored, as by fminf).
+__device__ __forceinline__ float min3(float a, float b, float c) {
+  float r;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 __device__ __forceinline__ uint32_t pick(const uint4 &q, int i) {
   return i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w;
 }
@@ -214,7 +223,7 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
   constexpr bool kPaired = paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT));
   constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC, kPaired);
   uint32_t v[NT];
-  float best[NT], first[NT];
+  float best[NT], first[NT], held[NT];
   if (KIND == FERN) {
     // every lane tests the same decisions: thresholds and feature indices come in 16-byte broadcasts
     constexpr int kPerWord = 4 / (int)sizeof(OrdT);   // feature indices per 32-bit word
@@ -250,6 +259,7 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
     for (int u = 0; u < NT; ++u) {
       v[u] = 1u;
       family[u] = 0u;
+      held[u] = 0.0f;
       if (kHead) head[u] = lds_b128(rec[u]);
     }
 #pragma unroll
@@ -262,15 +272,15 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
           thr = __uint_as_float(head[u].x);
           c = head[u].w & 0xffu;
         } else if (kHead && l == 1) {
-          thr = __uint_as_float((v[u] & 1u) ? head[u].z : head[u].y);
-          c = __byte_perm(head[u].w, 0u, 0x4440u + (v[u] - 1u));
+          thr = __uint_as_float(v[u] == 3u ? head[u].z : head[u].y);
+          c = __byte_perm(head[u].w, 0u, v[u] | 0x4440u);  // v is 2 or 3: the left or the right child's byte
         } else if (kPaired) {
           thr = lds_f32(rec[u] + 4u * v[u] + (lay.thr - 4u));
           if (l % 2 == 0) {
             family[u] = lds_b32(rec[u] + 4u * v[u] + (lay.ord + 4u * paired_first(l) - 4u * (1u << l)));
             c = family[u] & 0xffu;
           } else {
-            c = __byte_perm(family[u], 0u, 0x4441u + (v[u] & 1u));  // byte 1 (left child) or 2 (right child)
+            c = __byte_perm(family[u], 0u, (v[u] & 1u) | 0x4442u);  // byte 2 (left child) or 3 (right child)
           }
         } else {
           thr = lds_f32(rec[u] + 4u * v[u] + (lay.thr - 4u));
@@ -281,8 +291,10 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
         if (l == 0) {
           best[u] = am;
           first[u] = am;
+        } else if (l % 2 == 1) {
+          held[u] = am;  // joins the minimum together with the next level's
         } else {
-          best[u] = fminf(best[u], am);
+          best[u] = min3(best[u], held[u], am);
         }
         v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
       }
@@ -290,6 +302,7 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
   }
 #pragma unroll
   for (int u = 0; u < NT; ++u) {
+    if (DEPTH % 2 == 0 && KIND != FERN) best[u] = fminf(best[u], held[u]);  // the last level was an odd one
     const float am = (first[u] != first[u]) ? first[u] : best[u];
     path[u] = v[u];
     if (WREC)
@@ -335,14 +348,14 @@ __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], const uint3
         c = head[u].w & 0xffu;
       } else if (PAIRED && l == 1) {
         thr = __uint_as_float((at & 1u) ? head[u].z : head[u].y);
-        c = __byte_perm(head[u].w, 0u, 0x4440u + (at - 1u));
+        c = __byte_perm(head[u].w, 0u, at | 0x4440u);
       } else if (PAIRED) {
         thr = lds_f32(rec[u] + 4u * at + (lay.thr - 4u));
         if (l % 2 == 0) {
           family[u] = lds_b32(rec[u] + 4u * at + (lay.ord + 4u * paired_first(l) - 4u * (1u << l)));
           c = family[u] & 0xffu;
         } else {
-          c = __byte_perm(family[u], 0u, 0x4441u + (at & 1u));
+          c = __byte_perm(family[u], 0u, (at & 1u) | 0x4442u);
         }
       } else {
         thr = lds_f32(rec[u] + 4u * at + (lay.thr - 4u));
