@@ -15,8 +15,15 @@ step).  Rank 0 prints ONE JSON line:
                 pinned input copied in and the result copied back inside the timed region
   roofline      algorithmic bytes of one step / measured step time, against the measured HBM peak
   cpu_baseline  the C restatement of the reference algorithm on all host threads (bounded sample)
-  fwd_bwd       (c3 only) forward + backward of the same shape, device resident
+  fwd_bwd       (c3 only) forward + backward of the same shape, device resident: a training step, in which the
+                forward keeps its traversal for the backward; a 64-row slice of it is checked against the port
   cuda_graph    (c1, c2) the same step captured once and replayed as a CUDA graph
+  workloads     (c3 at N = 1) the other configurations c1, c2, c4, c5, a few device-resident steps each, with a
+                slice of each result checked against the port in the CPU leg
+  strong, train (c3 at N > 1) the large batch split over the ranks (no collective; shards compared with the
+                whole on rank 0), and training steps of c2 and c5 with the NCCL all-reduce of the parameter
+                gradients inside the timed region
+  gpu_launches  kernels of this library launched inside the timed region (the library's own counter)
 
 Other workloads: c1 (the reference's speedtest shape, fwd+bwd), c2 (ferns, fwd+bwd), c4 (2-D
 convolution, fwd+bwd), c5 (Linear -> BatchNorm1d -> sequential-ordinal forest training step).
@@ -51,12 +58,9 @@ WORKLOADS = {
 }
 
 
-# DRAM bytes (read + write) of the tile kernel per input row of the c3 shape, from an Nsight Compute
-# capture of the kernel on 65 536 rows (dram__bytes_read.sum + dram__bytes_write.sum =
-# 38 455 040 + 214 589 952 B; the summary is kept with the repository's profile summaries).
-# Traffic grows in proportion to the rows (every CTA handles 256 rows the same way), so the
-# full-size launch is that figure times its rows.
-C3_DRAM_BYTES_PER_ROW = (38455040 + 214589952) / 65536
+# DRAM bytes (read + write) of one full-size launch of the c3 tile kernel, from an Nsight Compute capture of that
+# launch with the two DRAM byte counters alone (one pass, nothing saved or restored); None until it was taken.
+C3_DRAM_BYTES_PER_LAUNCH = None
 
 
 def decisions(kind, depth):
@@ -291,8 +295,8 @@ class ForestRunner:
         self.forest = _cabi.Forest(wl["kind"], self.x, self.w)
         self.out = torch.empty(self.forest.out_shape, dtype=torch.float32, device=device)
         self.g = None
-        # ordinal pack (+ record repack when the tile kernel runs) + the evaluation kernel
-        self.launches = 3 if B * wl["T"] >= 32768 else 2
+        # a training step keeps the forward's traversal for the backward where the library offers it
+        self.keep = self.forest.saves_forward()
 
     def enable_backward(self):
         torch = self.torch
@@ -305,21 +309,14 @@ class ForestRunner:
             self.grads = (torch.empty_like(self.x), self.param_grads[:n].view_as(self.thr),
                           self.param_grads[n:].view_as(self.w))
 
-    def step(self, backward):
-        self.forest.forward(self.x, self.thr, self.ord, self.w, out=self.out)
+    def step(self, backward, reduce=True):
+        keep = backward and self.keep
+        self.forest.forward(self.x, self.thr, self.ord, self.w, out=self.out, save=keep)
         if backward:
-            self.forest.backward(self.x, self.thr, self.ord, self.w, self.g, outs=self.grads)
-            if self.world > 1 and self.wl["bwd"]:  # a training workload: parameter gradients summed over the ranks
+            self.forest.backward(self.x, self.thr, self.ord, self.w, self.g, outs=self.grads, saved=keep)
+            if self.world > 1 and reduce:  # a training step: parameter gradients summed over the ranks
                 import torch.distributed as dist
                 dist.all_reduce(self.param_grads)
-
-    def launches_per_step(self, backward):
-        if not backward:
-            return self.launches
-        # one output per leaf on the tile path: ordinal pack, record repack, traversal, two ordered reductions;
-        # otherwise ordinal pack + the scatter kernel
-        tiled = self.launches == 3 and self.wl["M"] <= 1
-        return self.launches + (5 if tiled else 2)
 
     def check(self):
         if self.forest.ordinal_flags() != 0:
@@ -377,6 +374,11 @@ class ForestRunner:
         if not self.torch.equal(self.out_pinned[:256], self.out[:256].cpu()):
             raise SystemExit("bench.py: end-to-end output differs from the device-resident output")
 
+    def release_e2e(self):
+        self.x_pinned = self.out_pinned = None
+        if self.wl["bwd"]:
+            self.g_pinned = self.gx_pinned = None
+
 
 class ModuleRunner:
     """Workloads driven through the nn.Module surface: convolution (c4) and the Linear->BN->forest pipeline (c5)."""
@@ -410,24 +412,19 @@ class ModuleRunner:
     def enable_backward(self):
         pass
 
-    def _train_step(self, x):
+    def _train_step(self, x, reduce=True):
         for p in self.model.parameters():
             p.grad = None
         if x.grad is not None:
             x.grad = None
         loss = self.model(x).sum()
         loss.backward()
-        if self.bucket is not None:
+        if self.bucket is not None and reduce:
             self.bucket.all_reduce()
         return loss
 
-    def step(self, backward):
-        self._train_step(self.x)
-
-    def launches_per_step(self, backward):
-        # this library's kernels only (torch's GEMM / BN not counted): ordinal pack, record repack and the tile
-        # kernel in each direction; the forest backward adds its two ordered reductions
-        return 6 if self.wl["op"] == "conv" else 8
+    def step(self, backward, reduce=True):
+        self._train_step(self.x, reduce)
 
     def check(self):
         pass
@@ -447,6 +444,206 @@ class ModuleRunner:
         if not self.torch.isfinite(self.loss_host):
             raise SystemExit("bench.py: end-to-end loss is not finite")
 
+    def release_e2e(self):
+        self.x_pinned = None
+
+
+def launch_count():
+    """Kernels the library has launched so far in this process (its own counter)."""
+    from hingetreefortorch_b200 import _cabi
+    return int(_cabi.library().ht_launch_count())
+
+
+def make_runner(wl, B, device, rank, world):
+    runner = ForestRunner(wl, B, device, rank, world) if wl["op"] == "forest" else ModuleRunner(wl, B, device, rank, world)
+    if wl["bwd"]:
+        runner.enable_backward()
+    return runner
+
+
+class Timer:
+    """Times steps with CUDA events on the current stream, bracketed by a barrier and a device synchronisation on
+    both sides; the figure is the maximum over the ranks."""
+
+    def __init__(self, device, world):
+        import torch
+        self.torch, self.device, self.world = torch, device, world
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def run(self, step, steps):
+        """Returns (elapsed ms of all steps, max over ranks; per-step ms on this rank; launches of the library)."""
+        torch = self.torch
+        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        before = launch_count()
+        begin.record()
+        for s, e in events:
+            s.record()
+            step()
+            e.record()
+        end.record()
+        self.barrier()
+        launches = launch_count() - before
+        t = torch.tensor([begin.elapsed_time(end)], dtype=torch.float64, device=self.device)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), [s.elapsed_time(e) for s, e in events], launches
+
+
+def side_workload(key, device, timer, peak, steps=8):
+    """One of the other configurations, device resident, a few steps: what the driver's single run records of it.
+    Returns the figures and what the CPU leg needs to check a slice of the result against the port."""
+    import torch
+    wl = WORKLOADS[key]
+    runner = make_runner(wl, wl["B"], device, 0, 1)
+    for _ in range(3):
+        runner.step(wl["bwd"])
+    ms, _, launches = timer.run(lambda: runner.step(wl["bwd"]), steps)
+    ms /= steps
+    evals = evals_per_step(wl, wl["B"])
+    nbytes = algorithmic_bytes(wl, wl["B"], wl["bwd"])
+    figures = {"workload": wl["name"], "ms_per_step": ms, "value": evals / (ms * 1e-3), "unit": "tree-evals/s",
+               "steps": steps, "bytes_per_step": nbytes, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9,
+               "frac": nbytes / (ms * 1e-3) / 1e9 / peak, "gpu_launches_per_step": launches / steps}
+    check = None
+    rows = min(64, wl["B"])
+    if wl["op"] == "forest":
+        runner.step(True)
+        torch.cuda.synchronize()
+        check = {"kind": wl["kind"], "op": "forest", "x": runner.x[:rows].cpu().numpy(), "thr": runner.thr.cpu().numpy(),
+                 "ord": runner.ord.cpu().numpy(), "w": runner.w.cpu().numpy(), "g": runner.g[:rows].cpu().numpy(),
+                 "out": runner.out[:rows].cpu().numpy(), "gx": runner.grads[0][:rows].cpu().numpy()}
+    elif wl["op"] == "conv":
+        module = runner.model
+        x1 = runner.x[:1].detach()
+        with torch.no_grad():
+            out1 = module(x1)
+        check = {"kind": wl["kind"], "op": "conv", "x": x1.cpu().numpy(), "thr": module.thresholds.detach().cpu().numpy(),
+                 "ord": module.ordinals.cpu().numpy(), "w": module.weights.detach().cpu().numpy(), "out": out1.cpu().numpy()}
+    else:  # the pipeline's forest stage on the normalised activations the model itself produced
+        lin, bn, forest = runner.model[0], runner.model[1], runner.model[2]
+        with torch.no_grad():
+            z = bn(lin(runner.x))[:rows].contiguous()
+            out = forest(z)
+        check = {"kind": wl["kind"], "op": "forest", "x": z.cpu().numpy(), "thr": forest.thresholds.detach().cpu().numpy(),
+                 "ord": forest.ordinals.cpu().numpy(), "w": forest.weights.detach().cpu().numpy(), "out": out.cpu().numpy()}
+    del runner
+    torch.cuda.empty_cache()
+    return figures, check
+
+
+def check_against_port(check):
+    """CPU leg: a slice of a workload's device result against the C restatement of the reference algorithm.
+    Forward bit for bit; the x gradient (where kept) within 1e-5 of the summed term magnitudes."""
+    import numpy as np
+    from oracle import hinge_oracle as ho
+    if check["op"] == "conv":
+        want = ho.conv_forward(check["kind"], check["x"], check["thr"], check["ord"], check["w"], (3, 3), (1, 1), (1, 1), (1, 1))
+    else:
+        want = ho.forward(check["kind"], check["x"], check["thr"], check["ord"], check["w"])
+    ok = bool(np.array_equal(want.reshape(check["out"].shape), check["out"]))
+    if ok and "gx" in check:
+        ref = ho.backward(check["kind"], check["x"], check["thr"], check["ord"], check["w"], check["g"])[0]
+        mag = ho.magnitudes(ho.backward, check["kind"], check["x"], check["thr"], check["ord"], check["w"], check["g"])[0]
+        ok = bool(np.all(np.abs(check["gx"].astype(np.float64) - ref) <= 1e-5 * mag + 1e-30))
+    return ok
+
+
+def bind_to_gpu_numa_node(local):
+    """Best effort: run this rank (and first-touch its pinned buffers) on the host cores next to its GPU.
+    Returns what was done, for the end-to-end record."""
+    try:
+        import torch
+        props = torch.cuda.get_device_properties(local)
+        bus = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        node = int(open("/sys/bus/pci/devices/%s/numa_node" % bus).read())
+        if node < 0:
+            return {"node": None}
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        usable = cpus & os.sched_getaffinity(0)
+        if usable:
+            os.sched_setaffinity(0, usable)
+        return {"node": node, "cpus": len(usable)}
+    except Exception as exc:  # no sysfs entry, no such attribute: leave the affinity alone
+        return {"node": None, "why": type(exc).__name__}
+
+
+def scale_legs(a, device, rank, world, timer, peak):
+    """N > 1 only.  `strong`: the large-batch forward with its 1 048 576 rows split over the ranks (no communication),
+    checked by comparing sampled rows of every shard with rank 0's evaluation of the whole batch.  `train`: training
+    steps of the fern and the pipeline configurations with the all-reduce of the parameter gradients inside the timed
+    region, next to the same step without it and the all-reduce alone."""
+    import torch
+    import torch.distributed as dist
+    from hingetreefortorch_b200 import _cabi
+    from hingetreefortorch_b200.distributed import shard_bounds
+    out = {}
+    wl = WORKLOADS["c3"]
+    B = wl["B"]
+    lo, hi = shard_bounds(B, rank, world)
+    gen = torch.Generator().manual_seed(4242)
+    x_all = torch.randn((B, wl["C"]), generator=gen)  # the same batch on every rank
+    thr, ord_, w = [t.to(device) for t in make_params(wl)]
+    x = x_all[lo:hi].to(device)
+    forest = _cabi.Forest(wl["kind"], x, w, backward_workspace=False)
+    res = torch.empty(forest.out_shape, dtype=torch.float32, device=device)
+    step = lambda: forest.forward(x, thr, ord_, w, out=res)
+    for _ in range(3):
+        step()
+    steps = max(3, min(a.steps, 20))
+    ms, _, _ = timer.run(step, steps)
+    ms /= steps
+    # sampled rows of every shard against the whole batch evaluated on rank 0
+    picks = torch.linspace(0, hi - lo - 1, 64).long().to(device)
+    mine = torch.cat([res[picks], (picks + lo).float().unsqueeze(1)], dim=1)
+    gathered = [torch.empty_like(mine) for _ in range(world)] if rank == 0 else None
+    dist.gather(mine, gathered, dst=0)
+    equal = None
+    if rank == 0:
+        xg = x_all.to(device)
+        whole = _cabi.Forest(wl["kind"], xg, w, backward_workspace=False).forward(xg, thr, ord_, w)
+        equal = all(bool(torch.equal(t[:, :-1], whole[t[:, -1].long()])) for t in gathered)
+        del whole, xg
+    nbytes = algorithmic_bytes(wl, B, False)
+    out["strong"] = {"workload": wl["name"], "rows_per_gpu": hi - lo, "ms_per_step": ms, "steps": steps,
+                     "value": B * wl["T"] / (ms * 1e-3), "unit": "tree-evals/s", "collective": None,
+                     "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_n_gpus": nbytes / (ms * 1e-3) / 1e9 / (peak * world),
+                     "shards_equal_whole": equal}
+    del forest, res, x, x_all
+    torch.cuda.empty_cache()
+
+    train = {}
+    for key in ("c2", "c5"):
+        twl = WORKLOADS[key]
+        runner = make_runner(twl, twl["B"], device, rank, world)
+        for _ in range(3):
+            runner.step(True)
+        steps = 10
+        with_ms, _, _ = timer.run(lambda: runner.step(True), steps)
+        without_ms, _, _ = timer.run(lambda: runner.step(True, reduce=False), steps)
+        bucket = runner.param_grads if twl["op"] == "forest" else runner.bucket.flat
+        alone_ms, _, _ = timer.run(lambda: dist.all_reduce(bucket), steps)
+        nbytes = bucket.numel() * 4
+        train[key] = {"workload": twl["name"], "rows_per_gpu": twl["B"], "ms_per_step": with_ms / steps,
+                      "ms_per_step_without_allreduce": without_ms / steps, "allreduce_alone_ms": alone_ms / steps,
+                      "bucket_bytes": nbytes, "value": evals_per_step(twl, twl["B"]) * world / (with_ms / steps * 1e-3),
+                      "unit": "tree-evals/s (weak: every rank its own batch)",
+                      "allreduce_bus_gbs": 2 * (world - 1) / world * nbytes / (alone_ms / steps * 1e-3) / 1e9}
+        del runner
+        torch.cuda.empty_cache()
+    out["train"] = train
+    return out
+
 
 def our_arm(a, wl):
     import torch
@@ -459,46 +656,30 @@ def our_arm(a, wl):
         raise SystemExit("bench.py: no CUDA device; the product arm has no CPU path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(local) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
     B = a.rows or wl["B"]
     if a.linear == "tf32":
         torch.backends.cuda.matmul.allow_tf32 = True
-    runner = ForestRunner(wl, B, device, rank, world) if wl["op"] == "forest" else ModuleRunner(wl, B, device, rank, world)
-    if wl["bwd"]:
-        runner.enable_backward()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(steps, backward):
-        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        begin.record()
-        for s, e in events:
-            s.record()
-            runner.step(backward)
-            e.record()
-        end.record()
-        barrier()
-        t = torch.tensor([begin.elapsed_time(end)], dtype=torch.float64, device=device)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()), [s.elapsed_time(e) for s, e in events]
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    timer = Timer(device, world)
+    runner = make_runner(wl, B, device, rank, world)
 
     for _ in range(a.warmup):
         runner.step(wl["bwd"])
-    barrier()
+    timer.barrier()
     runner.check()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    elapsed_ms, per_step_ms = timed(a.steps, wl["bwd"])
+    elapsed_ms, per_step_ms, launches = timer.run(lambda: runner.step(wl["bwd"]), a.steps)
     clocks = sampler.stop() if rank == 0 else None
     evals = evals_per_step(wl, B)
     value = evals * world * a.steps / (elapsed_ms * 1e-3)
@@ -510,17 +691,28 @@ def our_arm(a, wl):
             dist.destroy_process_group()
         return
 
-    # forward + backward of the inference shape, as a second device-resident figure
+    checks = {}  # slices of device results for the CPU leg to compare with the port
+
+    # forward + backward of the inference shape (a training step: the forward keeps its traversal for the
+    # backward), as a second device-resident figure
     fwd_bwd = None
     if wl["op"] == "forest" and not wl["bwd"]:
         runner.enable_backward()
-        runner.step(True)
-        fb_steps = max(1, min(a.steps, 3))
-        fb_ms, _ = timed(fb_steps, True)
+        runner.step(True, reduce=False)
+        fb_steps = max(1, min(a.steps, 5))
+        fb_ms, _, fb_launches = timer.run(lambda: runner.step(True, reduce=False), fb_steps)
         fb_bytes = algorithmic_bytes(wl, B, True)
         fwd_bwd = {"value": evals * world * fb_steps / (fb_ms * 1e-3), "unit": "tree-evals/s",
                    "ms_per_step": fb_ms / fb_steps, "steps": fb_steps, "bytes_per_step": fb_bytes,
-                   "achieved_gbs": fb_bytes / (fb_ms / fb_steps * 1e-3) / 1e9}
+                   "achieved_gbs": fb_bytes / (fb_ms / fb_steps * 1e-3) / 1e9, "gpu_launches": fb_launches,
+                   "forward_keeps_traversal": bool(runner.keep)}
+        fwd_bwd["frac"] = fwd_bwd["achieved_gbs"] / peak
+        if rank == 0 and world == 1:
+            rows = 64
+            checks["fwd_bwd"] = {"kind": wl["kind"], "op": "forest", "x": runner.x[:rows].cpu().numpy(),
+                                 "thr": runner.thr.cpu().numpy(), "ord": runner.ord.cpu().numpy(), "w": runner.w.cpu().numpy(),
+                                 "g": runner.g[:rows].cpu().numpy(), "out": runner.out[:rows].cpu().numpy(),
+                                 "gx": runner.grads[0][:rows].cpu().numpy()}
         runner.g = runner.grads = runner.param_grads = None
         torch.cuda.empty_cache()
 
@@ -528,34 +720,14 @@ def our_arm(a, wl):
     # allocates nor synchronises, so a step is capturable as it stands
     cuda_graph = None
     if wl["op"] == "forest" and B * wl["T"] <= 4096 * 1024 and world == 1:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            runner.step(wl["bwd"])
-        torch.cuda.current_stream().wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            runner.step(wl["bwd"])
-        for _ in range(3):
-            graph.replay()
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        replays = max(a.steps, 50)
-        torch.cuda.synchronize()
-        begin.record()
-        for _ in range(replays):
-            graph.replay()
-        end.record()
-        torch.cuda.synchronize()
-        graph_ms = begin.elapsed_time(end) / replays
-        cuda_graph = {"ms_per_step": graph_ms, "value": evals / (graph_ms * 1e-3), "unit": "tree-evals/s", "steps": replays}
-        runner.check()
+        cuda_graph = graph_replay(runner, wl, evals, a.steps)
 
     # ---- end to end through the reference-facing surface, host buffers in and out -------------
     h2d, d2h, call = runner.prepare_e2e()
     e2e_steps = max(1, min(a.steps, 5))
     for _ in range(2):
         runner.e2e_step()
-    barrier()
+    timer.barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         runner.e2e_step()
@@ -565,21 +737,33 @@ def our_arm(a, wl):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = evals * world * e2e_steps / float(t.item())
     runner.verify_e2e()
+    runner.release_e2e()
+
+    # ---- what else one run records: the other configurations (N = 1), the collective and the split (N > 1) ----
+    workloads, scale = None, None
+    if a.workload == "c3" and not a.rows and not a.lean:
+        del runner
+        torch.cuda.empty_cache()
+        if world == 1:
+            workloads = {}
+            for key in ("c1", "c2", "c4", "c5"):
+                workloads[key], checks[key] = side_workload(key, device, timer, peak)
+        else:
+            scale = scale_legs(a, device, rank, world, timer, peak)
 
     if rank == 0:
-        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        if os.path.exists(peaks_path):
-            peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
-        else:
-            peak, peak_src = 6650.0, "fallback"
         launch_ms = statistics.mean(per_step_ms)
         bytes_per_step = algorithmic_bytes(wl, B, wl["bwd"])
         achieved = bytes_per_step / (launch_ms * 1e-3) / 1e9
-        if fwd_bwd is not None:
-            fwd_bwd["frac"] = fwd_bwd["achieved_gbs"] / peak
+        # CPU leg: the port timed on the host cores, and, as the checker, slices of this run's device results
         cores = os.cpu_count() or 1
         sample_rows = cpu_sample_rows(wl, cores)
         cpu_value, cpu_dt = cpu_port_rate(wl, sample_rows, cores)
+        parity = {name: check_against_port(c) for name, c in checks.items() if c is not None}
+        if fwd_bwd is not None and "fwd_bwd" in parity:
+            fwd_bwd["slice_matches_port"] = parity.pop("fwd_bwd")
+        for key, ok in parity.items():
+            workloads[key]["slice_matches_port"] = ok
         line = {
             "metric": "tree-evals/sec " + ("fwd+bwd" if wl["bwd"] else "fwd"),
             "value": value, "unit": "tree-evals/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
@@ -587,29 +771,60 @@ def our_arm(a, wl):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl["name"] + ("" if B == wl["B"] else " (rows overridden)") +
                        (" [Linear in tf32]" if a.linear == "tf32" and wl["op"] == "pipeline" else ""), "rows_per_gpu": B,
-                       "l2": "inputs and outputs exceed L2 (126 MB)" if bytes_per_step > 4 * 126e6
-                       else "working set fits L2; launch-latency regime",
+                       "l2": "inputs and outputs exceed L2 (126 MB): no flush between iterations" if bytes_per_step > 126e6
+                       else "working set fits L2 (126 MB); launch-latency regime",
                        "parallelism": "batch-sharded x%d, replicated parameters%s"
                        % (world, ", one NCCL all-reduce of parameter gradients per step"
                           if world > 1 and wl["bwd"] else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": C3_DRAM_BYTES_PER_ROW * B if a.workload == "c3" else None,
+                         "traffic": C3_DRAM_BYTES_PER_LAUNCH if a.workload == "c3" and B == wl["B"] else None,
                          "peak_source": peak_src, "bytes_per_launch": bytes_per_step,
                          "launch_ms": launch_ms, "frac_of_8TBs": achieved / 8000.0},
             "cpu_baseline": {"value": cpu_value, "unit": "tree-evals/s", "cores": cores, "kind": "port",
                              "sample": "forward of %d of %d rows, %.1f s" % (sample_rows, wl["B"], cpu_dt)},
             "e2e": {"value": e2e_value, "unit": "tree-evals/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "call": call},
-            "gpu_launches": a.steps * runner.launches_per_step(wl["bwd"]),
+            "gpu_launches": launches,
             "clocks": clocks,
         }
+        if numa is not None:
+            line["e2e"]["host_binding"] = numa
         if fwd_bwd is not None:
             line["fwd_bwd"] = fwd_bwd
         if cuda_graph is not None:
             line["cuda_graph"] = cuda_graph
+        if workloads is not None:
+            line["workloads"] = workloads
+        if scale is not None:
+            line.update(scale)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def graph_replay(runner, wl, evals, steps):
+    import torch
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        runner.step(wl["bwd"])
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        runner.step(wl["bwd"])
+    for _ in range(3):
+        graph.replay()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    replays = max(steps, 50)
+    torch.cuda.synchronize()
+    begin.record()
+    for _ in range(replays):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    graph_ms = begin.elapsed_time(end) / replays
+    runner.check()
+    return {"ms_per_step": graph_ms, "value": evals / (graph_ms * 1e-3), "unit": "tree-evals/s", "steps": replays}
 
 
 def main():
@@ -622,6 +837,8 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="rows per GPU instead of the workload's (profiler captures)")
     ap.add_argument("--linear", default="fp32", choices=["fp32", "tf32"],
                     help="c5 only: arithmetic of torch's Linear (cuBLAS); the forest stage is fp32 either way")
+    ap.add_argument("--lean", action="store_true",
+                    help="c3 only: skip the other configurations (N = 1) and the strong-scaling / training legs (N > 1)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="time the device-resident step only (profiler captures): no end-to-end and no CPU leg")
     a = ap.parse_args()

@@ -20,7 +20,7 @@ HT_FLAG_PIPELINE_TIMEOUT = 0x80000000  # a bounded wait inside a kernel ran out:
 
 # every symbol include/hingetree_b200.h declares (checked by the CPU test-suite)
 SYMBOLS = [
-    "ht_version", "ht_status_string", "ht_last_cuda_error", "ht_forest_workspace_bytes", "ht_forest_forward_saves",
+    "ht_version", "ht_status_string", "ht_last_cuda_error", "ht_forest_workspace_bytes", "ht_forest_forward_saves", "ht_launch_count",
     "ht_forest_forward_f32", "ht_forest_leafmap_f32", "ht_forest_marginmap_f32",
     "ht_forest_reachability_f32", "ht_forest_backward_f32",
     "ht_forest_static_scratch_bytes", "ht_forest_forward_static_f32",
@@ -136,6 +136,7 @@ def library():
         lib.ht_forest_workspace_bytes.restype = ctypes.c_size_t
         lib.ht_forest_workspace_bytes.argtypes = [ctypes.POINTER(ForestProblem)]
         lib.ht_forest_static_scratch_bytes.restype = ctypes.c_size_t
+        lib.ht_launch_count.restype = ctypes.c_uint64
         _lib = lib
     return _lib
 

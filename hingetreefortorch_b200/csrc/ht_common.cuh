@@ -26,8 +26,15 @@ inline int cuda_fail(cudaError_t e) {
     if (_e != cudaSuccess) return ::ht::cuda_fail(_e);      \
   } while (0)
 
-// Checks the launch that was just issued (never synchronises).
-#define HT_CHECK_LAUNCH() HT_CUDA_TRY(cudaPeekAtLastError())
+// Kernel launches issued by this library in this process (ht_launch_count()).
+void count_launch();
+
+// Checks the launch that was just issued (never synchronises) and counts it.
+#define HT_CHECK_LAUNCH()                    \
+  do {                                       \
+    ::ht::count_launch();                    \
+    HT_CUDA_TRY(cudaPeekAtLastError());      \
+  } while (0)
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 

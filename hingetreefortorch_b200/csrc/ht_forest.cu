@@ -4,12 +4,17 @@
 // parameters and the input through L1/L2.  They accept every shape the reference accepts
 // (any C, K, M, depth up to 31).  Shapes the shared-memory tile kernel (ht_forest_tiled.cu)
 // can take are routed there by ht_forest_forward_f32.
+#include <atomic>
+
 #include "ht_common.cuh"
 #include "ht_forest_tiled.cuh"
 
 namespace ht {
 
 thread_local int g_last_cuda_error = 0;
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 namespace {
 
@@ -314,6 +319,8 @@ extern "C" {
 int ht_version(void) { return 100; }
 
 int ht_last_cuda_error(void) { return ht::g_last_cuda_error; }
+
+uint64_t ht_launch_count(void) { return ht::g_launches.load(std::memory_order_relaxed); }
 
 const char *ht_status_string(int status) {
   switch (status) {

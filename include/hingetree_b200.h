@@ -70,6 +70,7 @@ typedef struct ht_forest_problem {
 int ht_version(void);
 const char *ht_status_string(int status);
 int ht_last_cuda_error(void); /* cudaError_t of the last failed runtime call on this thread */
+uint64_t ht_launch_count(void); /* kernels this library has launched in this process (diagnostics; no reference counterpart) */
 
 /* Scratch bytes ht_forest_* calls need for this problem: compact ordinals and the tile kernel's
  * per-tree records.  With HT_WORKSPACE_FOR_BACKWARD in p->flags the figure also covers 12 bytes
