@@ -28,7 +28,7 @@ SYMBOLS = [
     "ht_forest_linear_workspace_bytes", "ht_forest_linear_forward_f32", "ht_forest_linear_backward_f32",
     "ht_conv_output_size", "ht_conv_workspace_bytes", "ht_conv_forward_f32", "ht_conv_backward_f32",
     "ht_contract", "ht_expand",
-    "ht_trie_forward_f32", "ht_trie_backward_f32", "ht_forest_touched_f32",
+    "ht_trie_forward_f32", "ht_trie_backward_f32", "ht_forest_touched_f32", "ht_linear_tf32_stats_f32",
 ]
 
 
@@ -307,3 +307,17 @@ class ForestFamily:
                                                        _ptr(ord_), _ptr(w), _ptr(lin), _ptr(g), _ptr(gx), _ptr(gvec),
                                                        _ptr(gthr), _ptr(gw), _ptr(glin), *self._tail(x)))
         return gx, gvec, gthr, gw, glin
+
+
+def linear_tf32_stats(x, w, status=None):
+    """z = x @ w.T on the tensor cores (TF32 products, fp32 accumulation) with the column sums and sums of
+    squares of z: returns (z [M, N], colsum [N], colsumsq [N])."""
+    import torch
+    M, K = x.shape
+    N = w.shape[0]
+    z = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    colsum = torch.empty(N, dtype=torch.float32, device=x.device)
+    colsumsq = torch.empty(N, dtype=torch.float32, device=x.device)
+    _check(library().ht_linear_tf32_stats_f32(_ptr(x), _ptr(w), _ptr(z), _ptr(colsum), _ptr(colsumsq), ctypes.c_int64(M),
+                                              ctypes.c_int64(N), ctypes.c_int64(K), _ptr(status), _stream(x)))
+    return z, colsum, colsumsq

@@ -377,6 +377,29 @@ std::vector<torch::Tensor> forest_backward_saved(int kind, bool deterministic, t
   return grads;
 }
 
+// ---- dense projection with batch-normalisation statistics on the tensor cores --------------------------------
+// Not part of the reference's operator set (its pipelines call torch.nn.Linear and torch.nn.BatchNorm1d,
+// README.md:110-129).  Returns {z = x w^T (TF32 products, fp32 accumulation), column sums of z, column sums of z^2}.
+std::vector<torch::Tensor> linear_tf32_stats(torch::Tensor x, torch::Tensor w) {
+  if (x.scalar_type() != torch::kFloat32 || w.scalar_type() != torch::kFloat32)
+    bad_argument("Error: x and w are expected to be torch.float32.");
+  if (x.device() != w.device()) bad_argument("Error: All tensors are expected to be on the same device.");
+  require_cuda(x);
+  if (x.dim() != 2 || w.dim() != 2 || x.size(1) != w.size(1))
+    bad_argument("Error: x must be [M, K] and w [N, K].");
+  if (!x.is_contiguous() || !w.is_contiguous()) bad_argument("Error: All tensors are expected to be contiguous.");
+  c10::DeviceGuard guard(x.device());
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  torch::Tensor z = torch::empty({M, N}, x.options());
+  torch::Tensor sum = torch::empty({N}, x.options()), sumsq = torch::empty({N}, x.options());
+  torch::Tensor status = sticky_word(x.device(), true);
+  raise_status(ht_linear_tf32_stats_f32(x.data_ptr<float>(), w.data_ptr<float>(), z.data_ptr<float>(), sum.data_ptr<float>(),
+                                        sumsq.data_ptr<float>(), M, N, K,
+                                        reinterpret_cast<uint32_t *>(status.data_ptr<int32_t>()), current_stream(x)),
+               "linear (tf32) with column statistics");
+  return {z, sum, sumsq};
+}
+
 torch::Tensor forest_leafmap(int kind, torch::Tensor x, torch::Tensor thr, torch::Tensor ord, torch::Tensor w) {
   ForestCall call(kind, x, thr, ord, w, nullptr);
   c10::DeviceGuard guard(x.device());
@@ -629,6 +652,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_backward_scratch_limit", &set_backward_scratch_limit,
         "Upper bound in bytes on the scratch a default-mode backward call allocates for its per-evaluation records "
         "(12 bytes per tree evaluation); above it the gradients are scattered with atomics instead. Default: no bound.");
+  m.def("linear_tf32_stats", &linear_tf32_stats,
+        "z = x @ w.T on the tensor cores (TF32 products, fp32 accumulation) and the column sums of z and z*z: "
+        "[z, sum, sumsq]. K and N must be multiples of 4.");
   m.def("set_save_forward", [](bool on) { g_save_forward = on; },
         "Whether tree_/fern_forward_saving keep the traversal for the backward (default) or act as the plain forward.");
   m.def("pipeline_status", &pipeline_status,

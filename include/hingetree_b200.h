@@ -190,6 +190,18 @@ int ht_forest_linear_backward_f32(const ht_forest_problem *p, int64_t out_channe
                                   float *glin, void *workspace, size_t workspace_bytes, uint32_t *status_word,
                                   ht_stream_t stream);
 
+/* ---- dense projection with batch-normalisation statistics, on the tensor cores -------------------
+ *   z[M,N] = x[M,K] * w[N,K]^T        colsum[n] = sum_m z[m,n]        colsumsq[n] = sum_m z[m,n]^2
+ * x, w, z row-major fp32; the products are taken in TF32 (tcgen05.mma.kind::tf32: the operands' upper 19 bits),
+ * accumulated in fp32; z differs from an fp32 product by about 1e-3 relative to sum_k |x||w|.  colsum / colsumsq
+ * [N] are cleared here.  K and N must be multiples of 4 and x, w, z 16-byte aligned (HT_ERR_UNSUPPORTED otherwise).
+ * No workspace.  This is the front of the reference's sequential-initialisation pipeline, Linear ->
+ * BatchNorm1d(affine=False) -> RandomHingeForest(init_type="sequential") (README.md:110-129,
+ * RandomHingeForest/_RandomHingeForest.py:56-59), where the reference calls torch.nn.Linear and lets BatchNorm
+ * read the activations again for its statistics; the reference has no operator of its own for it. */
+int ht_linear_tf32_stats_f32(const float *x, const float *w, float *z, float *colsum, float *colsumsq, int64_t M,
+                             int64_t N, int64_t K, uint32_t *status_word, ht_stream_t stream);
+
 /* ---- hinge trie ---------------------------------------------------------------------------------
  *   out[i,j,k,m] = sum over depth d (ascending) of |margin_d| * w[j, vertex_d, m]
  * every decision on the path contributes; w is [T, 2^depth - 1, M], one row per internal vertex
