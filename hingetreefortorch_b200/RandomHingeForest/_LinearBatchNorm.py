@@ -16,26 +16,50 @@ import torch.nn as nn
 from .._ext import hingetree_cpp
 
 
-class _LinearStats(torch.autograd.Function):
-    """(z, sum_m z, sum_m z*z) = f(x, w) with z = x @ w.T; TF32 products, fp32 accumulation."""
+class _LinearBatchNorm(torch.autograd.Function):
+    """y = (z - mean) * invstd with z = x @ w.T (TF32 products, fp32 accumulation) and mean / invstd either the batch
+    statistics of z, which come out of the projection kernel's epilogue, or given ones.
+
+    The normalisation and its backward use ATen's fused element-wise and reduction kernels for batch normalisation
+    (the ones torch.nn.SyncBatchNorm is built from), so the activations are read once in the forward and twice in
+    the backward.  The weight (and input) gradients are products of the same size as the forward's and are taken in
+    TF32 as well, by torch.matmul."""
 
     @staticmethod
-    def forward(ctx, x, w):
-        z, total, total_sq = hingetree_cpp.linear_tf32_stats(x.contiguous(), w.contiguous())
-        ctx.save_for_backward(x, w, z)
-        return z, total, total_sq
+    def forward(ctx, x, w, eps, given_mean, given_var):
+        x, w = x.contiguous(), w.contiguous()
+        z, total, total_sq = hingetree_cpp.linear_tf32_stats(x, w)
+        rows = x.shape[0]
+        if given_mean is None:
+            mean = total / rows
+            var = (total_sq / rows - mean * mean).clamp_min_(0.0)
+        else:
+            mean, var = given_mean, given_var
+        invstd = torch.rsqrt(var + eps)
+        y = torch.batch_norm_elemt(z, None, None, mean, invstd, eps)
+        ctx.batch_statistics = given_mean is None
+        ctx.save_for_backward(x, w, z, mean, invstd)
+        ctx.mark_non_differentiable(mean, var)
+        return y, mean, var
 
     @staticmethod
-    def backward(ctx, grad_z, grad_total, grad_total_sq):
-        x, w, z = ctx.saved_tensors
-        g = grad_z
-        if grad_total is not None:
-            g = g + grad_total.unsqueeze(0)
-        if grad_total_sq is not None:
-            g = torch.addcmul(g, z, grad_total_sq.unsqueeze(0), value=2.0)
-        grad_x = g @ w if ctx.needs_input_grad[0] else None
-        grad_w = g.t() @ x if ctx.needs_input_grad[1] else None
-        return grad_x, grad_w
+    def backward(ctx, grad_y, _grad_mean, _grad_var):
+        x, w, z, mean, invstd = ctx.saved_tensors
+        grad_y = grad_y.contiguous()
+        if ctx.batch_statistics:
+            sum_dy, sum_dy_xmu, _, _ = torch.batch_norm_backward_reduce(grad_y, z, mean, invstd, None, True, False, False)
+            count = torch.full((1,), z.shape[0], dtype=torch.int32, device=z.device)
+            grad_z = torch.batch_norm_backward_elemt(grad_y, z, mean, invstd, None, sum_dy, sum_dy_xmu, count)
+        else:
+            grad_z = grad_y * invstd
+        previous = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        try:
+            grad_x = grad_z @ w if ctx.needs_input_grad[0] else None
+            grad_w = grad_z.t() @ x if ctx.needs_input_grad[1] else None
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = previous
+        return grad_x, grad_w, None, None, None
 
 
 class LinearBatchNorm1d(nn.Module):
@@ -55,19 +79,15 @@ class LinearBatchNorm1d(nn.Module):
         self.register_buffer("num_batches_tracked", torch.tensor(0, dtype=torch.long))
 
     def forward(self, x):
-        z, total, total_sq = _LinearStats.apply(x, self.weight)
-        if self.training:
+        if not self.training:
+            return _LinearBatchNorm.apply(x, self.weight, self.eps, self.running_mean, self.running_var)[0]
+        y, mean, var = _LinearBatchNorm.apply(x, self.weight, self.eps, None, None)
+        with torch.no_grad():
             rows = x.shape[0]
-            mean = total / rows
-            var = (total_sq / rows - mean * mean).clamp_min(0.0)
-            with torch.no_grad():
-                self.num_batches_tracked += 1
-                unbiased = var * (rows / max(rows - 1, 1))
-                self.running_mean.lerp_(mean.detach(), self.momentum)
-                self.running_var.lerp_(unbiased.detach(), self.momentum)
-        else:
-            mean, var = self.running_mean, self.running_var
-        return (z - mean) * torch.rsqrt(var + self.eps)
+            self.num_batches_tracked += 1
+            self.running_mean.lerp_(mean, self.momentum)
+            self.running_var.lerp_(var * (rows / max(rows - 1, 1)), self.momentum)
+        return y
 
     def extra_repr(self):
         return "in_features=%d, out_features=%d, eps=%g, momentum=%g" % (self.in_features, self.out_features, self.eps,

@@ -23,6 +23,8 @@ SYMBOLS = [
     "ht_version", "ht_status_string", "ht_last_cuda_error", "ht_forest_workspace_bytes", "ht_forest_forward_saves", "ht_launch_count",
     "ht_forest_forward_f32", "ht_forest_leafmap_f32", "ht_forest_marginmap_f32",
     "ht_forest_reachability_f32", "ht_forest_backward_f32",
+    "ht_forest_forward_f64", "ht_forest_leafmap_f64", "ht_forest_marginmap_f64", "ht_forest_reachability_f64",
+    "ht_forest_backward_f64",
     "ht_forest_static_scratch_bytes", "ht_forest_forward_static_f32",
     "ht_forest_fusion_workspace_bytes", "ht_forest_fusion_forward_f32", "ht_forest_fusion_backward_f32",
     "ht_forest_linear_workspace_bytes", "ht_forest_linear_forward_f32", "ht_forest_linear_backward_f32",

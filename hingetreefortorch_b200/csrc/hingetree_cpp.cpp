@@ -70,7 +70,8 @@ void require_cuda(const torch::Tensor &t) {
 void require_float32(const torch::Tensor &t) {
   if (t.scalar_type() == torch::kFloat32) return;
   if (t.scalar_type() == torch::kFloat64)
-    bad_argument("Error: torch.float64 is not supported by this build; only torch.float32 is.");
+    bad_argument("Error: torch.float64 is supported by the plain tree / fern operators only (forward, backward, "
+                 "backward_deterministic, leafmap, marginmap, reachability); this operator takes torch.float32.");
   bad_argument("Error: Unsupported data type. Only torch.float32 and torch.float64 are supported.");
 }
 
@@ -210,7 +211,7 @@ torch::Tensor make_workspace(size_t bytes, const torch::Tensor &like) {
 // ---- plain forest ------------------------------------------------------------------------
 
 ForestCall::ForestCall(int kind, const torch::Tensor &x, const torch::Tensor &thr, const torch::Tensor &ord,
-                       const torch::Tensor &w, const torch::Tensor *g) {
+                       const torch::Tensor &w, const torch::Tensor *g, bool allow_double) {
   // same order of checks as the reference dispatcher and GPU host function
   // (hingetree.cpp:648-664, hingetree_gpu.cu:420-447)
   if (x.dtype() != thr.dtype() || torch::kInt64 != ord.scalar_type() || x.dtype() != w.dtype() ||
@@ -226,7 +227,8 @@ ForestCall::ForestCall(int kind, const torch::Tensor &x, const torch::Tensor &th
   if (!x.is_contiguous() || !thr.is_contiguous() || !ord.is_contiguous() || !w.is_contiguous() ||
       (g != nullptr && !g->is_contiguous()))
     bad_argument("Error: All tensors are expected to be contiguous.");
-  require_float32(x);
+  is_double = allow_double && x.scalar_type() == torch::kFloat64;
+  if (!is_double) require_float32(x);
   require_cuda(x);
   if (x.dim() < 2 || thr.dim() != 2 || ord.dim() != 2 || w.dim() < 2)
     bad_argument("Error: inData, inWeights must have at least 2 dimensions. inThresholds and inOrdinals must have 2 "
@@ -266,11 +268,19 @@ ForestCall::ForestCall(int kind, const torch::Tensor &x, const torch::Tensor &th
 namespace {
 
 torch::Tensor forest_forward(int kind, torch::Tensor x, torch::Tensor thr, torch::Tensor ord, torch::Tensor w) {
-  ForestCall call(kind, x, thr, ord, w, nullptr);
+  ForestCall call(kind, x, thr, ord, w, nullptr, true);
   c10::DeviceGuard guard(x.device());
   torch::Tensor out = torch::empty(call.out_sizes, x.options());
   torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
   OrdinalGuard og(ord, call.problem.C);
+  if (call.is_double) {
+    raise_status(ht_forest_forward_f64(&call.problem, x.data_ptr<double>(), thr.data_ptr<double>(), ord.data_ptr<int64_t>(),
+                                       w.data_ptr<double>(), out.data_ptr<double>(), ws.data_ptr(), ws.numel(), og.word(),
+                                       current_stream(x)),
+                 "forest forward");
+    og.finish();
+    return out;
+  }
   raise_status(ht_forest_forward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
                                      w.data_ptr<float>(), out.data_ptr<float>(), ws.data_ptr(), ws.numel(), og.word(),
                                      current_stream(x)),
@@ -283,17 +293,30 @@ std::vector<torch::Tensor> forest_backward(int kind, bool deterministic, torch::
                                            bool need_thr, torch::Tensor ord, bool need_ord, torch::Tensor w, bool need_w,
                                            torch::Tensor g) {
   if (need_ord) bad_runtime("Error: Gradient on inOrdinals is requested, but inOrdinals never has a gradient.");
-  ForestCall call(kind, x, thr, ord, w, &g);
+  ForestCall call(kind, x, thr, ord, w, &g, true);
   c10::DeviceGuard guard(x.device());
   std::vector<torch::Tensor> grads(4);
   if (!need_x && !need_thr && !need_w) return grads;
   if (deterministic) call.problem.flags |= HT_DETERMINISTIC;
-  call.problem.flags |= HT_WORKSPACE_FOR_BACKWARD;
-  if ((int64_t)ht_forest_workspace_bytes(&call.problem) > g_backward_scratch_limit && !deterministic)
-    call.problem.flags &= ~HT_WORKSPACE_FOR_BACKWARD;
   if (need_x) grads[0] = torch::empty_like(x);
   if (need_thr) grads[1] = torch::empty_like(thr);
   if (need_w) grads[3] = torch::empty_like(w);
+  if (call.is_double) {
+    torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
+    OrdinalGuard og(ord, call.problem.C);
+    raise_status(
+        ht_forest_backward_f64(&call.problem, x.data_ptr<double>(), thr.data_ptr<double>(), ord.data_ptr<int64_t>(),
+                               w.data_ptr<double>(), g.data_ptr<double>(), need_x ? grads[0].data_ptr<double>() : nullptr,
+                               need_thr ? grads[1].data_ptr<double>() : nullptr,
+                               need_w ? grads[3].data_ptr<double>() : nullptr, ws.data_ptr(), ws.numel(), og.word(),
+                               current_stream(x)),
+        "forest backward");
+    og.finish();
+    return grads;
+  }
+  call.problem.flags |= HT_WORKSPACE_FOR_BACKWARD;
+  if ((int64_t)ht_forest_workspace_bytes(&call.problem) > g_backward_scratch_limit && !deterministic)
+    call.problem.flags &= ~HT_WORKSPACE_FOR_BACKWARD;
   torch::Tensor ws;
   try {
     ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
@@ -324,6 +347,8 @@ static bool g_save_forward = true;
 
 std::vector<torch::Tensor> forest_forward_saving(int kind, torch::Tensor x, torch::Tensor thr, torch::Tensor ord,
                                                  torch::Tensor w) {
+  if (x.scalar_type() == torch::kFloat64)  // no kept traversal in double precision: the plain forward
+    return {forest_forward(kind, x, thr, ord, w), torch::empty({0}, x.options().dtype(torch::kUInt8))};
   ForestCall call(kind, x, thr, ord, w, nullptr);
   c10::DeviceGuard guard(x.device());
   const bool saves = g_save_forward && ht_forest_forward_saves(&call.problem) != 0;
@@ -401,11 +426,18 @@ std::vector<torch::Tensor> linear_tf32_stats(torch::Tensor x, torch::Tensor w) {
 }
 
 torch::Tensor forest_leafmap(int kind, torch::Tensor x, torch::Tensor thr, torch::Tensor ord, torch::Tensor w) {
-  ForestCall call(kind, x, thr, ord, w, nullptr);
+  ForestCall call(kind, x, thr, ord, w, nullptr, true);
   c10::DeviceGuard guard(x.device());
   torch::Tensor leaf = torch::empty(call.map_sizes, x.options().dtype(torch::kInt64));
   torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
   OrdinalGuard og(ord, call.problem.C);
+  if (call.is_double) {
+    raise_status(ht_forest_leafmap_f64(&call.problem, x.data_ptr<double>(), thr.data_ptr<double>(), ord.data_ptr<int64_t>(),
+                                       leaf.data_ptr<int64_t>(), ws.data_ptr(), ws.numel(), og.word(), current_stream(x)),
+                 "forest leafmap");
+    og.finish();
+    return leaf;
+  }
   raise_status(ht_forest_leafmap_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
                                      leaf.data_ptr<int64_t>(), ws.data_ptr(), ws.numel(), og.word(), current_stream(x)),
                "forest leafmap");
@@ -415,12 +447,21 @@ torch::Tensor forest_leafmap(int kind, torch::Tensor x, torch::Tensor thr, torch
 
 std::vector<torch::Tensor> forest_marginmap(int kind, torch::Tensor x, torch::Tensor thr, torch::Tensor ord,
                                             torch::Tensor w) {
-  ForestCall call(kind, x, thr, ord, w, nullptr);
+  ForestCall call(kind, x, thr, ord, w, nullptr, true);
   c10::DeviceGuard guard(x.device());
   torch::Tensor margins = torch::empty(call.map_sizes, x.options());
   torch::Tensor ords = torch::empty(call.map_sizes, x.options().dtype(torch::kInt64));
   torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
   OrdinalGuard og(ord, call.problem.C);
+  if (call.is_double) {
+    raise_status(
+        ht_forest_marginmap_f64(&call.problem, x.data_ptr<double>(), thr.data_ptr<double>(), ord.data_ptr<int64_t>(),
+                                margins.data_ptr<double>(), ords.data_ptr<int64_t>(), ws.data_ptr(), ws.numel(), og.word(),
+                                current_stream(x)),
+        "forest marginmap");
+    og.finish();
+    return {margins, ords};
+  }
   raise_status(
       ht_forest_marginmap_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
                               margins.data_ptr<float>(), ords.data_ptr<int64_t>(), ws.data_ptr(), ws.numel(), og.word(),
@@ -431,11 +472,19 @@ std::vector<torch::Tensor> forest_marginmap(int kind, torch::Tensor x, torch::Te
 }
 
 torch::Tensor forest_reachability(int kind, torch::Tensor x, torch::Tensor thr, torch::Tensor ord, torch::Tensor w) {
-  ForestCall call(kind, x, thr, ord, w, nullptr);
+  ForestCall call(kind, x, thr, ord, w, nullptr, true);
   c10::DeviceGuard guard(x.device());
   torch::Tensor counts = torch::empty({w.size(0), w.size(1)}, x.options().dtype(torch::kInt64));
   torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
   OrdinalGuard og(ord, call.problem.C);
+  if (call.is_double) {
+    raise_status(ht_forest_reachability_f64(&call.problem, x.data_ptr<double>(), thr.data_ptr<double>(),
+                                            ord.data_ptr<int64_t>(), counts.data_ptr<int64_t>(), ws.data_ptr(), ws.numel(),
+                                            og.word(), current_stream(x)),
+                 "forest reachability");
+    og.finish();
+    return counts;
+  }
   raise_status(ht_forest_reachability_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(),
                                           ord.data_ptr<int64_t>(), counts.data_ptr<int64_t>(), ws.data_ptr(),
                                           ws.numel(), og.word(), current_stream(x)),

@@ -41,9 +41,11 @@ class OrdinalGuard {
 
 // Argument checks and shape bookkeeping of the plain forest operators.
 struct ForestCall {
+  // allow_double: torch.float64 tensors are taken too (the plain operators have double precision kernels)
   ForestCall(int kind, const torch::Tensor &x, const torch::Tensor &thr, const torch::Tensor &ord,
-             const torch::Tensor &w, const torch::Tensor *g);
+             const torch::Tensor &w, const torch::Tensor *g, bool allow_double = false);
   ht_forest_problem problem;
+  bool is_double = false;
   std::vector<int64_t> out_sizes;  // [B, T, inner data dims..., inner weight dims...]
   std::vector<int64_t> map_sizes;  // [B, T, inner data dims...]
 };

@@ -44,22 +44,36 @@ __host__ __device__ inline int64_t threshold_count(int kind, int depth) {
 
 // Result of one traversal: leaf key (bit l = decision at depth l, LSB = root), signed margin
 // of the decision with the smallest |margin| (first one wins ties) and its vertex index.
-struct Path {
+template <typename Real>
+struct PathOf {
   uint32_t key;
-  float margin;
+  Real margin;
   uint32_t vertex;
 };
+using Path = PathOf<float>;
+
+// Rounded-once arithmetic (no contraction into fused multiply-adds) and |.| for both real types.
+__device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
+__device__ __forceinline__ float abs_of(float a) { return fabsf(a); }
+__device__ __forceinline__ double abs_of(double a) { return fabs(a); }
 
 // Feature of one (sample, position): x[i, c, k] with the (i, k) part folded into `base`.
-struct PlainFeature {
-  const float *__restrict__ base;
+template <typename Real>
+struct PlainFeatureOf {
+  typedef Real value_type;
+  const Real *__restrict__ base;
   int64_t stride;  // K
-  __device__ __forceinline__ float operator()(int c) const { return __ldg(base + (int64_t)c * stride); }
+  __device__ __forceinline__ Real operator()(int c) const { return __ldg(base + (int64_t)c * stride); }
 };
+using PlainFeature = PlainFeatureOf<float>;
 
 // Image + per-sample vector lookup: features below the image channel count come from the
 // image, the rest from the vector (reference semantics: HingeTreeCommon.cuh:81-107, 156-184).
 struct FusionFeature {
+  typedef float value_type;
   const float *__restrict__ img;
   int64_t stride;
   const float *__restrict__ vec;
@@ -73,18 +87,20 @@ struct FusionFeature {
 // strict `<` keeps the shallowest minimum.  Level 0 seeds the minimum, which is what the
 // reference's initialisation from vertex 0 amounts to (also for NaN margins).
 template <int KIND, typename OrdT, typename Feature>
-__device__ __forceinline__ Path traverse(const Feature &feat, const float *__restrict__ thr,
-                                         const OrdT *__restrict__ ord, int depth) {
-  Path p;
+__device__ __forceinline__ PathOf<typename Feature::value_type> traverse(const Feature &feat,
+                                                                        const typename Feature::value_type *__restrict__ thr,
+                                                                        const OrdT *__restrict__ ord, int depth) {
+  typedef typename Feature::value_type Real;
+  PathOf<Real> p;
   p.key = 0;
   p.vertex = 0;
-  p.margin = 0.0f;
+  p.margin = (Real)0;
   uint32_t v = 0;
   for (int l = 0; l < depth; ++l) {
     const uint32_t at = (KIND == FERN) ? (uint32_t)l : v;
-    const float m = feat((int)ord[at]) - thr[at];
-    const uint32_t bit = (m > 0.0f) ? 1u : 0u;
-    if (l == 0 || fabsf(m) < fabsf(p.margin)) {
+    const Real m = feat((int)ord[at]) - thr[at];
+    const uint32_t bit = (m > (Real)0) ? 1u : 0u;
+    if (l == 0 || abs_of(m) < abs_of(p.margin)) {
       p.margin = m;
       p.vertex = at;
     }
@@ -95,6 +111,7 @@ __device__ __forceinline__ Path traverse(const Feature &feat, const float *__res
 }
 
 __device__ __forceinline__ float sign_of(float m) { return (float)((0.0f < m) - (m < 0.0f)); }
+__device__ __forceinline__ double sign_of(double m) { return (double)((0.0 < m) - (m < 0.0)); }
 
 // Common argument screening for the forest entry points.
 inline int check_forest_problem(const ht_forest_problem *p) {

@@ -75,6 +75,7 @@ __device__ __forceinline__ int cell_index(const ConvArgs &a, const int (&origin)
 }
 
 struct WindowFeature {
+  typedef float value_type;
   const ConvArgs &a;
   const float *chan;
   const int (&origin)[3];

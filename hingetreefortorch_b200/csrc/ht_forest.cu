@@ -32,16 +32,19 @@ __global__ void pack_ordinals_kernel(const int64_t *__restrict__ ord, int64_t n,
   packed[e] = (int32_t)o;
 }
 
-struct ForestArgs {
-  const float *x;
-  const float *thr;
+template <typename Real>
+struct ForestArgsOf {
+  const Real *x;
+  const Real *thr;
   const int32_t *ord;
-  const float *w;
+  const Real *w;
   int64_t B, C, K, T, N, L, M;
   int depth;
 };
+using ForestArgs = ForestArgsOf<float>;
 
-__device__ __forceinline__ void split_index(const ForestArgs &a, int64_t e, int64_t &i, int64_t &j, int64_t &k) {
+template <typename Real>
+__device__ __forceinline__ void split_index(const ForestArgsOf<Real> &a, int64_t e, int64_t &i, int64_t &j, int64_t &k) {
   if (a.K == 1) {
     k = 0;
     i = e / a.T;
@@ -56,19 +59,19 @@ __device__ __forceinline__ void split_index(const ForestArgs &a, int64_t e, int6
 
 enum { MODE_FORWARD = 0, MODE_LEAFMAP = 1, MODE_MARGINMAP = 2, MODE_REACH = 3 };
 
-template <int KIND, int MODE>
-__global__ void __launch_bounds__(kBlock) forest_any_kernel(ForestArgs a, float *__restrict__ out_f,
+template <int KIND, int MODE, typename Real>
+__global__ void __launch_bounds__(kBlock) forest_any_kernel(ForestArgsOf<Real> a, Real *__restrict__ out_f,
                                                             int64_t *__restrict__ out_i) {
   const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= a.B * a.T * a.K) return;
   int64_t i, j, k;
   split_index(a, e, i, j, k);
-  const PlainFeature feat{a.x + i * a.C * a.K + k, a.K};
-  const Path p = traverse<KIND>(feat, a.thr + j * a.N, a.ord + j * a.N, a.depth);
+  const PlainFeatureOf<Real> feat{a.x + i * a.C * a.K + k, a.K};
+  const PathOf<Real> p = traverse<KIND>(feat, a.thr + j * a.N, a.ord + j * a.N, a.depth);
   if (MODE == MODE_FORWARD) {
-    const float am = fabsf(p.margin);
-    const float *wl = a.w + (j * a.L + p.key) * a.M;
-    float *o = out_f + e * a.M;
+    const Real am = abs_of(p.margin);
+    const Real *wl = a.w + (j * a.L + p.key) * a.M;
+    Real *o = out_f + e * a.M;
     for (int64_t m = 0; m < a.M; ++m) o[m] = am * __ldg(wl + m);
   } else if (MODE == MODE_LEAFMAP) {
     out_i[e] = (int64_t)p.key;
@@ -81,24 +84,24 @@ __global__ void __launch_bounds__(kBlock) forest_any_kernel(ForestArgs a, float 
 }
 
 // One thread per (i, j, k): the three gradient scatters after a single traversal.
-template <int KIND>
-__global__ void __launch_bounds__(kBlock) forest_backward_atomic_kernel(ForestArgs a, const float *__restrict__ g,
-                                                                        float *gx, float *gthr, float *gw) {
+template <int KIND, typename Real>
+__global__ void __launch_bounds__(kBlock) forest_backward_atomic_kernel(ForestArgsOf<Real> a, const Real *__restrict__ g,
+                                                                        Real *gx, Real *gthr, Real *gw) {
   const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= a.B * a.T * a.K) return;
   int64_t i, j, k;
   split_index(a, e, i, j, k);
-  const PlainFeature feat{a.x + i * a.C * a.K + k, a.K};
-  const Path p = traverse<KIND>(feat, a.thr + j * a.N, a.ord + j * a.N, a.depth);
-  const float s = sign_of(p.margin);
-  const float am = fabsf(p.margin);
-  const float *wl = a.w + (j * a.L + p.key) * a.M;
-  const float *gl = g + e * a.M;
-  float acc = 0.0f;
+  const PlainFeatureOf<Real> feat{a.x + i * a.C * a.K + k, a.K};
+  const PathOf<Real> p = traverse<KIND>(feat, a.thr + j * a.N, a.ord + j * a.N, a.depth);
+  const Real s = sign_of(p.margin);
+  const Real am = abs_of(p.margin);
+  const Real *wl = a.w + (j * a.L + p.key) * a.M;
+  const Real *gl = g + e * a.M;
+  Real acc = (Real)0;
   for (int64_t m = 0; m < a.M; ++m) {
-    const float gm = __ldg(gl + m);
-    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s, __ldg(wl + m)), gm));
-    if (gw != nullptr) atomicAdd(gw + (j * a.L + p.key) * a.M + m, __fmul_rn(am, gm));
+    const Real gm = __ldg(gl + m);
+    acc = add_rn(acc, mul_rn(mul_rn(s, __ldg(wl + m)), gm));
+    if (gw != nullptr) atomicAdd(gw + (j * a.L + p.key) * a.M + m, mul_rn(am, gm));
   }
   if (gx != nullptr) atomicAdd(gx + (i * a.C + a.ord[j * a.N + p.vertex]) * a.K + k, acc);
   if (gthr != nullptr) atomicAdd(gthr + j * a.N + p.vertex, -acc);
@@ -128,51 +131,51 @@ __device__ __forceinline__ void in_lane_order_per_key(bool valid, uint32_t key, 
 }
 
 // x gradient, one thread per (i, k) walking the trees in ascending order.
-template <int KIND>
-__global__ void __launch_bounds__(128) forest_backward_x_ordered_thread_kernel(ForestArgs a, const float *__restrict__ g,
-                                                                               float *gx) {
+template <int KIND, typename Real>
+__global__ void __launch_bounds__(128) forest_backward_x_ordered_thread_kernel(ForestArgsOf<Real> a,
+                                                                               const Real *__restrict__ g, Real *gx) {
   const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= a.B * a.K) return;
   const int64_t i = p / a.K, k = p - i * a.K;
-  const PlainFeature feat{a.x + i * a.C * a.K + k, a.K};
+  const PlainFeatureOf<Real> feat{a.x + i * a.C * a.K + k, a.K};
   for (int64_t j = 0; j < a.T; ++j) {
-    const Path path = traverse<KIND>(feat, a.thr + j * a.N, a.ord + j * a.N, a.depth);
-    const float s = sign_of(path.margin);
-    const float *wl = a.w + (j * a.L + path.key) * a.M;
-    const float *gl = g + ((i * a.T + j) * a.K + k) * a.M;
-    float *dst = gx + (i * a.C + a.ord[j * a.N + path.vertex]) * a.K + k;
-    float acc = *dst;
-    for (int64_t m = 0; m < a.M; ++m) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s, __ldg(wl + m)), __ldg(gl + m)));
+    const PathOf<Real> path = traverse<KIND>(feat, a.thr + j * a.N, a.ord + j * a.N, a.depth);
+    const Real s = sign_of(path.margin);
+    const Real *wl = a.w + (j * a.L + path.key) * a.M;
+    const Real *gl = g + ((i * a.T + j) * a.K + k) * a.M;
+    Real *dst = gx + (i * a.C + a.ord[j * a.N + path.vertex]) * a.K + k;
+    Real acc = *dst;
+    for (int64_t m = 0; m < a.M; ++m) acc = add_rn(acc, mul_rn(mul_rn(s, __ldg(wl + m)), __ldg(gl + m)));
     *dst = acc;
   }
 }
 
 // x gradient, one warp per (i, k): lanes take 32 consecutive trees, traverse concurrently and
 // then add into the row in tree order wherever two of them hit the same feature.
-template <int KIND>
-__global__ void __launch_bounds__(128) forest_backward_x_ordered_warp_kernel(ForestArgs a, const float *__restrict__ g,
-                                                                             float *gx) {
+template <int KIND, typename Real>
+__global__ void __launch_bounds__(128) forest_backward_x_ordered_warp_kernel(ForestArgsOf<Real> a,
+                                                                             const Real *__restrict__ g, Real *gx) {
   const int64_t p = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (p >= a.B * a.K) return;  // whole warps leave together
   const unsigned lane = threadIdx.x & 31u;
   const int64_t i = p / a.K, k = p - i * a.K;
-  const PlainFeature feat{a.x + i * a.C * a.K + k, a.K};
+  const PlainFeatureOf<Real> feat{a.x + i * a.C * a.K + k, a.K};
   for (int64_t j0 = 0; j0 < a.T; j0 += 32) {
     const int64_t j = j0 + lane;
     const bool valid = j < a.T;
-    Path path{0u, 0.0f, 0u};
+    PathOf<Real> path{0u, (Real)0, 0u};
     int c = 0;
     if (valid) {
       path = traverse<KIND>(feat, a.thr + j * a.N, a.ord + j * a.N, a.depth);
       c = a.ord[j * a.N + path.vertex];
     }
     in_lane_order_per_key(valid, (uint32_t)c, [&]() {
-      const float s = sign_of(path.margin);
-      const float *wl = a.w + (j * a.L + path.key) * a.M;
-      const float *gl = g + ((i * a.T + j) * a.K + k) * a.M;
-      float *dst = gx + (i * a.C + c) * a.K + k;
-      float acc = __ldcg(dst);
-      for (int64_t m = 0; m < a.M; ++m) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s, __ldg(wl + m)), __ldg(gl + m)));
+      const Real s = sign_of(path.margin);
+      const Real *wl = a.w + (j * a.L + path.key) * a.M;
+      const Real *gl = g + ((i * a.T + j) * a.K + k) * a.M;
+      Real *dst = gx + (i * a.C + c) * a.K + k;
+      Real acc = __ldcg(dst);
+      for (int64_t m = 0; m < a.M; ++m) acc = add_rn(acc, mul_rn(mul_rn(s, __ldg(wl + m)), __ldg(gl + m)));
       __stcg(dst, acc);
     });
   }
@@ -182,53 +185,54 @@ __global__ void __launch_bounds__(128) forest_backward_x_ordered_warp_kernel(For
 // positions, traverse concurrently, then add into the tree's bins in position order wherever
 // two of them hit the same bin.  Bins live in shared memory when they fit, else in the
 // (already cleared) global outputs, which no other warp touches.
-template <int KIND>
-__global__ void __launch_bounds__(32) forest_backward_params_ordered_kernel(ForestArgs a, const float *__restrict__ g,
-                                                                            float *gthr, float *gw, int thr_in_smem,
+template <int KIND, typename Real>
+__global__ void __launch_bounds__(32) forest_backward_params_ordered_kernel(ForestArgsOf<Real> a, const Real *__restrict__ g,
+                                                                            Real *gthr, Real *gw, int thr_in_smem,
                                                                             int w_in_smem) {
-  extern __shared__ float bins[];
+  extern __shared__ __align__(16) unsigned char bins_raw[];
+  Real *bins = reinterpret_cast<Real *>(bins_raw);
   const int64_t j = blockIdx.x;
   const unsigned lane = threadIdx.x;
   const int64_t LM = a.L * a.M;
-  float *thr_bins = nullptr, *w_bins = nullptr;
+  Real *thr_bins = nullptr, *w_bins = nullptr;
   if (gthr != nullptr) thr_bins = thr_in_smem ? bins : gthr + j * a.N;
   if (gw != nullptr) w_bins = w_in_smem ? bins + (thr_in_smem ? a.N : 0) : gw + j * LM;
   if (thr_bins != nullptr && thr_in_smem)
-    for (int64_t t = lane; t < a.N; t += 32) thr_bins[t] = 0.0f;
+    for (int64_t t = lane; t < a.N; t += 32) thr_bins[t] = (Real)0;
   if (w_bins != nullptr && w_in_smem)
-    for (int64_t t = lane; t < LM; t += 32) w_bins[t] = 0.0f;
+    for (int64_t t = lane; t < LM; t += 32) w_bins[t] = (Real)0;
   __syncwarp();
 
-  const float *thr = a.thr + j * a.N;
+  const Real *thr = a.thr + j * a.N;
   const int32_t *ord = a.ord + j * a.N;
   const int64_t P = a.B * a.K;
   for (int64_t p0 = 0; p0 < P; p0 += 32) {
     const int64_t p = p0 + lane;
     const bool valid = p < P;
-    Path path{0u, 0.0f, 0u};
+    PathOf<Real> path{0u, (Real)0, 0u};
     int64_t i = 0, k = 0;
     if (valid) {
       i = p / a.K;
       k = p - i * a.K;
-      const PlainFeature feat{a.x + i * a.C * a.K + k, a.K};
+      const PlainFeatureOf<Real> feat{a.x + i * a.C * a.K + k, a.K};
       path = traverse<KIND>(feat, thr, ord, a.depth);
     }
-    const float *gl = g + ((i * a.T + j) * a.K + k) * a.M;
-    const float *wl = a.w + (j * a.L + path.key) * a.M;
+    const Real *gl = g + ((i * a.T + j) * a.K + k) * a.M;
+    const Real *wl = a.w + (j * a.L + path.key) * a.M;
     if (thr_bins != nullptr) {
       in_lane_order_per_key(valid, path.vertex, [&]() {
-        const float ns = -sign_of(path.margin);
-        volatile float *dst = thr_bins + path.vertex;
-        float acc = *dst;
-        for (int64_t m = 0; m < a.M; ++m) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(ns, __ldg(wl + m)), __ldg(gl + m)));
+        const Real ns = -sign_of(path.margin);
+        volatile Real *dst = thr_bins + path.vertex;
+        Real acc = *dst;
+        for (int64_t m = 0; m < a.M; ++m) acc = add_rn(acc, mul_rn(mul_rn(ns, __ldg(wl + m)), __ldg(gl + m)));
         *dst = acc;
       });
     }
     if (w_bins != nullptr) {
       in_lane_order_per_key(valid, path.key, [&]() {
-        const float am = fabsf(path.margin);
-        volatile float *dst = w_bins + (int64_t)path.key * a.M;
-        for (int64_t m = 0; m < a.M; ++m) dst[m] = __fadd_rn(dst[m], __fmul_rn(am, __ldg(gl + m)));
+        const Real am = abs_of(path.margin);
+        volatile Real *dst = w_bins + (int64_t)path.key * a.M;
+        for (int64_t m = 0; m < a.M; ++m) dst[m] = add_rn(dst[m], mul_rn(am, __ldg(gl + m)));
       });
     }
   }
@@ -246,16 +250,19 @@ inline size_t ordinals_bytes(const ht_forest_problem *p) {
 
 inline unsigned blocks_for(int64_t n, int block) { return (unsigned)((n + block - 1) / block); }
 
-struct Prepared {
-  ForestArgs args;
+template <typename Real>
+struct PreparedOf {
+  ForestArgsOf<Real> args;
   cudaStream_t stream;
   int64_t evals;
 };
+using Prepared = PreparedOf<float>;
 
 // Validates the call, converts the ordinals into the workspace and fills the kernel arguments.
-int prepare(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
+template <typename Real>
+int prepare(const ht_forest_problem *p, const Real *x, const Real *thr, const int64_t *ord, const Real *w,
             bool need_w, void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream,
-            Prepared &out) {
+            PreparedOf<Real> &out) {
   const int rc = check_forest_problem(p);
   if (rc != HT_OK) return rc;
   // a null pointer is only acceptable for a tensor without elements
@@ -263,10 +270,11 @@ int prepare(const ht_forest_problem *p, const float *x, const float *thr, const 
   if ((x == nullptr && p->B * p->C * p->K > 0) || ((thr == nullptr || ord == nullptr) && decisions > 0) ||
       (need_w && w == nullptr && p->T * p->M > 0))
     return HT_ERR_INVALID_ARGUMENT;
-  const size_t need = ht_forest_workspace_bytes(p);
+  // the double precision entry points run the any-shape kernels only: compact ordinals are all they keep
+  const size_t need = sizeof(Real) == 4 ? ht_forest_workspace_bytes(p) : ordinals_bytes(p) + 256;
   if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
     return HT_ERR_WORKSPACE;
-  ForestArgs &a = out.args;
+  ForestArgsOf<Real> &a = out.args;
   a.x = x;
   a.thr = thr;
   a.ord = static_cast<const int32_t *>(workspace);
@@ -288,15 +296,77 @@ int prepare(const ht_forest_problem *p, const float *x, const float *thr, const 
   return HT_OK;
 }
 
-template <int MODE>
-int launch_any(const ht_forest_problem *p, const Prepared &pr, float *out_f, int64_t *out_i) {
+template <int MODE, typename Real>
+int launch_any(const ht_forest_problem *p, const PreparedOf<Real> &pr, Real *out_f, int64_t *out_i) {
   if (pr.evals == 0) return HT_OK;
   const unsigned grid = blocks_for(pr.evals, kBlock);
   if (p->kind == TREE)
-    forest_any_kernel<TREE, MODE><<<grid, kBlock, 0, pr.stream>>>(pr.args, out_f, out_i);
+    forest_any_kernel<TREE, MODE, Real><<<grid, kBlock, 0, pr.stream>>>(pr.args, out_f, out_i);
   else
-    forest_any_kernel<FERN, MODE><<<grid, kBlock, 0, pr.stream>>>(pr.args, out_f, out_i);
+    forest_any_kernel<FERN, MODE, Real><<<grid, kBlock, 0, pr.stream>>>(pr.args, out_f, out_i);
   HT_CHECK_LAUNCH();
+  return HT_OK;
+}
+
+// Clears the requested gradients (the entry points' contract).
+template <typename Real>
+int clear_gradients(const PreparedOf<Real> &pr, Real *gx, Real *gthr, Real *gw) {
+  const ForestArgsOf<Real> &a = pr.args;
+  if (gx != nullptr && a.B * a.C * a.K > 0)
+    HT_CUDA_TRY(cudaMemsetAsync(gx, 0, sizeof(Real) * (size_t)(a.B * a.C * a.K), pr.stream));
+  if (gthr != nullptr && a.T * a.N > 0)
+    HT_CUDA_TRY(cudaMemsetAsync(gthr, 0, sizeof(Real) * (size_t)(a.T * a.N), pr.stream));
+  if (gw != nullptr && a.T * a.L * a.M > 0)
+    HT_CUDA_TRY(cudaMemsetAsync(gw, 0, sizeof(Real) * (size_t)(a.T * a.L * a.M), pr.stream));
+  return HT_OK;
+}
+
+// The backward with the any-shape kernels: one traversal and atomic scatters in default mode; in fixed-order
+// mode the x gradient by a thread (or a warp) per (sample, position) in tree order and the parameter gradients
+// by a warp per tree in sample order.
+template <typename Real>
+int backward_any(const ht_forest_problem *p, const PreparedOf<Real> &pr, const Real *g, Real *gx, Real *gthr, Real *gw) {
+  const ForestArgsOf<Real> &a = pr.args;
+  if ((p->flags & HT_DETERMINISTIC) == 0) {
+    const unsigned grid = blocks_for(pr.evals, kBlock);
+    if (p->kind == TREE)
+      forest_backward_atomic_kernel<TREE, Real><<<grid, kBlock, 0, pr.stream>>>(a, g, gx, gthr, gw);
+    else
+      forest_backward_atomic_kernel<FERN, Real><<<grid, kBlock, 0, pr.stream>>>(a, g, gx, gthr, gw);
+    HT_CHECK_LAUNCH();
+    return HT_OK;
+  }
+  const int64_t P = a.B * a.K;
+  if (gx != nullptr) {
+    if (P >= 32768) {
+      const unsigned grid = blocks_for(P, 128);
+      if (p->kind == TREE)
+        forest_backward_x_ordered_thread_kernel<TREE, Real><<<grid, 128, 0, pr.stream>>>(a, g, gx);
+      else
+        forest_backward_x_ordered_thread_kernel<FERN, Real><<<grid, 128, 0, pr.stream>>>(a, g, gx);
+    } else {
+      const unsigned grid = blocks_for(P * 32, 128);
+      if (p->kind == TREE)
+        forest_backward_x_ordered_warp_kernel<TREE, Real><<<grid, 128, 0, pr.stream>>>(a, g, gx);
+      else
+        forest_backward_x_ordered_warp_kernel<FERN, Real><<<grid, 128, 0, pr.stream>>>(a, g, gx);
+    }
+    HT_CHECK_LAUNCH();
+  }
+  if (gthr != nullptr || gw != nullptr) {
+    const size_t thr_bytes = gthr != nullptr ? sizeof(Real) * (size_t)a.N : 0;
+    const size_t w_bytes = gw != nullptr ? sizeof(Real) * (size_t)(a.L * a.M) : 0;
+    const size_t limit = 96 * 1024;
+    const int thr_in_smem = thr_bytes > 0 && thr_bytes <= 32 * 1024;
+    const int w_in_smem = w_bytes > 0 && w_bytes + (thr_in_smem ? thr_bytes : 0) <= limit;
+    const size_t smem = (thr_in_smem ? thr_bytes : 0) + (w_in_smem ? w_bytes : 0);
+    auto kernel = p->kind == TREE ? forest_backward_params_ordered_kernel<TREE, Real>
+                                  : forest_backward_params_ordered_kernel<FERN, Real>;
+    if (smem > 48 * 1024)
+      HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit));
+    kernel<<<(unsigned)a.T, 32, smem, pr.stream>>>(a, g, gthr, gw, thr_in_smem, w_in_smem);
+    HT_CHECK_LAUNCH();
+  }
   return HT_OK;
 }
 
@@ -368,17 +438,17 @@ int ht_forest_leafmap_f32(const ht_forest_problem *p, const float *x, const floa
                           int64_t *leaf, void *workspace, size_t workspace_bytes, uint32_t *status_word,
                           ht_stream_t stream) {
   Prepared pr;
-  const int rc = prepare(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
+  const int rc = prepare<float>(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
   if (rc != HT_OK) return rc;
   if (leaf == nullptr && pr.evals > 0) return HT_ERR_INVALID_ARGUMENT;
-  return launch_any<MODE_LEAFMAP>(p, pr, nullptr, leaf);
+  return launch_any<MODE_LEAFMAP, float>(p, pr, nullptr, leaf);
 }
 
 int ht_forest_marginmap_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
                             float *margin, int64_t *margin_ord, void *workspace, size_t workspace_bytes,
                             uint32_t *status_word, ht_stream_t stream) {
   Prepared pr;
-  const int rc = prepare(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
+  const int rc = prepare<float>(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
   if (rc != HT_OK) return rc;
   if ((margin == nullptr || margin_ord == nullptr) && pr.evals > 0) return HT_ERR_INVALID_ARGUMENT;
   return launch_any<MODE_MARGINMAP>(p, pr, margin, margin_ord);
@@ -388,12 +458,12 @@ int ht_forest_reachability_f32(const ht_forest_problem *p, const float *x, const
                                int64_t *counts, void *workspace, size_t workspace_bytes, uint32_t *status_word,
                                ht_stream_t stream) {
   Prepared pr;
-  const int rc = prepare(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
+  const int rc = prepare<float>(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
   if (rc != HT_OK) return rc;
   if (counts == nullptr && pr.args.T > 0) return HT_ERR_INVALID_ARGUMENT;
   if (pr.args.T * pr.args.L > 0)
     HT_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int64_t) * (size_t)(pr.args.T * pr.args.L), pr.stream));
-  return launch_any<MODE_REACH>(p, pr, nullptr, counts);
+  return launch_any<MODE_REACH, float>(p, pr, nullptr, counts);
 }
 
 int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const float *thr, const int64_t *ord,
@@ -404,12 +474,8 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
   if (rc != HT_OK) return rc;
   if (g == nullptr && pr.evals * p->M > 0) return HT_ERR_INVALID_ARGUMENT;
   const ForestArgs &a = pr.args;
-  if (gx != nullptr && a.B * a.C * a.K > 0)
-    HT_CUDA_TRY(cudaMemsetAsync(gx, 0, sizeof(float) * (size_t)(a.B * a.C * a.K), pr.stream));
-  if (gthr != nullptr && a.T * a.N > 0)
-    HT_CUDA_TRY(cudaMemsetAsync(gthr, 0, sizeof(float) * (size_t)(a.T * a.N), pr.stream));
-  if (gw != nullptr && a.T * a.L * a.M > 0)
-    HT_CUDA_TRY(cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)(a.T * a.L * a.M), pr.stream));
+  const int crc = clear_gradients(pr, gx, gthr, gw);
+  if (crc != HT_OK) return crc;
   if (pr.evals * a.M == 0 || (gx == nullptr && gthr == nullptr && gw == nullptr)) return HT_OK;
 
   {
@@ -431,48 +497,64 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
                                          forward_tiled_workspace_bytes(p), status_word, pr.stream);
     if (mrc != HT_ERR_UNSUPPORTED) return mrc;
   }
-  if ((p->flags & HT_DETERMINISTIC) == 0) {
-    const unsigned grid = blocks_for(pr.evals, kBlock);
-    if (p->kind == TREE)
-      forest_backward_atomic_kernel<TREE><<<grid, kBlock, 0, pr.stream>>>(a, g, gx, gthr, gw);
-    else
-      forest_backward_atomic_kernel<FERN><<<grid, kBlock, 0, pr.stream>>>(a, g, gx, gthr, gw);
-    HT_CHECK_LAUNCH();
-    return HT_OK;
-  }
+  return backward_any(p, pr, g, gx, gthr, gw);
+}
 
-  const int64_t P = a.B * a.K;
-  if (gx != nullptr) {
-    if (P >= 32768) {
-      const unsigned grid = blocks_for(P, 128);
-      if (p->kind == TREE)
-        forest_backward_x_ordered_thread_kernel<TREE><<<grid, 128, 0, pr.stream>>>(a, g, gx);
-      else
-        forest_backward_x_ordered_thread_kernel<FERN><<<grid, 128, 0, pr.stream>>>(a, g, gx);
-    } else {
-      const unsigned grid = blocks_for(P * 32, 128);
-      if (p->kind == TREE)
-        forest_backward_x_ordered_warp_kernel<TREE><<<grid, 128, 0, pr.stream>>>(a, g, gx);
-      else
-        forest_backward_x_ordered_warp_kernel<FERN><<<grid, 128, 0, pr.stream>>>(a, g, gx);
-    }
-    HT_CHECK_LAUNCH();
-  }
-  if (gthr != nullptr || gw != nullptr) {
-    const size_t thr_bytes = gthr != nullptr ? sizeof(float) * (size_t)a.N : 0;
-    const size_t w_bytes = gw != nullptr ? sizeof(float) * (size_t)(a.L * a.M) : 0;
-    const size_t limit = 96 * 1024;
-    const int thr_in_smem = thr_bytes > 0 && thr_bytes <= 32 * 1024;
-    const int w_in_smem = w_bytes > 0 && w_bytes + (thr_in_smem ? thr_bytes : 0) <= limit;
-    const size_t smem = (thr_in_smem ? thr_bytes : 0) + (w_in_smem ? w_bytes : 0);
-    auto kernel = p->kind == TREE ? forest_backward_params_ordered_kernel<TREE>
-                                  : forest_backward_params_ordered_kernel<FERN>;
-    if (smem > 48 * 1024)
-      HT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit));
-    kernel<<<(unsigned)a.T, 32, smem, pr.stream>>>(a, g, gthr, gw, thr_in_smem, w_in_smem);
-    HT_CHECK_LAUNCH();
-  }
-  return HT_OK;
+/* ---- double precision: the any-shape kernels instantiated for double ---------------------------------------- */
+
+int ht_forest_forward_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord,
+                          const double *w, double *out, void *workspace, size_t workspace_bytes, uint32_t *status_word,
+                          ht_stream_t stream) {
+  PreparedOf<double> pr;
+  const int rc = prepare(p, x, thr, ord, w, true, workspace, workspace_bytes, status_word, stream, pr);
+  if (rc != HT_OK) return rc;
+  if (pr.evals * p->M == 0) return HT_OK;
+  if (out == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  return launch_any<MODE_FORWARD>(p, pr, out, nullptr);
+}
+
+int ht_forest_leafmap_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord, int64_t *leaf,
+                          void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream) {
+  PreparedOf<double> pr;
+  const int rc = prepare<double>(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
+  if (rc != HT_OK) return rc;
+  if (leaf == nullptr && pr.evals > 0) return HT_ERR_INVALID_ARGUMENT;
+  return launch_any<MODE_LEAFMAP, double>(p, pr, nullptr, leaf);
+}
+
+int ht_forest_marginmap_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord,
+                            double *margin, int64_t *margin_ord, void *workspace, size_t workspace_bytes,
+                            uint32_t *status_word, ht_stream_t stream) {
+  PreparedOf<double> pr;
+  const int rc = prepare<double>(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
+  if (rc != HT_OK) return rc;
+  if ((margin == nullptr || margin_ord == nullptr) && pr.evals > 0) return HT_ERR_INVALID_ARGUMENT;
+  return launch_any<MODE_MARGINMAP>(p, pr, margin, margin_ord);
+}
+
+int ht_forest_reachability_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord,
+                               int64_t *counts, void *workspace, size_t workspace_bytes, uint32_t *status_word,
+                               ht_stream_t stream) {
+  PreparedOf<double> pr;
+  const int rc = prepare<double>(p, x, thr, ord, nullptr, false, workspace, workspace_bytes, status_word, stream, pr);
+  if (rc != HT_OK) return rc;
+  if (counts == nullptr && pr.args.T > 0) return HT_ERR_INVALID_ARGUMENT;
+  if (pr.args.T * pr.args.L > 0)
+    HT_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int64_t) * (size_t)(pr.args.T * pr.args.L), pr.stream));
+  return launch_any<MODE_REACH, double>(p, pr, nullptr, counts);
+}
+
+int ht_forest_backward_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord,
+                           const double *w, const double *g, double *gx, double *gthr, double *gw, void *workspace,
+                           size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream) {
+  PreparedOf<double> pr;
+  const int rc = prepare(p, x, thr, ord, w, true, workspace, workspace_bytes, status_word, stream, pr);
+  if (rc != HT_OK) return rc;
+  if (g == nullptr && pr.evals * p->M > 0) return HT_ERR_INVALID_ARGUMENT;
+  const int crc = clear_gradients(pr, gx, gthr, gw);
+  if (crc != HT_OK) return crc;
+  if (pr.evals * p->M == 0 || (gx == nullptr && gthr == nullptr && gw == nullptr)) return HT_OK;
+  return backward_any(p, pr, g, gx, gthr, gw);
 }
 
 }  // extern "C"

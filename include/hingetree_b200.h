@@ -154,6 +154,27 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
                            const float *w, const float *g, float *gx, float *gthr, float *gw,
                            void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
 
+/* ---- double precision ---------------------------------------------------------------------------
+ * The plain forest operators for fp64 tensors, as the reference instantiates them (dispatch hingetree.cpp:666-689,
+ * instantiations hingetree_gpu.cu:935-969): same contracts as their _f32 counterparts, every tensor double.  They
+ * run the any-shape kernels (a thread per (sample, tree, position)); the shared-memory tile kernels are fp32 only.
+ * Workspace: ht_forest_workspace_bytes(p) is enough (only the compact ordinals are kept there). */
+int ht_forest_forward_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord,
+                          const double *w, double *out, void *workspace, size_t workspace_bytes,
+                          uint32_t *status_word, ht_stream_t stream);
+int ht_forest_leafmap_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord,
+                          int64_t *leaf, void *workspace, size_t workspace_bytes, uint32_t *status_word,
+                          ht_stream_t stream);
+int ht_forest_marginmap_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord,
+                            double *margin, int64_t *margin_ord, void *workspace, size_t workspace_bytes,
+                            uint32_t *status_word, ht_stream_t stream);
+int ht_forest_reachability_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord,
+                               int64_t *counts, void *workspace, size_t workspace_bytes, uint32_t *status_word,
+                               ht_stream_t stream);
+int ht_forest_backward_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord,
+                           const double *w, const double *g, double *gx, double *gthr, double *gw,
+                           void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+
 /* ---- image + per-sample vector ("fusion") forests ------------------------------------------
  * Feature f of sample i at position k is img[i,f,k] for f < C (p->C = image channels) and
  * vec[i, f - C] otherwise, without materialising the concatenation; ordinals range over

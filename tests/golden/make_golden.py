@@ -101,6 +101,7 @@ def main():
     print("wrote forest.npz with", len(out), "arrays")
     families(ref)
     init_vectors(ref)
+    double_vectors(ref)
 
 
 LINEAR_CASES = [
@@ -120,6 +121,38 @@ CONV_CASES = [
 ]
 
 PATCH_CASES = [((2, 3, 7, 9), (2, 3), (1, 0)), ((1, 2, 8, 8), (4, 4), (2, 2)), ((1, 2, 5, 6, 7), (2, 3, 2), (1, 1, 0))]
+
+
+def double_vectors(ref):
+    """The forest cases once more in double precision -> forest64.npz (forward, maps, backward)."""
+    out = {}
+    for idx, (seed, kind, B, C, inner, T, depth, extra, adv) in enumerate(forest_cases()):
+        gen = torch.Generator().manual_seed(9000 + seed)
+        N = decisions(kind, depth)
+        x = torch.randn((B, C) + tuple(inner), generator=gen, dtype=torch.float64)
+        thr = torch.rand((T, N), generator=gen, dtype=torch.float64) * 6 - 3
+        ord_ = torch.randint(0, C, (T, N), generator=gen)
+        w = torch.randn((T, 2 ** depth) + tuple(extra), generator=gen, dtype=torch.float64)
+        if adv:
+            x = torch.round(x * 2) / 2
+            thr = torch.round(thr * 2) / 2
+            ord_[:, : min(N, 3)] = ord_[:, :1]
+        f = getattr(ref, kind + "_forward")(x, thr, ord_, w)
+        g = torch.randn(f.shape, generator=gen, dtype=torch.float64)
+        gx, gthr, _, gw = getattr(ref, kind + "_backward")(x, True, thr, True, ord_, False, w, True, g)
+        leaf = getattr(ref, kind + "_leafmap")(x, thr, ord_, w)
+        margin, mord = getattr(ref, kind + "_marginmap")(x, thr, ord_, w)
+        reach = getattr(ref, kind + "_reachability")(x, thr, ord_, w)
+        p = "forest%02d_" % idx
+        out[p + "kind"] = np.array(kind)
+        for name, t in [("x", x), ("thr", thr), ("ord", ord_), ("w", w), ("g", g), ("out", f), ("gx", gx),
+                        ("gthr", gthr), ("gw", gw), ("margin", margin), ("margin_ord", mord)]:
+            out[p + name] = t.numpy()
+        out[p + "leaf"] = leaf.numpy().astype(np.int64)
+        out[p + "reach"] = reach.numpy().astype(np.int64)
+    out["forest_count"] = np.array(len(forest_cases()))
+    np.savez_compressed(os.path.join(HERE, "forest64.npz"), **out)
+    print("wrote forest64.npz with", len(out), "arrays")
 
 
 def families(ref):
@@ -250,4 +283,7 @@ def init_vectors(ref):
 
 
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "double":  # only the double precision file
+        double_vectors(build_ref.load())
+    else:
+        main()

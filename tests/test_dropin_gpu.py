@@ -105,8 +105,10 @@ def test_error_contract_on_device(ext):
         ext.tree_forward(dx, dthr[:, :6].contiguous(), dord[:, :6].contiguous(), dw)
     with pytest.raises(ValueError, match="outDataGrad.shape"):
         ext.tree_backward(dx, True, dthr, True, dord, False, dw, True, torch.ones(8, 4, device="cuda"))
-    with pytest.raises(ValueError):
-        ext.tree_forward(dx.double(), dthr.double(), dord, dw.double())
+    with pytest.raises(ValueError):  # mixed real types
+        ext.tree_forward(dx.double(), dthr, dord, dw)
+    with pytest.raises(ValueError):  # half precision is taken by no operator
+        ext.tree_forward(dx.half(), dthr.half(), dord, dw.half())
     # a valid ordinals tensor that is later corrupted in place is re-validated (version changed)
     ext.tree_forward(dx, dthr, dord, dw)
     dord[1, 1] = -3
