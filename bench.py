@@ -678,6 +678,8 @@ def our_arm(a, wl):
         peak, peak_src = 6650.0, "fallback"
     timer = Timer(device, world)
     runner = make_runner(wl, B, device, rank, world)
+    if a.rewalk and wl["op"] == "forest":
+        runner.keep = False
 
     for _ in range(a.warmup):
         runner.step(wl["bwd"])
@@ -845,6 +847,8 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="rows per GPU instead of the workload's (profiler captures)")
     ap.add_argument("--linear", default="fp32", choices=["fp32", "tf32"],
                     help="c5 only: arithmetic of torch's Linear (cuBLAS); the forest stage is fp32 either way")
+    ap.add_argument("--rewalk", action="store_true",
+                    help="forest workloads: the forward keeps nothing and the backward walks the trees again")
     ap.add_argument("--lean", action="store_true",
                     help="c3 only: skip the other configurations (N = 1) and the strong-scaling / training legs (N > 1)")
     ap.add_argument("--kernel-only", action="store_true",
