@@ -5,9 +5,22 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "hingetree_b200.h"
 
 namespace ht {
+
+// f(std::integral_constant<int, I>) for I = 0 .. N-1, unrolled at compile time (the index can then
+// be used where the language wants a constant: template arguments, immediate operands).
+template <int I, int N, typename F>
+__host__ __device__ __forceinline__ void static_for(F &&f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, N>(f);
+  }
+}
+
 
 constexpr int TREE = HT_KIND_TREE;
 constexpr int FERN = HT_KIND_FERN;

@@ -84,15 +84,6 @@ __device__ __forceinline__ uint32_t stream_raw_where_at(const WT *base) {
     asm volatile("ld.global.cs.u32 %0, [%1+%2];" : "=r"(v) : "l"(base), "n"(ELEMENTS * 4));
   return v;
 }
-// f(std::integral_constant<int, I>) for I = 0 .. N-1, unrolled at compile time.
-template <int I, int N, typename F>
-__device__ __forceinline__ void static_for(F &&f) {
-  if constexpr (I < N) {
-    f(std::integral_constant<int, I>{});
-    static_for<I + 1, N>(f);
-  }
-}
-
 template <typename WT>
 __device__ __forceinline__ uint32_t unpack_where(uint32_t raw) {
   return sizeof(WT) == 2 ? (raw & 0xffu) | ((raw >> 8) << 16) : raw;

@@ -148,7 +148,6 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(const
   const int slots = kWarps / groups_of_samples;
   const int sample_group = warp % groups_of_samples;
   const int slot = warp / groups_of_samples;
-  const int per_warp = a.per_warp;
   const int64_t row0 = (int64_t)blockIdx.x * S;
   // blockIdx.y splits the tree groups among CTAs when there are too few sample tiles to fill the
   // machine; this CTA walks groups [group0, group0 + num_groups), `it` counts them from 0
@@ -158,6 +157,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(const
   const int num_groups = max(0, min(groups_per_cta, all_groups - group0));
   const uint32_t params_addr = smem_addr(params);
 
+  const int per_warp = a.per_warp;
   auto issue = [&](int it) {
     const int64_t first_tree = (int64_t)(group0 + it) * G;
     const int64_t count = min((int64_t)G, a.T - first_tree);
@@ -232,17 +232,44 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(const
   auto done_with_buffer = [&](int it) {
     __syncwarp();
     if (lane == 0) {
-      __threadfence_block();
-      const uint32_t before = atomicAdd(&finished[it & 1], 1u);
-      if (before == kWarps - 1) {
-        atomicExch(&finished[it & 1], 0u);
-        __threadfence_block();
-        if (it + 2 < num_groups) issue(it + 2);
-      }
+      uint32_t before;  // wraps to zero with the last warp: acquire / release order the warps' reads before the refill
+      asm volatile("atom.acq_rel.cta.shared::cta.inc.u32 %0, [%1], %2;"
+                   : "=r"(before)
+                   : "r"(smem_addr(&finished[it & 1])), "r"((uint32_t)kWarps - 1u)
+                   : "memory");
+      if (before == (uint32_t)kWarps - 1u && it + 2 < num_groups) issue(it + 2);
     }
   };
 
-  for (int it = 0; it < num_groups; ++it) {
+  int it = 0;
+  if (!SAVE && tma_store) {
+    // The loop of the benchmark shapes, with nothing in it that the full groups of a forest with the
+    // weights in its records do not need: one register addresses the warp's four consecutive records,
+    // and the buffer goes back with one atomic (it wraps to zero with the last warp, which refills).
+    const int fast = max(0, min(num_groups, full_groups - group0));
+    for (; it < fast; ++it) {
+      const uint32_t buffer = (uint32_t)(it & 1);
+      if (!poisoned && !mbar_wait(&full[buffer], (uint32_t)((it >> 1) & 1))) {
+        poisoned = true;
+        if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
+      }
+      const uint32_t rec[4] = {params_addr + buffer * (uint32_t)G * lay.bytes + warp_records, 0u, 0u, 0u};
+      uint32_t unused[4];
+      float result[4] = {0.f, 0.f, 0.f, 0.f};
+      if (!poisoned) walk<KIND, DEPTH, OrdT, 4, WREC, true>(rec, xl_addr, x_stride, result, unused);
+      done_with_buffer(it);
+      if (store_issuer) tma::wait_stores_read();  // the previous box has been read out of the staging area
+      named_barrier(1 + sample_group, group_threads);
+      sts_b128(box_mine, result[0], result[1], result[2], result[3]);
+      tma::fence_async_shared();
+      named_barrier(1 + sample_group, group_threads);  // box complete and visible to the TMA engine
+      if (store_issuer) {
+        tma::store_2d(&a.out_map, box_addr, (group0 + it) * G, (int)(row0 + sample_group * 32));
+        tma::commit_group();
+      }
+    }
+  }
+  for (; it < num_groups; ++it) {
     const int group = group0 + it;
     if (!poisoned && !mbar_wait(&full[it & 1], (uint32_t)((it >> 1) & 1))) {
       poisoned = true;

@@ -12,9 +12,12 @@ constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr size_t kSmemBudget = 227 * 1024;
 constexpr int kHeadBytes = 16;  // tree records start with {thr(1), thr(2), thr(3), packed ordinals}
-// Spin limit for the parameter pipeline: far beyond any real copy latency, small enough that a
-// lost copy ends the kernel (with a flag) instead of hanging the device.
-constexpr uint32_t kMaxSpins = 1u << 22;
+// Limits of a wait on the parameter pipeline: one try may sleep in the hardware for up to kTryNanoseconds
+// (no issue slots spent meanwhile), and kMaxSpins tries end the wait: far beyond any real copy latency,
+// small enough that a lost copy ends the kernel (with a flag) within about two seconds instead of hanging
+// the device.
+constexpr uint32_t kTryNanoseconds = 4096;
+constexpr uint32_t kMaxSpins = 1u << 19;
 
 __host__ __device__ constexpr uint32_t round16(uint32_t v) { return (v + 15u) & ~15u; }
 
@@ -153,10 +156,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(smem_addr(bar)), "r"(parity)
+        : "r"(smem_addr(bar)), "r"(parity), "n"(kTryNanoseconds)
         : "memory");
     if (done) return true;
   }
@@ -170,6 +173,28 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+
+// The same loads with a constant part of the address as an immediate operand of the instruction.
+template <uint32_t OFFSET>
+__device__ __forceinline__ float lds_f32_at(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(OFFSET));
+  return v;
+}
+template <uint32_t OFFSET>
+__device__ __forceinline__ uint32_t lds_b32_at(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFFSET));
+  return v;
+}
+template <uint32_t OFFSET>
+__device__ __forceinline__ uint4 lds_b128_at(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr), "n"(OFFSET));
   return v;
 }
 
@@ -210,6 +235,15 @@ __device__ __forceinline__ float min3(float a, float b, float c) {
   return r;
 }
 
+// Byte permute as the instruction defines it (the selector is used as given: bit 3 of a nibble would
+// replicate the chosen byte's sign, so callers keep it clear).  The intrinsic of the same purpose first
+// masks the selector, which costs an instruction.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(selector));
+  return r;
+}
+
 __device__ __forceinline__ uint32_t pick(const uint4 &q, int i) {
   return i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w;
 }
@@ -217,14 +251,19 @@ __device__ __forceinline__ uint32_t pick(const uint4 &q, int i) {
 // Walks NT trees (records at rec[0..NT)) for this lane's sample.  With the leaf weights in the
 // records (WREC) result is |min margin| * leaf weight; otherwise result is |min margin| and
 // path is 2^DEPTH + the path bits, root first.
-template <int KIND, int DEPTH, typename OrdT, int NT, bool WREC>
+// CONSECUTIVE: the NT records follow one another from rec[0] (rec[1..] are not read), so the place of a
+// record is a constant that joins the immediate offset of every load and one register addresses all NT.
+template <int KIND, int DEPTH, typename OrdT, int NT, bool WREC, bool CONSECUTIVE = false>
 __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr, uint32_t x_stride,
                                      float (&result)[NT], uint32_t (&path)[NT]) {
   constexpr bool kPaired = paired_ordinals(KIND, DEPTH, (uint32_t)sizeof(OrdT));
   constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT), WREC, kPaired);
+  // scalar copies: constants a lambda may use without capturing the struct
+  constexpr uint32_t kRecordBytes = lay.bytes, kThrAt = lay.thr, kOrdAt = lay.ord, kWeightAt = lay.w;
+  constexpr uint32_t kLeaves = 1u << DEPTH;
   uint32_t v[NT];
-  float best[NT], first[NT], held[NT];
-  if (KIND == FERN) {
+  float best[NT], first[NT], held[NT] = {};
+  if constexpr (KIND == FERN) {
     // every lane tests the same decisions: thresholds and feature indices come in 16-byte broadcasts
     constexpr int kPerWord = 4 / (int)sizeof(OrdT);   // feature indices per 32-bit word
     constexpr int kPerQuad = 4 * kPerWord;            // ... per 16-byte load
@@ -235,8 +274,9 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
     for (int l = 0; l < DEPTH; ++l) {
 #pragma unroll
       for (int u = 0; u < NT; ++u) {
-        if (l % 4 == 0) tq[u] = lds_b128(rec[u] + lay.thr + 4u * l);
-        if (l % kPerQuad == 0) oq[u] = lds_b128(rec[u] + lay.ord + (uint32_t)sizeof(OrdT) * l);
+        const uint32_t at = CONSECUTIVE ? rec[0] + (uint32_t)u * lay.bytes : rec[u];
+        if (l % 4 == 0) tq[u] = lds_b128(at + lay.thr + 4u * l);
+        if (l % kPerQuad == 0) oq[u] = lds_b128(at + lay.ord + (uint32_t)sizeof(OrdT) * l);
         const uint32_t tbits = pick(tq[u], l % 4);
         const uint32_t obits = pick(oq[u], (l % kPerQuad) / kPerWord);
         const uint32_t c = (obits >> (8 * (int)sizeof(OrdT) * (l % kPerWord))) & (sizeof(OrdT) == 1 ? 0xffu : 0xffffu);
@@ -253,63 +293,71 @@ __device__ __forceinline__ void walk(const uint32_t (&rec)[NT], uint32_t xl_addr
     }
   } else {
     constexpr bool kHead = sizeof(OrdT) == 1;  // root + children in one 16-byte broadcast
-    uint4 head[NT];
+    uint4 head[NT] = {};
     uint32_t family[NT];  // paired form: feature indices of an even-level vertex and its children
-#pragma unroll
-    for (int u = 0; u < NT; ++u) {
+    static_for<0, NT>([&](auto tree) {
+      constexpr int u = decltype(tree)::value;
       v[u] = 1u;
       family[u] = 0u;
       held[u] = 0.0f;
-      if (kHead) head[u] = lds_b128(rec[u]);
-    }
-#pragma unroll
-    for (int l = 0; l < DEPTH; ++l) {
-#pragma unroll
-      for (int u = 0; u < NT; ++u) {
+      if constexpr (kHead) head[u] = lds_b128_at<(CONSECUTIVE ? u * kRecordBytes : 0u)>(rec[CONSECUTIVE ? 0 : u]);
+    });
+    static_for<0, DEPTH>([&](auto level) {
+      constexpr int l = decltype(level)::value;
+      static_for<0, NT>([&](auto tree) {
+        constexpr int u = decltype(tree)::value;
+        [[maybe_unused]] constexpr uint32_t place = CONSECUTIVE ? u * kRecordBytes : 0u;  // of record u, from the base register
+        [[maybe_unused]] const uint32_t base = rec[CONSECUTIVE ? 0 : u];
         float thr;
         uint32_t c;
-        if (kHead && l == 0) {
+        if constexpr (kHead && l == 0) {
           thr = __uint_as_float(head[u].x);
           c = head[u].w & 0xffu;
-        } else if (kHead && l == 1) {
+        } else if constexpr (kHead && l == 1) {
           thr = __uint_as_float(v[u] == 3u ? head[u].z : head[u].y);
-          c = __byte_perm(head[u].w, 0u, v[u] | 0x4440u);  // v is 2 or 3: the left or the right child's byte
-        } else if (kPaired) {
-          thr = lds_f32(rec[u] + 4u * v[u] + (lay.thr - 4u));
-          if (l % 2 == 0) {
-            family[u] = lds_b32(rec[u] + 4u * v[u] + (lay.ord + 4u * paired_first(l) - 4u * (1u << l)));
-            c = family[u] & 0xffu;
-          } else {
-            c = __byte_perm(family[u], 0u, (v[u] & 1u) | 0x4442u);  // byte 2 (left child) or 3 (right child)
-          }
+          c = prmt(head[u].w, 0u, v[u] | 0x4440u);  // v is 2 or 3: the left or the right child's byte
         } else {
-          thr = lds_f32(rec[u] + 4u * v[u] + (lay.thr - 4u));
-          c = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * v[u] + (lay.ord - (uint32_t)sizeof(OrdT)));
+          const uint32_t at = base + 4u * v[u];  // one address for this vertex's threshold and feature word
+          thr = lds_f32_at<place + kThrAt - 4u>(at);
+          if constexpr (kPaired) {
+            if constexpr (l % 2 == 0) {
+              family[u] = lds_b32_at<place + kOrdAt + 4u * paired_first(l) - 4u * (1u << l)>(at);
+              c = family[u] & 0xffu;
+            } else {
+              c = prmt(family[u], 0u, (v[u] & 1u) | 0x4442u);  // byte 2 (left child) or 3 (right child)
+            }
+          } else {
+            c = lds_ord<OrdT>(base + place + (uint32_t)sizeof(OrdT) * v[u] + (kOrdAt - (uint32_t)sizeof(OrdT)));
+          }
         }
         const float nm = thr - lds_f32(c * x_stride + xl_addr);
         const float am = fabsf(nm);
-        if (l == 0) {
+        if constexpr (l == 0) {
           best[u] = am;
           first[u] = am;
-        } else if (l % 2 == 1) {
+        } else if constexpr (l % 2 == 1) {
           held[u] = am;  // joins the minimum together with the next level's
         } else {
           best[u] = min3(best[u], held[u], am);
         }
         v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
-      }
-    }
+      });
+    });
   }
-#pragma unroll
-  for (int u = 0; u < NT; ++u) {
+  static_for<0, NT>([&](auto tree) {
+    constexpr int u = decltype(tree)::value;
+    [[maybe_unused]] constexpr uint32_t place = CONSECUTIVE ? u * kRecordBytes : 0u;
+    [[maybe_unused]] const uint32_t base = rec[CONSECUTIVE ? 0 : u];
     if (DEPTH % 2 == 0 && KIND != FERN) best[u] = fminf(best[u], held[u]);  // the last level was an odd one
     const float am = (first[u] != first[u]) ? first[u] : best[u];
     path[u] = v[u];
-    if (WREC)
-      result[u] = __fmul_rn(am, lds_f32(rec[u] + 4u * v[u] + (lay.w - 4u * (1u << DEPTH))));
-    else
+    if constexpr (!WREC)
       result[u] = am;
-  }
+    else if constexpr (kWeightAt >= 4u * kLeaves)
+      result[u] = __fmul_rn(am, lds_f32_at<place + kWeightAt - 4u * kLeaves>(base + 4u * v[u]));
+    else  // short records (ferns): the constant is negative
+      result[u] = __fmul_rn(am, lds_f32(base + place + 4u * v[u] + (kWeightAt - 4u * kLeaves)));
+  });
 }
 
 // The traversal as the backward needs it: the signed margin and the deciding vertex, with the
@@ -348,14 +396,14 @@ __device__ __forceinline__ void walk_full(const uint32_t (&rec)[NT], const uint3
         c = head[u].w & 0xffu;
       } else if (PAIRED && l == 1) {
         thr = __uint_as_float((at & 1u) ? head[u].z : head[u].y);
-        c = __byte_perm(head[u].w, 0u, at | 0x4440u);
+        c = prmt(head[u].w, 0u, at | 0x4440u);
       } else if (PAIRED) {
         thr = lds_f32(rec[u] + 4u * at + (lay.thr - 4u));
         if (l % 2 == 0) {
           family[u] = lds_b32(rec[u] + 4u * at + (lay.ord + 4u * paired_first(l) - 4u * (1u << l)));
           c = family[u] & 0xffu;
         } else {
-          c = __byte_perm(family[u], 0u, (at & 1u) | 0x4442u);
+          c = prmt(family[u], 0u, (at & 1u) | 0x4442u);
         }
       } else {
         thr = lds_f32(rec[u] + 4u * at + (lay.thr - 4u));
