@@ -24,6 +24,9 @@ step).  Rank 0 prints ONE JSON line:
   strong, train (c3 at N > 1) the large batch split over the ranks (no collective; shards compared with the
                 whole on rank 0), and training steps of c2 and c5 with the NCCL all-reduce of the parameter
                 gradients inside the timed region
+  reference_gpu (c3 at N = 1, when oracle/_ref holds the reference built with its CUDA kernels) the reference's own
+                GPU kernels on the same device and tensors: c1 and c2 steps and the c3 forward on a 65 536-row
+                chunk, each with this library's time for the same call and whether the results are equal
   gpu_launches  kernels of this library launched inside the timed region (the library's own counter)
 
 Other workloads: c1 (the reference's speedtest shape, fwd+bwd), c2 (ferns, fwd+bwd), c4 (2-D
@@ -564,6 +567,69 @@ def check_against_port(check):
     return ok
 
 
+def reference_gpu_leg(device, steps=5):
+    """The reference's own CUDA kernels (the unmodified reference built with ``-DWITH_CUDA=1`` by
+    ``oracle/build_ref.py --gpu``) on the same GPU and the same tensors, as a second baseline beside the CPU one:
+    C1 and C2 steps, and the C3 forward on 65 536-row chunks (the reference launches ``gridDim.y = B / 8`` unchecked,
+    hingetree_gpu.cu:491-495, so B stays far below 524 280).  Each figure comes with this library's time on
+    the same call and whether the two results are equal bit for bit.  None when the build is not there."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    try:
+        import build_ref
+        ref = build_ref.load_gpu()
+    except Exception:
+        return None
+    from hingetreefortorch_b200._ext import hingetree_cpp as ours
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / steps
+
+    legs = {}
+    for key, rows in (("c1", None), ("c2", None), ("c3", 65536)):
+        wl = WORKLOADS[key]
+        B = rows or wl["B"]
+        thr, ord_, w = (t.to(device) for t in make_params(wl))
+        x = make_x(wl, B, 0).to(device)
+        fwd_ref = getattr(ref, wl["kind"] + "_forward")
+        fwd_ours = getattr(ours, wl["kind"] + "_forward")
+        out_ref, out_ours = fwd_ref(x, thr, ord_, w), fwd_ours(x, thr, ord_, w)
+        leg = {"workload": wl["name"] if rows is None else "C3 forward on a %d-row chunk" % B,
+               "forward_equal": bool(torch.equal(out_ref, out_ours))}
+        if wl["bwd"]:
+            g = torch.randn(out_ref.shape, generator=torch.Generator().manual_seed(7)).to(device)
+            bwd_ref = getattr(ref, wl["kind"] + "_backward")
+            bwd_ours = getattr(ours, wl["kind"] + "_backward")
+            g_ref = bwd_ref(x, True, thr, True, ord_, False, w, True, g)
+            g_ours = bwd_ours(x, True, thr, True, ord_, False, w, True, g)
+            scale = [float(t.abs().max()) for t in (g_ref[0], g_ref[1], g_ref[3])]
+            leg["backward_max_difference_over_max"] = max(
+                float((a - b).abs().max()) / max(s_, 1e-30)
+                for a, b, s_ in zip((g_ref[0], g_ref[1], g_ref[3]), (g_ours[0], g_ours[1], g_ours[3]), scale))
+            t_ref = timed(lambda: (fwd_ref(x, thr, ord_, w), bwd_ref(x, True, thr, True, ord_, False, w, True, g)))
+            t_ours = timed(lambda: (fwd_ours(x, thr, ord_, w), bwd_ours(x, True, thr, True, ord_, False, w, True, g)))
+        else:
+            t_ref = timed(lambda: fwd_ref(x, thr, ord_, w))
+            t_ours = timed(lambda: fwd_ours(x, thr, ord_, w))
+        evals = evals_per_step(wl, B)
+        leg.update({"reference_ms": t_ref, "ours_ms": t_ours, "reference_value": evals / (t_ref * 1e-3),
+                    "ours_value": evals / (t_ours * 1e-3), "unit": "tree-evals/s", "ratio": t_ref / t_ours})
+        legs[key] = leg
+        del x, thr, ord_, w, out_ref, out_ours
+        torch.cuda.empty_cache()
+    legs["call"] = "hingetree_cpp operators of both libraries (allocation and the reference's per-call host sync included)"
+    return legs
+
+
 def bind_to_gpu_numa_node(local):
     """Best effort: run this rank (and first-touch its pinned buffers) on the host cores next to its GPU.
     Returns what was done, for the end-to-end record."""
@@ -750,7 +816,7 @@ def our_arm(a, wl):
     runner.release_e2e()
 
     # ---- what else one run records: the other configurations (N = 1), the collective and the split (N > 1) ----
-    workloads, scale = None, None
+    workloads, scale, reference_gpu = None, None, None
     if a.workload == "c3" and not a.rows and not a.lean:
         del runner
         torch.cuda.empty_cache()
@@ -758,6 +824,7 @@ def our_arm(a, wl):
             workloads = {}
             for key in ("c1", "c2", "c4", "c5", "c5tc"):
                 workloads[key], checks[key] = side_workload(key, device, timer, peak)
+            reference_gpu = reference_gpu_leg(device)
         else:
             scale = scale_legs(a, device, rank, world, timer, peak)
 
@@ -807,6 +874,8 @@ def our_arm(a, wl):
             line["workloads"] = workloads
         if scale is not None:
             line.update(scale)
+        if reference_gpu is not None:
+            line["reference_gpu"] = reference_gpu
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -11,7 +11,10 @@ imported next to this repository's own ``hingetree_cpp``.  The build is CPU only
 reference's ``WITH_CUDA`` macro stays undefined, as in the ``CppExtension`` branch of its
 setup.py:47-56) and uses the same ``-O2`` the reference's setup.py:24 passes.
 
-Usage:  python oracle/build_ref.py [--reference /path/to/HingeTreeForTorch] [--jobs N]
+Usage:  python oracle/build_ref.py [--reference /path/to/HingeTreeForTorch] [--jobs N] [--gpu]
+
+With ``--gpu`` the reference is built a second time with its CUDA kernels (``build_gpu``), as the second
+baseline bench.py times when the file is present.
 
 The product never imports this module or its output; only tests, the smoke check and the
 CPU-baseline legs of bench.py do, as the checker.
@@ -82,6 +85,89 @@ def build(reference, jobs=8, force=False):
     return target
 
 
+# The reference's GPU translation units (the torch.cuda.is_available() branch of its setup.py:29-37).
+GPU_MODULE = "hingetree_ref_gpu"
+GPU_SOURCES = [
+    "hingetree_gpu.cu", "hingetree_sparse_gpu.cu", "ImageToMatrix_gpu.cu", "hingetree_conv_gpu.cu",
+    "hingetree_fused_linear_gpu.cu", "hingetree_fusion_gpu.cu", "expand_gpu.cu",
+]
+
+
+def gpu_so_path():
+    return os.path.join(OUT, GPU_MODULE + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_gpu(reference, jobs=8, force=False):
+    """The unmodified reference WITH its CUDA kernels (``-DWITH_CUDA=1``, as its setup.py does when a GPU is
+    present), compiled for sm_100 into ``oracle/_ref/hingetree_ref_gpu*.so``: the reference's own GPU code as
+    a second baseline beside its CPU code.  nvcc cross-compiles, so this runs on a machine without a GPU.
+    Callers keep the batch at or below 524 280 rows: the reference launches ``gridDim.y = B / 8`` unchecked
+    (hingetree_gpu.cu:491-495)."""
+    from torch.utils import cpp_extension as ce
+    import torch
+
+    target = gpu_so_path()
+    cpu_srcs = [os.path.join(reference, s) for s in SOURCES]
+    gpu_srcs = [os.path.join(reference, s) for s in GPU_SOURCES]
+    if not all(os.path.exists(s) for s in cpu_srcs + gpu_srcs):
+        raise FileNotFoundError("reference sources not found under %s" % reference)
+    if os.path.exists(target) and not force:
+        if os.path.getmtime(target) >= max(os.path.getmtime(s) for s in cpu_srcs + gpu_srcs):
+            return target
+    gpu_out = os.path.join(OUT, "gpu")
+    os.makedirs(gpu_out, exist_ok=True)
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    nvcc = os.path.join(cuda_home, "bin", "nvcc")
+    cxx = os.environ.get("CXX", "g++")
+    try:
+        paths = ce.include_paths(device_type="cuda")
+    except TypeError:  # older signature
+        paths = ce.include_paths(True)
+    inc = []
+    for p in paths + [os.path.join(cuda_home, "include"), sysconfig.get_paths()["include"]]:
+        inc += ["-isystem", p]
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    defines = ["-DWITH_CUDA=1", "-DTORCH_EXTENSION_NAME=" + GPU_MODULE, "-DTORCH_API_INCLUDE_EXTENSION_H",
+               "-D_GLIBCXX_USE_CXX11_ABI=%d" % abi]
+
+    def compile_one(src):
+        obj = os.path.join(gpu_out, os.path.basename(src) + ".o")
+        if src.endswith(".cu"):
+            cmd = [nvcc, "-O2", "-std=c++17", "-w", "-gencode", "arch=compute_100,code=sm_100", "--expt-relaxed-constexpr",
+                   "-D__CUDA_NO_HALF_OPERATORS__", "-D__CUDA_NO_HALF_CONVERSIONS__", "-D__CUDA_NO_HALF2_OPERATORS__",
+                   "-D__CUDA_NO_BFLOAT16_CONVERSIONS__", "-Xcompiler", "-fPIC"] + defines + inc
+        else:
+            cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-w"] + defines + inc
+        subprocess.run(cmd + ["-c", src, "-o", obj], check=True)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=jobs) as ex:
+        objs = list(ex.map(compile_one, gpu_srcs + cpu_srcs))
+    link = [cxx, "-shared", "-o", target] + objs
+    for cand in ("/usr/lib/x86_64-linux-gnu/libstdc++.so.6", "/usr/lib64/libstdc++.so.6"):
+        if os.path.exists(cand):
+            link.append(cand)
+            break
+    for d in ce.library_paths(device_type="cuda") + [os.path.join(cuda_home, "lib64")]:
+        link += ["-L" + d, "-Wl,-rpath," + d]
+    link += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart"]
+    subprocess.run(link, check=True)
+    return target
+
+
+def load_gpu():
+    """Import the reference built with its GPU kernels (raises ImportError if it was never built)."""
+    import importlib.util
+    import torch  # noqa: F401
+    path = gpu_so_path()
+    if not os.path.exists(path):
+        raise ImportError("reference GPU build not present: run python oracle/build_ref.py --gpu")
+    spec = importlib.util.spec_from_file_location(GPU_MODULE, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def trained_forest_path():
     return os.path.join(OUT, "trained_forests.npz")
 
@@ -134,7 +220,10 @@ if __name__ == "__main__":
                     help="checkout of NIH-MIP/HingeTreeForTorch (or set HINGETREE_REFERENCE)")
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     ap.add_argument("--force", action="store_true")
+    ap.add_argument("--gpu", action="store_true", help="also build the reference with its CUDA kernels (several minutes)")
     a = ap.parse_args()
     print(build(a.reference, a.jobs, a.force))
     print(extract_trained_forests(a.reference))
+    if a.gpu:
+        print(build_gpu(a.reference, a.jobs, a.force))
     sys.exit(0)
