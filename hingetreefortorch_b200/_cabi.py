@@ -20,7 +20,7 @@ HT_FLAG_PIPELINE_TIMEOUT = 0x80000000  # a bounded wait inside a kernel ran out:
 
 # every symbol include/hingetree_b200.h declares (checked by the CPU test-suite)
 SYMBOLS = [
-    "ht_version", "ht_status_string", "ht_last_cuda_error", "ht_forest_workspace_bytes", "ht_forest_forward_saves", "ht_launch_count",
+    "ht_version", "ht_status_string", "ht_last_cuda_error", "ht_forest_workspace_bytes", "ht_forest_forward_saves", "ht_launch_count", "ht_selftest_bounded_wait",
     "ht_forest_forward_f32", "ht_forest_leafmap_f32", "ht_forest_marginmap_f32",
     "ht_forest_reachability_f32", "ht_forest_backward_f32",
     "ht_forest_forward_f64", "ht_forest_leafmap_f64", "ht_forest_marginmap_f64", "ht_forest_reachability_f64",
@@ -323,3 +323,9 @@ def linear_tf32_stats(x, w, status=None):
     _check(library().ht_linear_tf32_stats_f32(_ptr(x), _ptr(w), _ptr(z), _ptr(colsum), _ptr(colsumsq), ctypes.c_int64(M),
                                               ctypes.c_int64(N), ctypes.c_int64(K), _ptr(status), _stream(x)))
     return z, colsum, colsumsq
+
+
+def selftest_bounded_wait(status):
+    """Runs the library's self test of a bounded wait (a one-warp kernel waits a few tries on a barrier that
+    nothing arrives on): afterwards the int32 status word holds HT_FLAG_PIPELINE_TIMEOUT."""
+    _check(library().ht_selftest_bounded_wait(_ptr(status), _stream(status)))

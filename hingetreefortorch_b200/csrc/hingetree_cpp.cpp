@@ -182,6 +182,16 @@ int64_t pipeline_status() {
   return flags;
 }
 
+// The library's self test of a bounded wait, reporting into the current device's long-lived status word exactly
+// as a tile kernel would: the next pipeline_status() (or checked call) raises.
+void selftest_bounded_wait() {
+  const c10::Device device(c10::kCUDA, c10::cuda::current_device());
+  torch::Tensor word = sticky_word(device, true);
+  raise_status(ht_selftest_bounded_wait(reinterpret_cast<uint32_t *>(word.data_ptr<int32_t>()),
+                                        (ht_stream_t)c10::cuda::getCurrentCUDAStream().stream()),
+               "selftest_bounded_wait");
+}
+
 // Most scratch a backward call may take for its per-evaluation records (12 bytes per tree
 // evaluation).  Beyond it the call runs without them: atomic scatters instead of ordered sums.
 // Default: whatever fits (an allocation that fails falls back to the path without records); a caller may
@@ -706,6 +716,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         "[z, sum, sumsq]. K and N must be multiples of 4.");
   m.def("set_save_forward", [](bool on) { g_save_forward = on; },
         "Whether tree_/fern_forward_saving keep the traversal for the backward (default) or act as the plain forward.");
+  m.def("selftest_bounded_wait", &selftest_bounded_wait,
+        "Runs a one-warp kernel whose bounded wait has to run out (nothing faults): the next pipeline_status() raises.");
   m.def("pipeline_status", &pipeline_status,
         "Reads and clears the current device's long-lived kernel status word (calls on ordinals already known to be "
         "valid do not synchronise; a kernel that gave up on a bounded wait leaves its flag there). Raises RuntimeError "

@@ -678,3 +678,28 @@ int forward_tiled(const ht_forest_problem *p, const float *x, const float *thr, 
 }
 
 }  // namespace ht
+
+// ---- self test of the bounded wait ---------------------------------------------------------
+namespace ht {
+namespace {
+// One warp waits on a barrier that nothing ever arrives on, with a limit of a few tries: the wait has to
+// run out, the kernel has to set the flag and return with its context intact.  This is the path a lost
+// parameter copy takes in the tile kernels, exercised without losing a copy.
+__global__ void bounded_wait_selftest_kernel(uint32_t *status_word) {
+  __shared__ uint64_t never;
+  if (threadIdx.x == 0) {
+    tile::mbar_init(&never, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (!tile::mbar_wait(&never, 0u, 8u) && threadIdx.x == 0) atomicOr(status_word, HT_FLAG_PIPELINE_TIMEOUT);
+}
+}  // namespace
+}  // namespace ht
+
+extern "C" int ht_selftest_bounded_wait(uint32_t *status_word, ht_stream_t stream) {
+  if (status_word == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  ht::bounded_wait_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status_word);
+  HT_CHECK_LAUNCH();
+  return HT_OK;
+}

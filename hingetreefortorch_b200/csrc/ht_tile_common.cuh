@@ -151,8 +151,8 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
 }
 
 // Bounded wait on a phase of the barrier.  Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kMaxSpins; ++spin) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t max_tries = kMaxSpins) {
+  for (uint32_t spin = 0; spin < max_tries; ++spin) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

@@ -71,6 +71,10 @@ int ht_version(void);
 const char *ht_status_string(int status);
 int ht_last_cuda_error(void); /* cudaError_t of the last failed runtime call on this thread */
 uint64_t ht_launch_count(void); /* kernels this library has launched in this process (diagnostics; no reference counterpart) */
+/* Self test of the tile kernels' bounded waits: a one-warp kernel waits, with a limit of a few tries, on a barrier
+ * that nothing arrives on, and reports the way a tile kernel reports a copy that never came: it ORs
+ * HT_FLAG_PIPELINE_TIMEOUT into *status_word and returns.  Nothing faults or hangs.  (No reference counterpart.) */
+int ht_selftest_bounded_wait(uint32_t *status_word, ht_stream_t stream);
 
 /* Scratch bytes ht_forest_* calls need for this problem: compact ordinals and the tile kernel's
  * per-tree records.  With HT_WORKSPACE_FOR_BACKWARD in p->flags the figure also covers 12 bytes

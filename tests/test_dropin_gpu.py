@@ -228,3 +228,22 @@ def test_speedtest_sweeps_like_the_reference(ext, capfd):
     assert timings[1].tolist() == [float(d) for _ in range(10) for d in range(1, 13)]
     assert bool((timings[2:] > 0).all()) and float(timings[2:].max()) < 50.0
     assert "hingetree_forward: numBatches = 100" in capfd.readouterr().out
+
+
+def test_a_wait_that_runs_out_reaches_the_caller(ext):
+    """The error path of the tile kernels without a lost copy: the library's self-test kernel waits a few tries on
+    a barrier nothing arrives on, sets HT_FLAG_PIPELINE_TIMEOUT and returns; the C ABI shows the flag in the
+    caller's status word, the extension raises RuntimeError at its next status read and clears the word, and the
+    device keeps working."""
+    from hingetreefortorch_b200 import _cabi
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _cabi.selftest_bounded_wait(status)
+    assert int(status.item()) & _cabi.HT_FLAG_PIPELINE_TIMEOUT
+    assert ext.pipeline_status() == 0
+    ext.selftest_bounded_wait()
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        ext.pipeline_status()
+    assert ext.pipeline_status() == 0
+    x, thr, ord_, w = random_forest_inputs(3, "tree", 16, 8, (), 4, 3, ())
+    dx, dthr, dord, dw = dev(x, thr, ord_, w)
+    assert np.array_equal(ext.tree_forward(dx, dthr, dord, dw).cpu().numpy(), ho.forward("tree", x, thr, ord_, w))
