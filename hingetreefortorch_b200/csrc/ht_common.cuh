@@ -66,6 +66,14 @@ struct PathOf {
 using Path = PathOf<float>;
 
 // Rounded-once arithmetic (no contraction into fused multiply-adds) and |.| for both real types.
+// Two or four adjacent floats added to global memory with one reduction (8- / 16-byte aligned address).
+__device__ __forceinline__ void red_add_pair(float *p, float a, float b) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void red_add_quad(float *p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 __device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
 __device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
 __device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }

@@ -98,6 +98,37 @@ __global__ void __launch_bounds__(kBlock) forest_backward_atomic_kernel(ForestAr
   const Real *wl = a.w + (j * a.L + p.key) * a.M;
   const Real *gl = g + e * a.M;
   Real acc = (Real)0;
+  if constexpr (std::is_same<Real, float>::value) {
+    // an even number of outputs per leaf: the rows of g, w and gw start on 8-byte boundaries (given aligned
+    // tensors), so they are read two at a time and the leaf-weight gradient takes one reduction per pair
+    if ((a.M & 1) == 0 && ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(a.w) | reinterpret_cast<uintptr_t>(gw)) & 7u) == 0) {
+      float *gwl = gw != nullptr ? gw + (j * a.L + p.key) * a.M : nullptr;
+      // (a row of 8-byte alignment starts with a pair when it is not on a 16-byte boundary, then goes on in fours)
+      int64_t m = 0;
+      auto pair = [&]() {
+        const float2 gm = __ldg(reinterpret_cast<const float2 *>(gl + m));
+        const float2 wm = __ldg(reinterpret_cast<const float2 *>(wl + m));
+        acc = add_rn(acc, mul_rn(mul_rn(s, wm.x), gm.x));  // the same terms in the same order as one at a time
+        acc = add_rn(acc, mul_rn(mul_rn(s, wm.y), gm.y));
+        if (gwl != nullptr) red_add_pair(gwl + m, mul_rn(am, gm.x), mul_rn(am, gm.y));
+        m += 2;
+      };
+      if (gwl == nullptr || (reinterpret_cast<uintptr_t>(gwl) & 15u) != 0) pair();
+      for (; m + 4 <= a.M; m += 4) {
+        const float2 g0 = __ldg(reinterpret_cast<const float2 *>(gl + m)), g1 = __ldg(reinterpret_cast<const float2 *>(gl + m + 2));
+        const float2 w0 = __ldg(reinterpret_cast<const float2 *>(wl + m)), w1 = __ldg(reinterpret_cast<const float2 *>(wl + m + 2));
+        acc = add_rn(acc, mul_rn(mul_rn(s, w0.x), g0.x));
+        acc = add_rn(acc, mul_rn(mul_rn(s, w0.y), g0.y));
+        acc = add_rn(acc, mul_rn(mul_rn(s, w1.x), g1.x));
+        acc = add_rn(acc, mul_rn(mul_rn(s, w1.y), g1.y));
+        if (gwl != nullptr) red_add_quad(gwl + m, mul_rn(am, g0.x), mul_rn(am, g0.y), mul_rn(am, g1.x), mul_rn(am, g1.y));
+      }
+      while (m < a.M) pair();
+      if (gx != nullptr) atomicAdd(gx + (i * a.C + a.ord[j * a.N + p.vertex]) * a.K + k, acc);
+      if (gthr != nullptr) atomicAdd(gthr + j * a.N + p.vertex, -acc);
+      return;
+    }
+  }
   for (int64_t m = 0; m < a.M; ++m) {
     const Real gm = __ldg(gl + m);
     acc = add_rn(acc, mul_rn(mul_rn(s, __ldg(wl + m)), gm));
