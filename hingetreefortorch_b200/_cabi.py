@@ -31,6 +31,7 @@ SYMBOLS = [
     "ht_conv_output_size", "ht_conv_workspace_bytes", "ht_conv_forward_f32", "ht_conv_backward_f32",
     "ht_contract", "ht_expand",
     "ht_trie_forward_f32", "ht_trie_backward_f32", "ht_forest_touched_f32", "ht_linear_tf32_stats_f32",
+    "ht_init_medians_workspace_bytes", "ht_init_medians_f32", "ht_init_medians_f64", "ht_thresholds_f32", "ht_thresholds_f64",
 ]
 
 
@@ -329,3 +330,36 @@ def selftest_bounded_wait(status):
     """Runs the library's self test of a bounded wait (a one-warp kernel waits a few tries on a barrier that
     nothing arrives on): afterwards the int32 status word holds HT_FLAG_PIPELINE_TIMEOUT."""
     _check(library().ht_selftest_bounded_wait(_ptr(status), _stream(status)))
+
+
+def init_medians(kind, x, thr, ord_):
+    """Median initialisation of the thresholds on the device (thr is overwritten): x [B, C, *inner], thr and
+    ord_ [T, N] on the same CUDA device, float32 or float64."""
+    import torch
+    lib = library()
+    lib.ht_init_medians_workspace_bytes.restype = ctypes.c_size_t
+    B, C = x.shape[0], x.shape[1]
+    K = 1
+    for d in x.shape[2:]:
+        K *= d
+    T, N = thr.shape
+    depth = N if kind == "fern" else (N + 1).bit_length() - 1
+    code = {"tree": 0, "fern": 1}[kind]
+    need = lib.ht_init_medians_workspace_bytes(code, ctypes.c_int64(B), ctypes.c_int64(K), ctypes.c_int64(T), depth,
+                                               x.element_size())
+    ws = torch.empty(max(int(need), 1), dtype=torch.uint8, device=x.device)
+    fn = lib.ht_init_medians_f64 if x.dtype == torch.float64 else lib.ht_init_medians_f32
+    _check(fn(code, _ptr(x), _ptr(thr), _ptr(ord_), ctypes.c_int64(B), ctypes.c_int64(C), ctypes.c_int64(K),
+              ctypes.c_int64(T), depth, _ptr(ws), ctypes.c_size_t(ws.numel()), _stream(x)))
+    return thr
+
+
+def thresholds(fix, thr, ord_):
+    """check (fix False: 1 per consistent tree) or fix (1 per changed tree; thr is edited) on the device."""
+    import torch
+    T, N = thr.shape
+    depth = (N + 1).bit_length() - 1
+    result = torch.zeros(T, dtype=torch.uint8, device=thr.device)
+    fn = library().ht_thresholds_f64 if thr.dtype == torch.float64 else library().ht_thresholds_f32
+    _check(fn(1 if fix else 0, _ptr(thr), _ptr(ord_), ctypes.c_int64(T), depth, _ptr(result), _stream(thr)))
+    return result

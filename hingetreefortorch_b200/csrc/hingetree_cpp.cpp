@@ -569,7 +569,6 @@ std::vector<bool> thresholds_utility(int kind, bool fix, torch::Tensor thr, torc
     bad_argument("Error: All tensors are expected to be on the same device.");
   if (!thr.is_contiguous() || !ord.is_contiguous() || !w.is_contiguous())
     bad_argument("Error: All tensors are expected to be contiguous.");
-  if (!thr.device().is_cpu()) bad_argument("Error: This operation is only supported on CPU tensors.");
   if (thr.dim() != 2 || ord.dim() != 2 || w.dim() < 2)
     bad_argument("Error: inWeights must have at least 2 dimensions. inThresholds and inOrdinals must have 2 dimensions.");
   if (thr.sizes() != ord.sizes() || w.size(0) != thr.size(0))
@@ -586,6 +585,23 @@ std::vector<bool> thresholds_utility(int kind, bool fix, torch::Tensor thr, torc
   const int64_t trees = thr.size(0), count = thr.size(1);
   std::vector<bool> result(trees, kind == HT_KIND_FERN ? !fix : false);
   if (kind == HT_KIND_FERN) return result;  // decision order is irrelevant for ferns
+  if (thr.scalar_type() != torch::kFloat32 && thr.scalar_type() != torch::kFloat64)
+    bad_argument("Error: Unsupported data type. Only torch.float32 and torch.float64 are supported.");
+  if (thr.device().is_cuda()) {
+    // the reference refuses anything but CPU tensors; parameters that live on a device are handled there
+    c10::DeviceGuard guard(thr.device());
+    torch::Tensor flags = torch::zeros({trees}, torch::TensorOptions().dtype(torch::kUInt8).device(thr.device()));
+    const int rc = thr.scalar_type() == torch::kFloat32
+                       ? ht_thresholds_f32(fix ? 1 : 0, thr.data_ptr<float>(), ord.data_ptr<int64_t>(), trees, depth,
+                                           flags.data_ptr<uint8_t>(), current_stream(thr))
+                       : ht_thresholds_f64(fix ? 1 : 0, thr.data_ptr<double>(), ord.data_ptr<int64_t>(), trees, depth,
+                                           flags.data_ptr<uint8_t>(), current_stream(thr));
+    raise_status(rc, "thresholds");
+    const torch::Tensor host = flags.cpu();
+    for (int64_t j = 0; j < trees; ++j) result[j] = host.data_ptr<uint8_t>()[j] != 0;
+    return result;
+  }
+  if (!thr.device().is_cpu()) bad_argument("Error: This operation is only supported on CPU and CUDA tensors.");
   const int64_t *po = ord.data_ptr<int64_t>();
   auto run = [&](auto *pt) {
     for (int64_t j = 0; j < trees; ++j)

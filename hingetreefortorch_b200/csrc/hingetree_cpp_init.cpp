@@ -25,6 +25,8 @@
 // counts over all samples of the vertex with counts over the drawn ones (GreedyInit.h:68-76,148-158).
 #include "hingetree_cpp_ops.h"
 
+#include <c10/core/DeviceGuard.h>
+
 #include <algorithm>
 #include <cmath>
 #include <limits>
@@ -258,14 +260,38 @@ bool init_medians(InitFamily family, torch::Tensor x, torch::Tensor thr, torch::
     bad_argument(
         "Error: inData, inThresholds, inWeights are expected to share the same torch real number data type. "
         "inOrdinals is expected to be type torch.int64.");
-  if (!x.device().is_cpu() || !thr.device().is_cpu() || !ord.device().is_cpu() || !w.device().is_cpu())
+  // The reference takes CPU tensors only; here tensors that all live on one CUDA device are taken as well
+  // and the medians are found there (ht_init_medians_*), with the same result.
+  const bool on_device = x.device().is_cuda();
+  if (on_device) {
+    if (thr.device() != x.device() || ord.device() != x.device() || w.device() != x.device())
+      bad_argument("Error: All tensors are expected to be on the same device.");
+  } else if (!x.device().is_cpu() || !thr.device().is_cpu() || !ord.device().is_cpu() || !w.device().is_cpu()) {
     bad_argument("Error: All tensors are expected to be on the CPU.");
+  }
   if (!x.is_contiguous() || !thr.is_contiguous() || !ord.is_contiguous() || !w.is_contiguous())
     bad_argument("Error: All tensors are expected to be contiguous.");
   if (x.scalar_type() != torch::kFloat32 && x.scalar_type() != torch::kFloat64)
     bad_argument("Error: Unsupported data type. Only torch.float32 and torch.float64 are supported.");
   InitShape s;
   if (!read_shape(family, x, thr, ord, w, s)) return false;
+  if (on_device) {
+    if (s.depth > 20) return false;
+    if (s.rows == 0) return true;
+    if (ord.min().item<int64_t>() < 0 || ord.max().item<int64_t>() >= s.channels) return false;  // as the host path
+    c10::DeviceGuard guard(x.device());
+    const int kind = family == InitFamily::Fern ? HT_KIND_FERN : HT_KIND_TREE;
+    const size_t need = ht_init_medians_workspace_bytes(kind, s.rows, s.inner, s.trees, (int)s.depth, (int)x.element_size());
+    torch::Tensor ws = torch::empty({(int64_t)std::max<size_t>(need, 1)}, torch::TensorOptions().dtype(torch::kUInt8).device(x.device()));
+    ht_stream_t stream = current_stream(x);
+    const int rc = x.scalar_type() == torch::kFloat32
+                       ? ht_init_medians_f32(kind, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(), s.rows,
+                                             s.channels, s.inner, s.trees, (int)s.depth, ws.data_ptr(), (size_t)ws.numel(), stream)
+                       : ht_init_medians_f64(kind, x.data_ptr<double>(), thr.data_ptr<double>(), ord.data_ptr<int64_t>(), s.rows,
+                                             s.channels, s.inner, s.trees, (int)s.depth, ws.data_ptr(), (size_t)ws.numel(), stream);
+    raise_status(rc, "init_medians");
+    return true;
+  }
   if (x.scalar_type() == torch::kFloat32)
     return median_splits<float>(family, s, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>());
   return median_splits<double>(family, s, x.data_ptr<double>(), thr.data_ptr<double>(), ord.data_ptr<int64_t>());

@@ -291,6 +291,29 @@ int ht_contract(int dims, int elem_bytes, const void *image, void *patches, int6
 int ht_expand(int dims, int elem_bytes, const void *patches, void *image, int64_t batch_times_channels,
               const int64_t *osize, const int64_t *window, const int64_t *padding, ht_stream_t stream);
 
+/* ---- threshold initialisation and hygiene on the device -------------------------------------------------
+ * The reference runs these on the host only (tree_/fern_/trie_init_medians: hingetree.cpp:1519-1533,
+ * MedianInit.h:133-257; tree_check_thresholds / tree_fix_thresholds: hingetree.cpp:936,1010,
+ * HingeTreeCommon.h:244-287); here the data may stay in device memory.
+ *
+ * ht_init_medians_*: thr [T, N] <- for every vertex the median (rank floor(n / 2) from the largest) of feature
+ * ord[t, v] over the samples of x [B, C, K] that reach it; samples with a larger value go to the right child; a
+ * vertex no sample reaches keeps its threshold; ferns (kind HT_KIND_FERN, N = depth) see all samples at every
+ * level; tries are trees.  Equal to the host operator bit for bit (except for the sign of a zero median when the
+ * samples hold both zeros, which the host leaves to its partition order).  The ordinals must be in [0, C).
+ * workspace: ht_init_medians_workspace_bytes(...) bytes (at most about 1 GiB: more trees go in several rounds). */
+size_t ht_init_medians_workspace_bytes(int kind, int64_t B, int64_t K, int64_t T, int depth, int element_bytes);
+int ht_init_medians_f32(int kind, const float *x, float *thr, const int64_t *ord, int64_t B, int64_t C, int64_t K, int64_t T,
+                        int depth, void *workspace, size_t workspace_bytes, ht_stream_t stream);
+int ht_init_medians_f64(int kind, const double *x, double *thr, const int64_t *ord, int64_t B, int64_t C, int64_t K, int64_t T,
+                        int depth, void *workspace, size_t workspace_bytes, ht_stream_t stream);
+/* ht_thresholds_*: trees only (thr, ord [T, 2^depth - 1]).  fix == 0: result[t] = 1 when no vertex of tree t has
+ * a threshold outside the interval its same-feature ancestors leave reachable; fix != 0: such thresholds are moved
+ * inside (parents first; to the middle of a bounded interval, 1 inside an unbounded one) and result[t] = 1 when
+ * tree t was changed.  result: T bytes in device memory. */
+int ht_thresholds_f32(int fix, float *thr, const int64_t *ord, int64_t T, int depth, unsigned char *result, ht_stream_t stream);
+int ht_thresholds_f64(int fix, double *thr, const int64_t *ord, int64_t T, int depth, unsigned char *result, ht_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
