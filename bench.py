@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the hinge forest evaluation path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c3b|c2|c1|c4|c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c3b|c2|c1|c4|c5|c5tc|c5f]
 
 A step is one pass of the hot path over one batch of seeded synthetic input.  The default
 workload (c3) is the large-batch forest inference configuration: x [1048576,128] ~ N(0,1), 1024
@@ -19,7 +19,8 @@ step).  Rank 0 prints ONE JSON line:
                 forward keeps its traversal for the backward; a 64-row slice of it is checked against the port
   cuda_graph    (c1, c2) the same step captured once and replayed as a CUDA graph
   workloads     (c3 at N = 1) the other configurations c1, c2, c4, c5 (and c5tc: c5 with this library's tensor-core
-                Linear + BatchNorm front), a few device-resident steps each, with a slice of each result checked
+                Linear + BatchNorm front; c5f: front and forest as one step, the normalised activations never
+                written), a few device-resident steps each, with a slice of each result checked
                 against the port in the CPU leg
   strong, train (c3 at N > 1) the large batch split over the ranks (no collective; shards compared with the
                 whole on rank 0), and training steps of c2 and c5 with the NCCL all-reduce of the parameter
@@ -59,6 +60,9 @@ WORKLOADS = {
                name="C4 HingeTreeConv2d fwd+bwd x[64,64,64,64] 3x3 s1 p1, 128x64 trees depth 5"),
     "c5": dict(op="pipeline", kind="tree", B=8192, C=784, T=100, depth=7, M=0, x="rand", bwd=True, hidden=12700,
                name="C5 Linear(784->12700) -> BatchNorm1d -> forest(100 trees depth 7, sequential ordinals) train step"),
+    "c5f": dict(op="pipeline", kind="tree", B=8192, C=784, T=100, depth=7, M=0, x="rand", bwd=True, hidden=12700, front="fused",
+                name="C5 as one step of this library: LinearBatchNormForest (tcgen05 TF32 projection + statistics, forest on "
+                     "the unmaterialised normalisation, one-pass batch-norm input gradient) train step"),
     "c5tc": dict(op="pipeline", kind="tree", B=8192, C=784, T=100, depth=7, M=0, x="rand", bwd=True, hidden=12700, front="tc",
                  name="C5 with this library's tensor-core front: LinearBatchNorm1d (tcgen05 TF32 projection + statistics) "
                       "-> forest(100 trees depth 7, sequential ordinals) train step"),
@@ -403,7 +407,9 @@ class ModuleRunner:
             self.model = module
         else:
             module = R.RandomHingeForest(wl["hidden"], wl["T"], wl["depth"], init_type="sequential")
-            if wl.get("front") == "tc":
+            if wl.get("front") == "fused":
+                self.model = R.LinearBatchNormForest(R.LinearBatchNorm1d(wl["C"], wl["hidden"]), module)
+            elif wl.get("front") == "tc":
                 self.model = nn.Sequential(R.LinearBatchNorm1d(wl["C"], wl["hidden"]), module)
             else:
                 self.model = nn.Sequential(nn.Linear(wl["C"], wl["hidden"], bias=False),
@@ -539,9 +545,11 @@ def side_workload(key, device, timer, peak, steps=8):
         check = {"kind": wl["kind"], "op": "conv", "x": x1.cpu().numpy(), "thr": module.thresholds.detach().cpu().numpy(),
                  "ord": module.ordinals.cpu().numpy(), "w": module.weights.detach().cpu().numpy(), "out": out1.cpu().numpy()}
     else:  # the pipeline's forest stage on the normalised activations the model itself produced
-        forest = runner.model[-1]
+        fused = wl.get("front") == "fused"
+        forest = runner.model.forest if fused else runner.model[-1]
+        front = runner.model.front if fused else runner.model[:-1]
         with torch.no_grad():
-            z = runner.model[:-1](runner.x)[:rows].contiguous()
+            z = front(runner.x)[:rows].contiguous()
             out = forest(z)
         check = {"kind": wl["kind"], "op": "forest", "x": z.cpu().numpy(), "thr": forest.thresholds.detach().cpu().numpy(),
                  "ord": forest.ordinals.cpu().numpy(), "w": forest.weights.detach().cpu().numpy(), "out": out.cpu().numpy()}
@@ -697,7 +705,7 @@ def scale_legs(a, device, rank, world, timer, peak):
     torch.cuda.empty_cache()
 
     train = {}
-    for key in ("c2", "c5", "c5tc"):
+    for key in ("c2", "c5", "c5tc", "c5f"):
         twl = WORKLOADS[key]
         runner = make_runner(twl, twl["B"], device, rank, world)
         for _ in range(3):
@@ -822,7 +830,7 @@ def our_arm(a, wl):
         torch.cuda.empty_cache()
         if world == 1:
             workloads = {}
-            for key in ("c1", "c2", "c4", "c5", "c5tc"):
+            for key in ("c1", "c2", "c4", "c5", "c5tc", "c5f"):
                 workloads[key], checks[key] = side_workload(key, device, timer, peak)
             reference_gpu = reference_gpu_leg(device)
         else:

@@ -92,3 +92,68 @@ class LinearBatchNorm1d(nn.Module):
     def extra_repr(self):
         return "in_features=%d, out_features=%d, eps=%g, momentum=%g" % (self.in_features, self.out_features, self.eps,
                                                                          self.momentum)
+
+
+class _LinearBatchNormForest(torch.autograd.Function):
+    """forest((z - mean) * invstd) with z = x @ w.T and batch statistics, the normalised activations never written:
+    the forest normalises the features it visits (bit-identical to the forest behind a materialised normalisation),
+    and its backward hands the normalisation's backward a gradient of one entry per (sample, tree) and the two column
+    sums it needs, so the gradient with respect to z takes one pass over z."""
+
+    @staticmethod
+    def forward(ctx, x, w, thresholds, ordinals, weights, eps, fern):
+        x, w = x.contiguous(), w.contiguous()
+        z, total, total_sq = hingetree_cpp.linear_tf32_stats(x, w)
+        rows = x.shape[0]
+        mean = total / rows
+        var = (total_sq / rows - mean * mean).clamp_min_(0.0)
+        invstd = torch.rsqrt(var + eps)
+        op = hingetree_cpp.fern_normalised_forward if fern else hingetree_cpp.tree_normalised_forward
+        out = op(z, mean, invstd, thresholds, ordinals, weights)
+        ctx.fern = fern
+        ctx.save_for_backward(x, w, z, mean, invstd, thresholds, ordinals, weights)
+        ctx.mark_non_differentiable(mean, var)
+        return out, mean, var
+
+    @staticmethod
+    def backward(ctx, grad_out, _grad_mean, _grad_var):
+        x, w, z, mean, invstd, thresholds, ordinals, weights = ctx.saved_tensors
+        op = hingetree_cpp.fern_normalised_backward if ctx.fern else hingetree_cpp.tree_normalised_backward
+        grad_z, grad_thr, grad_weights = op(z, mean, invstd, thresholds, ctx.needs_input_grad[2], ordinals, weights,
+                                            ctx.needs_input_grad[4], grad_out.contiguous())
+        previous = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        try:
+            grad_x = grad_z @ w if ctx.needs_input_grad[0] else None
+            grad_w = grad_z.t() @ x if ctx.needs_input_grad[1] else None
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = previous
+        return grad_x, grad_w, grad_thr, None, grad_weights, None, None
+
+
+class LinearBatchNormForest(nn.Module):
+    """A LinearBatchNorm1d front and a RandomHingeForest / RandomHingeFern behind it as one step: in training mode the
+    normalised activations are never materialised (see _LinearBatchNormForest); in evaluation mode the two modules
+    run one after the other.  The parameters stay those of the two modules (``front.weight``, ``forest.thresholds``,
+    ``forest.ordinals``, ``forest.weights``), so checkpoints of the unfused pair load as they are."""
+
+    def __init__(self, front, forest):
+        super().__init__()
+        if not isinstance(front, LinearBatchNorm1d):
+            raise TypeError("front must be a LinearBatchNorm1d")
+        if forest.in_channels != front.out_features:
+            raise ValueError("the forest reads %d channels, the front produces %d" % (forest.in_channels, front.out_features))
+        self.front, self.forest = front, forest
+
+    def forward(self, x):
+        if not self.training:
+            return self.forest(self.front(x))
+        front, forest = self.front, self.forest
+        out, mean, var = _LinearBatchNormForest.apply(x, front.weight, forest.thresholds, forest.ordinals, forest.weights,
+                                                      front.eps, bool(forest._fern))
+        with torch.no_grad():
+            rows = x.shape[0]
+            front.num_batches_tracked += 1
+            front.running_mean.lerp_(mean, front.momentum)
+            front.running_var.lerp_(var * (rows / max(rows - 1, 1)), front.momentum)
+        return out

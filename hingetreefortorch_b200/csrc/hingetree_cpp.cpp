@@ -435,6 +435,67 @@ std::vector<torch::Tensor> linear_tf32_stats(torch::Tensor x, torch::Tensor w) {
   return {z, sum, sumsq};
 }
 
+// The forest of a Linear -> BatchNorm1d(affine=False) -> forest pipeline on the raw activations z [B, C] with the
+// normalisation's mean and 1/std per column (no reference operator: its pipeline materialises the normalisation).
+namespace {
+void check_statistics(const torch::Tensor &z, const torch::Tensor &mean, const torch::Tensor &invstd) {
+  if (z.dim() != 2) bad_argument("Error: the activations are expected to be [batch, channels].");
+  if (mean.scalar_type() != torch::kFloat32 || invstd.scalar_type() != torch::kFloat32 || mean.device() != z.device() ||
+      invstd.device() != z.device() || mean.dim() != 1 || invstd.dim() != 1 || mean.size(0) != z.size(1) ||
+      invstd.size(0) != z.size(1) || !mean.is_contiguous() || !invstd.is_contiguous())
+    bad_argument("Error: mean and invstd are expected to be contiguous torch.float32 vectors of one entry per channel, "
+                 "on the device of the activations.");
+}
+}  // namespace
+
+torch::Tensor forest_normalised_forward(int kind, torch::Tensor z, torch::Tensor mean, torch::Tensor invstd, torch::Tensor thr,
+                                        torch::Tensor ord, torch::Tensor w) {
+  ForestCall call(kind, z, thr, ord, w, nullptr);
+  check_statistics(z, mean, invstd);
+  c10::DeviceGuard guard(z.device());
+  torch::Tensor out = torch::empty(call.out_sizes, z.options());
+  torch::Tensor ws = make_workspace(ht_forest_normalised_workspace_bytes(&call.problem), z);
+  OrdinalGuard og(ord, call.problem.C);
+  raise_status(ht_forest_normalised_forward_f32(&call.problem, z.data_ptr<float>(), mean.data_ptr<float>(),
+                                                invstd.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
+                                                w.data_ptr<float>(), out.data_ptr<float>(), ws.data_ptr(), ws.numel(), og.word(),
+                                                current_stream(z)),
+               "forest forward on normalised activations");
+  og.finish();
+  return out;
+}
+
+// Returns {dz, gthr or None, gw or None}: the gradient with respect to the RAW activations (through the
+// normalisation with batch statistics) and the forest's parameter gradients.
+std::vector<torch::Tensor> forest_normalised_backward(int kind, torch::Tensor z, torch::Tensor mean, torch::Tensor invstd,
+                                                      torch::Tensor thr, bool need_thr, torch::Tensor ord, torch::Tensor w,
+                                                      bool need_w, torch::Tensor g) {
+  ForestCall call(kind, z, thr, ord, w, &g);
+  check_statistics(z, mean, invstd);
+  c10::DeviceGuard guard(z.device());
+  const int64_t B = call.problem.B, C = call.problem.C, T = call.problem.T;
+  torch::Tensor gthr = need_thr ? torch::empty_like(thr) : torch::Tensor();
+  torch::Tensor gw = need_w ? torch::empty_like(w) : torch::Tensor();
+  torch::Tensor column = torch::empty({B, T}, z.options().dtype(torch::kInt32));
+  torch::Tensor value = torch::empty({B, T}, z.options());
+  torch::Tensor sums = torch::empty({2, C}, z.options());
+  torch::Tensor dz = torch::empty_like(z);
+  torch::Tensor ws = make_workspace(ht_forest_normalised_workspace_bytes(&call.problem), z);
+  OrdinalGuard og(ord, C);
+  raise_status(ht_forest_normalised_backward_f32(
+                   &call.problem, z.data_ptr<float>(), mean.data_ptr<float>(), invstd.data_ptr<float>(), thr.data_ptr<float>(),
+                   ord.data_ptr<int64_t>(), w.data_ptr<float>(), g.data_ptr<float>(), need_thr ? gthr.data_ptr<float>() : nullptr,
+                   need_w ? gw.data_ptr<float>() : nullptr, column.data_ptr<int32_t>(), value.data_ptr<float>(),
+                   sums.data_ptr<float>(), sums.data_ptr<float>() + C, ws.data_ptr(), ws.numel(), og.word(), current_stream(z)),
+               "forest backward on normalised activations");
+  raise_status(ht_batchnorm_input_grad_f32(z.data_ptr<float>(), mean.data_ptr<float>(), invstd.data_ptr<float>(),
+                                           sums.data_ptr<float>(), sums.data_ptr<float>() + C, column.data_ptr<int32_t>(),
+                                           value.data_ptr<float>(), dz.data_ptr<float>(), B, C, T, current_stream(z)),
+               "batch normalisation input gradient");
+  og.finish();
+  return {dz, gthr, gw};
+}
+
 torch::Tensor forest_leafmap(int kind, torch::Tensor x, torch::Tensor thr, torch::Tensor ord, torch::Tensor w) {
   ForestCall call(kind, x, thr, ord, w, nullptr, true);
   c10::DeviceGuard guard(x.device());
@@ -696,6 +757,14 @@ using namespace htx;
   m.def(prefix "_backward_saved", [](torch::Tensor x, bool nx, torch::Tensor t, bool nt, torch::Tensor o, bool no,  \
                                      torch::Tensor w, bool nw, torch::Tensor g, torch::Tensor saved, bool det) {    \
     return forest_backward_saved(KIND, det, x, nx, t, nt, o, no, w, nw, g, saved);                                  \
+  });                                                                                                               \
+  m.def(prefix "_normalised_forward", [](torch::Tensor z, torch::Tensor mean, torch::Tensor invstd, torch::Tensor t,  \
+                                         torch::Tensor o, torch::Tensor w) {                                        \
+    return forest_normalised_forward(KIND, z, mean, invstd, t, o, w);                                               \
+  });                                                                                                               \
+  m.def(prefix "_normalised_backward", [](torch::Tensor z, torch::Tensor mean, torch::Tensor invstd, torch::Tensor t, \
+                                          bool nt, torch::Tensor o, torch::Tensor w, bool nw, torch::Tensor g) {     \
+    return forest_normalised_backward(KIND, z, mean, invstd, t, nt, o, w, nw, g);                                   \
   });                                                                                                               \
   m.def(prefix "_check_thresholds", [](torch::Tensor t, torch::Tensor o, torch::Tensor w) {                         \
     return thresholds_utility(KIND, false, t, o, w);                                                                \

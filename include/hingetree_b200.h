@@ -291,6 +291,33 @@ int ht_contract(int dims, int elem_bytes, const void *image, void *patches, int6
 int ht_expand(int dims, int elem_bytes, const void *patches, void *image, int64_t batch_times_channels,
               const int64_t *osize, const int64_t *window, const int64_t *padding, ht_stream_t stream);
 
+/* ---- forest behind a batch normalisation that is not materialised ---------------------------------------
+ * The reference's sequential-initialisation pipeline is torch.nn.Linear -> torch.nn.BatchNorm1d(affine=False) ->
+ * RandomHingeForest (README.md:110-129).  These entries are the forest of that pipeline reading the RAW
+ * activations z [B, C] (K = 1) with the per-column mean and 1/std: a visited feature is (z - mean) * invstd,
+ * rounded as ATen's batch_norm_elemt rounds it, so the forward equals hingetree_gpu_forward (hingetree_gpu.cu:416)
+ * on the materialised normalisation bit for bit.  No reference counterpart.
+ * workspace: ht_forest_normalised_workspace_bytes(p) bytes. */
+size_t ht_forest_normalised_workspace_bytes(const ht_forest_problem *p);
+int ht_forest_normalised_forward_f32(const ht_forest_problem *p, const float *z, const float *mean, const float *invstd,
+                                     const float *thr, const int64_t *ord, const float *w, float *out, void *workspace,
+                                     size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+/* Backward of the same: gthr [T, N] and gw [T, L, M] (either may be NULL) as ht_forest_backward_f32 gives them
+ * (default mode: atomics), and the gradient with respect to the normalised activations y in the form it has —
+ * one entry per (sample, tree): column[B, T] (the feature the deciding vertex tests) and value[B, T] — with the two
+ * column sums the normalisation's backward needs: sum_g[c] = sum_i gy[i, c], sum_gy[c] = sum_i gy[i, c] * y[i, c]. */
+int ht_forest_normalised_backward_f32(const ht_forest_problem *p, const float *z, const float *mean, const float *invstd,
+                                      const float *thr, const int64_t *ord, const float *w, const float *g, float *gthr,
+                                      float *gw, int32_t *column, float *value, float *sum_g, float *sum_gy, void *workspace,
+                                      size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+/* Gradient with respect to z of y = (z - mean) * invstd with batch statistics (training mode, no affine part):
+ * dz[i, c] = invstd[c] * (gy[i, c] - sum_g[c] / B - y[i, c] * sum_gy[c] / B), gy given by the records above: one pass
+ * over z for the dense part, one over the records (the formula of torch's batch-norm backward,
+ * aten/src/ATen/native/cuda/Normalization.cuh, batch_norm_backward_elemt). */
+int ht_batchnorm_input_grad_f32(const float *z, const float *mean, const float *invstd, const float *sum_g, const float *sum_gy,
+                                const int32_t *column, const float *value, float *dz, int64_t B, int64_t C, int64_t T,
+                                ht_stream_t stream);
+
 /* ---- threshold initialisation and hygiene on the device -------------------------------------------------
  * The reference runs these on the host only (tree_/fern_/trie_init_medians: hingetree.cpp:1519-1533,
  * MedianInit.h:133-257; tree_check_thresholds / tree_fix_thresholds: hingetree.cpp:936,1010,

@@ -90,3 +90,68 @@ def test_pipeline_of_the_reference_readme_runs_on_the_module():
                       forest.ordinals.cpu().numpy(), forest.weights.detach().cpu().numpy())
     assert np.array_equal(y.detach().cpu().numpy(), want)
     assert front.weight.grad is not None and bool(torch.isfinite(front.weight.grad).all())
+
+
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+@pytest.mark.parametrize("extra", [(), (3,)])
+def test_forest_on_unmaterialised_normalisation(kind, extra):
+    """`*_normalised_forward` on raw activations equals the plain forward on ATen's materialised normalisation bit for
+    bit; `*_normalised_backward` gives the forest's parameter gradients at the usual bar and, for the gradient with
+    respect to the raw activations, what torch's batch-norm backward makes of the plain backward's dense gradient."""
+    from conftest import grad_close
+    from hingetreefortorch_b200._ext import hingetree_cpp as ext
+    from oracle import hinge_oracle as ho
+    gen = torch.Generator().manual_seed(5)
+    B, C, T, depth = 300, 52, 11, 5
+    N = depth if kind == "fern" else 2 ** depth - 1
+    z = (torch.randn(B, C, generator=gen) * 3 + 1).cuda()
+    thr = (torch.rand(T, N, generator=gen) * 2 - 1).cuda()
+    ord_ = torch.randint(0, C, (T, N), generator=gen).cuda()
+    w = torch.randn((T, 2 ** depth) + extra, generator=gen).cuda()
+    g = torch.randn((B, T) + extra, generator=gen).cuda()
+    mean = z.mean(0)
+    invstd = torch.rsqrt(z.var(0, unbiased=False) + 1e-5)
+    y = torch.batch_norm_elemt(z, None, None, mean, invstd, 1e-5)
+    plain = getattr(ext, kind + "_forward")(y, thr, ord_, w)
+    fused = getattr(ext, kind + "_normalised_forward")(z, mean, invstd, thr, ord_, w)
+    assert torch.equal(fused, plain)
+    dz, gthr, gw = getattr(ext, kind + "_normalised_backward")(z, mean, invstd, thr, True, ord_, w, True, g)
+    want = ho.backward(kind, y.cpu().numpy(), thr.cpu().numpy(), ord_.cpu().numpy(), w.cpu().numpy(), g.cpu().numpy())
+    mags = ho.backward_magnitudes(kind, y.cpu().numpy(), thr.cpu().numpy(), ord_.cpu().numpy(), w.cpu().numpy(), g.cpu().numpy())
+    assert grad_close(gthr, want[1], mags[1]) and grad_close(gw, want[2], mags[2])
+    gy = torch.from_numpy(want[0]).cuda()  # dense gradient with respect to the normalised activations
+    sum_dy, sum_dy_xmu, _, _ = torch.batch_norm_backward_reduce(gy, z, mean, invstd, None, True, False, False)
+    count = torch.full((1,), B, dtype=torch.int32, device="cuda")
+    want_dz = torch.batch_norm_backward_elemt(gy, z, mean, invstd, None, sum_dy, sum_dy_xmu, count)
+    scale = float(want_dz.abs().max())
+    assert float((dz - want_dz).abs().max()) <= 2e-5 * scale
+    only = getattr(ext, kind + "_normalised_backward")(z, mean, invstd, thr, False, ord_, w, False, g)
+    assert only[1] is None and only[2] is None and float((only[0] - want_dz).abs().max()) <= 2e-5 * scale
+
+
+def test_fused_front_and_forest_module_against_the_pair():
+    """LinearBatchNormForest in training mode against its own two modules run one after the other on the same
+    parameters: outputs equal bit for bit (same z, same statistics, same rounding of the normalisation), gradients
+    within the tolerance of sums in another order; running statistics advance the same way; evaluation mode is the pair."""
+    from hingetreefortorch_b200 import RandomHingeForest as R
+    torch.manual_seed(13)
+    trees, depth, hidden = 12, 5, 372  # 12 * 31
+    pair_front = R.LinearBatchNorm1d(40, hidden).cuda()
+    pair_forest = R.RandomHingeForest(hidden, trees, depth, init_type="sequential").cuda()
+    front, forest = R.LinearBatchNorm1d(40, hidden).cuda(), R.RandomHingeForest(hidden, trees, depth, init_type="sequential").cuda()
+    front.load_state_dict(pair_front.state_dict())
+    forest.load_state_dict(pair_forest.state_dict())
+    fused = R.LinearBatchNormForest(front, forest)
+    x = torch.rand(256, 40, device="cuda")
+    out = fused(x)
+    ref = pair_forest(pair_front(x))
+    assert torch.equal(out, ref)
+    g = torch.randn_like(out)
+    (out * g).sum().backward()
+    (ref * g).sum().backward()
+    for a, b in ((front.weight.grad, pair_front.weight.grad), (forest.thresholds.grad, pair_forest.thresholds.grad),
+                 (forest.weights.grad, pair_forest.weights.grad)):
+        assert float((a - b).abs().max()) <= 1e-3 * float(b.abs().max()) + 1e-6
+    assert torch.equal(front.running_mean, pair_front.running_mean) and torch.equal(front.running_var, pair_front.running_var)
+    fused.eval(), pair_front.eval(), pair_forest.eval()
+    assert torch.equal(fused(x), pair_forest(pair_front(x)))
