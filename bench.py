@@ -66,6 +66,17 @@ WORKLOADS = {
     "c5tc": dict(op="pipeline", kind="tree", B=8192, C=784, T=100, depth=7, M=0, x="rand", bwd=True, hidden=12700, front="tc",
                  name="C5 with this library's tensor-core front: LinearBatchNorm1d (tcgen05 TF32 projection + statistics) "
                       "-> forest(100 trees depth 7, sequential ordinals) train step"),
+    # the other operator families, for the profiler (--kernel-only): sizes whose tensors exceed L2
+    "a5": dict(op="family", family="linear", kind="tree", B=262144, C=784, T=100, depth=7, M=0, O=10, bwd=True,
+               name="A5 tree_fused_linear forward + backward x[262144,784] T=100 depth=7 O=10"),
+    "a6": dict(op="family", family="fusion", kind="tree", B=2048, C=32, Cv=16, T=64, depth=6, M=0, bwd=True,
+               name="A6 tree_fusion forward + backward img[2048,32,16,16] vec[2048,16] T=64 depth=6"),
+    "a7": dict(op="family", family="sparse", kind="tree", B=65536, C=256, T=256, depth=7, M=0, bwd=True,
+               name="A7 sparse_tree_backward x[65536,256] T=256 depth=7"),
+    "a8": dict(op="family", family="contract", kind="tree", B=64, C=64, T=0, depth=1, M=0, H=256, W=256, bwd=False,
+               name="A8 contract + expand x[64,64,256,256] float32 window 2x2"),
+    "a9": dict(op="family", family="trie", kind="tree", B=131072, C=256, T=256, depth=7, M=0, bwd=True,
+               name="A9 trie forward + backward x[131072,256] T=256 depth=7"),
 }
 
 
@@ -80,6 +91,9 @@ def decisions(kind, depth):
 
 
 def evals_per_step(wl, B):
+    if wl["op"] == "family":
+        inner = 256 if wl["family"] == "fusion" else 1
+        return B * max(wl["T"], 1) * inner
     if wl["op"] == "conv":
         return B * wl["H"] * wl["W"] * wl["T"] * wl["C"]  # one tree per (out channel, in channel, position)
     return B * wl["T"]
@@ -465,6 +479,70 @@ class ModuleRunner:
         self.x_pinned = None
 
 
+class FamilyRunner:
+    """One of the other operator families of the reference's surface through hingetree_cpp, device resident, at a
+    size whose tensors exceed L2: fused linear (A5), image + vector fusion (A6), sparse backward (A7), contract /
+    expand (A8), trie (A9).  These legs exist for the profiler (bench.py --workload a5 ... --kernel-only)."""
+
+    def __init__(self, wl, B, device, rank, world=1):
+        import torch
+        from hingetreefortorch_b200._ext import hingetree_cpp as ext
+        self.wl, self.B, self.device, self.torch = wl, B, device, torch
+        gen = torch.Generator().manual_seed(3)
+        family, kind, C, T, depth = wl["family"], wl["kind"], wl["C"], wl["T"], wl["depth"]
+        N, L = decisions(kind, depth), 2 ** depth
+
+        def dev(t):
+            return t.to(device)
+
+        if family == "contract":
+            x = dev(torch.randn((B, C, wl["H"], wl["W"]), generator=gen))
+            self.run = lambda: ext.expand(ext.contract(x, [2, 2], [0, 0]), [0, 0])
+            return
+        thr = dev(torch.rand((T, N), generator=gen) * 6 - 3)
+        if family == "linear":
+            x = dev(torch.rand((B, C), generator=gen))
+            ord_ = dev(torch.randint(0, C, (T, N), generator=gen))
+            w = dev(torch.randn((T, L), generator=gen))
+            lin, bias = dev(torch.randn((wl["O"], T), generator=gen)), dev(torch.randn((wl["O"],), generator=gen))
+            g = dev(torch.randn((B, wl["O"]), generator=gen))
+            fwd, bwd = getattr(ext, kind + "_fused_linear_forward"), getattr(ext, kind + "_fused_linear_backward")
+            self.run = lambda: (fwd(x, thr, ord_, w, lin, bias),
+                                bwd(x, True, thr, True, ord_, False, w, True, lin, True, bias, True, g))
+        elif family == "fusion":
+            img = dev(torch.randn((B, C, 16, 16), generator=gen))
+            vec = dev(torch.randn((B, wl["Cv"]), generator=gen))
+            ord_ = dev(torch.randint(0, C + wl["Cv"], (T, N), generator=gen))
+            w = dev(torch.randn((T, L), generator=gen))
+            g = dev(torch.randn((B, T, 16, 16), generator=gen))
+            fwd, bwd = getattr(ext, kind + "_fusion_forward"), getattr(ext, kind + "_fusion_backward")
+            self.run = lambda: (fwd(img, vec, thr, ord_, w), bwd(img, True, vec, True, thr, True, ord_, False, w, True, g))
+        elif family == "sparse":
+            x = dev(torch.randn((B, C), generator=gen))
+            ord_ = dev(torch.randint(0, C, (T, N), generator=gen))
+            w = dev(torch.randn((T, L), generator=gen))
+            g = dev(torch.randn((B, T), generator=gen))
+            bwd = getattr(ext, "sparse_" + kind + "_backward")
+            self.run = lambda: bwd(x, True, thr, True, ord_, False, w, True, g)
+        elif family == "trie":
+            x = dev(torch.randn((B, C), generator=gen))
+            ord_ = dev(torch.randint(0, C, (T, N), generator=gen))
+            w = dev(torch.randn((T, N), generator=gen))  # a weight per internal vertex
+            g = dev(torch.randn((B, T), generator=gen))
+            self.run = lambda: (ext.trie_forward(x, thr, ord_, w), ext.trie_backward(x, True, thr, True, ord_, False, w, True, g))
+        else:
+            raise SystemExit("bench.py: unknown family " + family)
+
+    def enable_backward(self):
+        pass
+
+    def step(self, backward, reduce=True):
+        self.run()
+
+    def check(self):
+        pass
+
+
 def launch_count():
     """Kernels the library has launched so far in this process (its own counter)."""
     from hingetreefortorch_b200 import _cabi
@@ -472,6 +550,8 @@ def launch_count():
 
 
 def make_runner(wl, B, device, rank, world):
+    if wl["op"] == "family":
+        return FamilyRunner(wl, B, device, rank, world)
     runner = ForestRunner(wl, B, device, rank, world) if wl["op"] == "forest" else ModuleRunner(wl, B, device, rank, world)
     if wl["bwd"]:
         runner.enable_backward()
@@ -768,7 +848,7 @@ def our_arm(a, wl):
     evals = evals_per_step(wl, B)
     value = evals * world * a.steps / (elapsed_ms * 1e-3)
 
-    if a.kernel_only:
+    if a.kernel_only or wl["op"] == "family":  # the operator-family legs are device-resident timings only
         if rank == 0:
             print(json.dumps({"kernel_only": True, "rows": B, "ms_per_step": elapsed_ms / a.steps, "value": value}))
         if world > 1:

@@ -216,6 +216,107 @@ __global__ void __launch_bounds__(kBlock) expand_kernel(PatchArgs a, const Word 
   image[e] = covered ? patches[(b * a.window_count + p) * a.cells + q] : Word(0);
 }
 
+// The same two gathers with 32-bit index arithmetic and divisions by multiplication (every divisor is a
+// launch constant), for images and patch sets of fewer than 2^31 elements each: the 64-bit division chains
+// above cost several hundred instructions per element and kept these pure copies at an eighth of the
+// memory bandwidth.  blockIdx.y walks the (batch x channel) images.
+struct FastDivisor {
+  uint32_t divisor, multiplier, shift;
+  __device__ __forceinline__ uint32_t quotient(uint32_t n) const {  // n < 2^31
+    return divisor == 1u ? n : __umulhi(n, multiplier) >> shift;
+  }
+  __device__ __forceinline__ void split(uint32_t n, uint32_t &q, uint32_t &r) const {  // q may be the variable n came from
+    const uint32_t whole = quotient(n);
+    r = n - whole * divisor;
+    q = whole;
+  }
+};
+
+inline FastDivisor make_divisor(int64_t d) {
+  FastDivisor f;
+  f.divisor = (uint32_t)d;
+  f.multiplier = 0;
+  f.shift = 0;
+  if (d > 1) {
+    uint32_t log2 = 0;
+    while ((((uint64_t)1) << log2) < (uint64_t)d) ++log2;  // ceil(log2 d)
+    const uint32_t p = 31 + log2;
+    f.multiplier = (uint32_t)(((((uint64_t)1) << p) + (uint64_t)d - 1) / (uint64_t)d);
+    f.shift = p - 32;
+  }
+  return f;
+}
+
+struct PatchArgs32 {
+  int dims;
+  uint32_t image_count, per_image;  // elements of one image, of one image's patches
+  int64_t BC;
+  FastDivisor cells, osize[3], win[3], size[3];
+  uint32_t pad[3], window_count;
+};
+
+template <typename Word>
+__global__ void __launch_bounds__(kBlock) contract32_kernel(PatchArgs32 a, const Word *__restrict__ image,
+                                                            Word *__restrict__ patches) {
+  const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= a.per_image) return;
+  uint32_t p, q;
+  a.cells.split(r, p, q);
+  uint32_t index = 0, scale = 1;
+  bool inside = true;
+  for (int d = a.dims - 1; d >= 0; --d) {
+    uint32_t pd, qd;
+    a.osize[d].split(p, p, pd);
+    a.win[d].split(q, q, qd);
+    const uint32_t at = pd * a.win[d].divisor + qd - a.pad[d];  // wraps below zero: caught by the comparison
+    inside = inside && at < a.size[d].divisor;
+    index += at * scale;
+    scale *= a.size[d].divisor;
+  }
+  // the same place in every image: the index arithmetic above is paid once per thread, four copies in flight
+  const int64_t step = gridDim.y;
+  int64_t b = blockIdx.y;
+  for (; b + 3 * step < a.BC; b += 4 * step) {
+    Word v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = inside ? image[(b + u * step) * a.image_count + index] : Word(0);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) patches[(b + u * step) * a.per_image + r] = v[u];
+  }
+  for (; b < a.BC; b += step) patches[b * a.per_image + r] = inside ? image[b * a.image_count + index] : Word(0);
+}
+
+template <typename Word>
+__global__ void __launch_bounds__(kBlock) expand32_kernel(PatchArgs32 a, const Word *__restrict__ patches,
+                                                          Word *__restrict__ image) {
+  const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= a.image_count) return;
+  uint32_t rest = e, p = 0, q = 0, pscale = 1, qscale = 1;
+  bool covered = true;
+  for (int d = a.dims - 1; d >= 0; --d) {
+    uint32_t at, od, cell;
+    a.size[d].split(rest, rest, at);
+    at += a.pad[d];
+    a.win[d].split(at, od, cell);
+    covered = covered && od < a.osize[d].divisor;
+    p += od * pscale;
+    q += cell * qscale;
+    pscale *= a.osize[d].divisor;
+    qscale *= a.win[d].divisor;
+  }
+  const uint32_t from = p * a.cells.divisor + q;
+  const int64_t step = gridDim.y;
+  int64_t b = blockIdx.y;
+  for (; b + 3 * step < a.BC; b += 4 * step) {
+    Word v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = covered ? patches[(b + u * step) * a.per_image + from] : Word(0);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) image[(b + u * step) * a.image_count + e] = v[u];
+  }
+  for (; b < a.BC; b += step) image[b * a.image_count + e] = covered ? patches[b * a.per_image + from] : Word(0);
+}
+
 inline unsigned blocks_for(int64_t n) { return (unsigned)((n + kBlock - 1) / kBlock); }
 
 int check_conv(const ht_conv_problem *p, ConvArgs &a) {
@@ -310,6 +411,34 @@ int prepare_conv(const ht_conv_problem *p, const float *x, const float *thr, con
 
 template <typename Word>
 int launch_patches(bool contract, const PatchArgs &a, const void *in, void *out, cudaStream_t stream) {
+  const int64_t per_image = a.window_count * a.cells;
+  bool narrow = a.image_count < 0x40000000 && per_image < 0x40000000 && a.BC > 0;
+  for (int d = 0; d < a.dims; ++d) narrow = narrow && a.pad[d] < 0x40000000 && a.size[d] + a.pad[d] < 0x40000000;
+  if (narrow) {
+    PatchArgs32 n;
+    n.dims = a.dims;
+    n.image_count = (uint32_t)a.image_count;
+    n.per_image = (uint32_t)per_image;
+    n.window_count = (uint32_t)a.window_count;
+    n.BC = a.BC;
+    n.cells = make_divisor(a.cells);
+    for (int d = 0; d < 3; ++d) {
+      n.osize[d] = make_divisor(d < a.dims ? a.osize[d] : 1);
+      n.win[d] = make_divisor(d < a.dims ? a.win[d] : 1);
+      n.size[d] = make_divisor(d < a.dims ? a.size[d] : 1);
+      n.pad[d] = d < a.dims ? (uint32_t)a.pad[d] : 0u;
+    }
+    // enough blocks to fill the machine several times over, and as many images per thread as that leaves
+    const unsigned across = blocks_for(contract ? per_image : a.image_count);
+    const int64_t wanted = std::max<int64_t>(1, (148 * 32 + across - 1) / across);
+    const dim3 grid(across, (unsigned)std::min<int64_t>(std::min<int64_t>(a.BC, wanted), 65535));
+    if (contract)
+      contract32_kernel<Word><<<grid, kBlock, 0, stream>>>(n, static_cast<const Word *>(in), static_cast<Word *>(out));
+    else
+      expand32_kernel<Word><<<grid, kBlock, 0, stream>>>(n, static_cast<const Word *>(in), static_cast<Word *>(out));
+    HT_CHECK_LAUNCH();
+    return HT_OK;
+  }
   if (contract) {
     const int64_t n = a.BC * a.window_count * a.cells;
     if (n > 0) contract_kernel<Word><<<blocks_for(n), kBlock, 0, stream>>>(a, static_cast<const Word *>(in), static_cast<Word *>(out));
