@@ -6,6 +6,8 @@
 // (|margin| * L[o,j]) * w[j,leaf,m] for j ascending -- the reference CPU order
 // (hingetree_fused_linear.cpp:154-181), so the result is deterministic and equal to it bit for
 // bit (the reference GPU kernel scatters the same terms with atomics in arbitrary order).
+#include <algorithm>
+
 #include "ht_common.cuh"
 
 namespace ht {
@@ -131,16 +133,15 @@ __global__ void __launch_bounds__(kBlock) linear_backward_kernel(FusionArgs a, P
   const int64_t leaf = r.leaf[e], vertex = r.vertex[e];
   const float s = sign_of(margin), am = fabsf(margin);
   const float *wl = a.w + (j * a.L + leaf) * a.M;
+  // the gradient arriving at this tree's output m: the upstream gradients of all linear outputs, weighted; then the
+  // tree's own backward with it (one reduction per leaf-weight element, not one per linear output)
   float acc = 0.0f;
-  for (int64_t o = 0; o < O; ++o) {
-    const float lw = __ldg(lin + o * a.T + j);
-    const float *gl = g + ((i * O + o) * a.K + k) * a.M;
-    const float sl = __fmul_rn(s, lw), al = __fmul_rn(am, lw);
-    for (int64_t m = 0; m < a.M; ++m) {
-      const float gm = __ldg(gl + m);
-      acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl, __ldg(wl + m)), gm));
-      if (gw != nullptr) atomicAdd(gw + (j * a.L + leaf) * a.M + m, __fmul_rn(al, gm));
-    }
+  for (int64_t m = 0; m < a.M; ++m) {
+    float through = 0.0f;
+    for (int64_t o = 0; o < O; ++o)
+      through = __fadd_rn(through, __fmul_rn(__ldg(lin + o * a.T + j), __ldg(g + ((i * O + o) * a.K + k) * a.M + m)));
+    acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s, __ldg(wl + m)), through));
+    if (gw != nullptr) atomicAdd(gw + (j * a.L + leaf) * a.M + m, __fmul_rn(am, through));
   }
   float *slot = data_grad_slot(a, gimg, gvec, i, a.ord[j * a.N + vertex], k);
   if (slot != nullptr) atomicAdd(slot, acc);
@@ -148,30 +149,46 @@ __global__ void __launch_bounds__(kBlock) linear_backward_kernel(FusionArgs a, P
 }
 
 // Gradient of the linear weights: gL[o,j] = sum over (i,k,m) of (|margin| * w[j,leaf,m]) * g[i,o,k,m].
-// One CTA per tree; for each output the CTA's threads sum their positions and reduce in a fixed
-// tree, so the result does not depend on scheduling.
+// CTA = (tree j, a slice of the positions): its threads walk the slice ONCE, keeping the sums of up to kLinearOutputs
+// linear outputs in registers, reduce them over the CTA and add the result to glin (cleared by the caller) with one
+// reduction per output.
+constexpr int kLinearOutputs = 16;
+
 __global__ void __launch_bounds__(kBlock) linear_weight_grad_kernel(FusionArgs a, PathRecords r, const float *__restrict__ g,
-                                                                    int64_t O, float *__restrict__ glin) {
-  __shared__ float partial[kBlock / 32];
+                                                                    int64_t O, float *glin) {
+  __shared__ float partial[kBlock / 32][kLinearOutputs];
   const int64_t j = blockIdx.x;
   const int64_t P = a.B * a.K;
-  for (int64_t o = 0; o < O; ++o) {
-    float sum = 0.0f;
-    for (int64_t p = threadIdx.x; p < P; p += kBlock) {
+  const int64_t per_slice = (P + gridDim.y - 1) / gridDim.y;
+  const int64_t first = (int64_t)blockIdx.y * per_slice, last = min(P, first + per_slice);
+  for (int64_t o0 = 0; o0 < O; o0 += kLinearOutputs) {
+    const int outputs = (int)min((int64_t)kLinearOutputs, O - o0);
+    float sum[kLinearOutputs];
+#pragma unroll
+    for (int u = 0; u < kLinearOutputs; ++u) sum[u] = 0.0f;
+    for (int64_t p = first + threadIdx.x; p < last; p += kBlock) {
       const int64_t i = p / a.K, k = p - i * a.K;
       const int64_t e = (i * a.T + j) * a.K + k;
       const float am = fabsf(r.margin[e]);
       const float *wl = a.w + (j * a.L + r.leaf[e]) * a.M;
-      const float *gl = g + ((i * O + o) * a.K + k) * a.M;
-      for (int64_t m = 0; m < a.M; ++m) sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(am, __ldg(wl + m)), __ldg(gl + m)));
+      for (int64_t m = 0; m < a.M; ++m) {
+        const float scaled = __fmul_rn(am, __ldg(wl + m));
+#pragma unroll
+        for (int u = 0; u < kLinearOutputs; ++u)
+          if (u < outputs) sum[u] = __fadd_rn(sum[u], __fmul_rn(scaled, __ldg(g + ((i * O + o0 + u) * a.K + k) * a.M + m)));
+      }
     }
-    for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, off);
-    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = sum;
+#pragma unroll
+    for (int u = 0; u < kLinearOutputs; ++u) {
+      float v = sum[u];
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+      if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5][u] = v;
+    }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if ((int)threadIdx.x < outputs) {
       float total = 0.0f;
-      for (int wi = 0; wi < kBlock / 32; ++wi) total += partial[wi];
-      glin[o * a.T + j] = total;
+      for (int wi = 0; wi < kBlock / 32; ++wi) total += partial[wi][threadIdx.x];
+      atomicAdd(glin + (o0 + threadIdx.x) * a.T + j, total);
     }
     __syncthreads();
   }
@@ -347,7 +364,11 @@ int ht_forest_linear_backward_f32(const ht_forest_problem *p, int64_t out_channe
     HT_CHECK_LAUNCH();
   }
   if (glin != nullptr) {
-    linear_weight_grad_kernel<<<(unsigned)a.T, kBlock, 0, pr.stream>>>(a, pr.records, g, out_channels, glin);
+    // enough CTAs to fill the machine: the positions of a tree are split when there are few trees
+    const int64_t positions = a.B * a.K;
+    const unsigned slices = (unsigned)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>((148 * 8 + a.T - 1) / a.T, 65535),
+                                                                             (positions + 4 * kBlock - 1) / (4 * kBlock)));
+    linear_weight_grad_kernel<<<dim3((unsigned)a.T, slices), kBlock, 0, pr.stream>>>(a, pr.records, g, out_channels, glin);
     HT_CHECK_LAUNCH();
   }
   return HT_OK;
