@@ -31,6 +31,9 @@ SYMBOLS = [
     "ht_conv_output_size", "ht_conv_workspace_bytes", "ht_conv_forward_f32", "ht_conv_backward_f32",
     "ht_contract", "ht_expand",
     "ht_trie_forward_f32", "ht_trie_backward_f32", "ht_forest_touched_f32", "ht_linear_tf32_stats_f32",
+    "ht_forest_linear_workspace_bytes_f64", "ht_forest_fusion_forward_f64", "ht_forest_fusion_backward_f64",
+    "ht_forest_linear_forward_f64", "ht_forest_linear_backward_f64", "ht_conv_forward_f64", "ht_conv_backward_f64",
+    "ht_trie_forward_f64", "ht_trie_backward_f64", "ht_forest_touched_f64",
     "ht_forest_normalised_workspace_bytes", "ht_forest_normalised_forward_f32", "ht_forest_normalised_backward_f32",
     "ht_batchnorm_input_grad_f32",
     "ht_init_medians_workspace_bytes", "ht_init_medians_f32", "ht_init_medians_f64", "ht_thresholds_f32", "ht_thresholds_f64",

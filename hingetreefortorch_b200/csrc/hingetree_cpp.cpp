@@ -70,8 +70,8 @@ void require_cuda(const torch::Tensor &t) {
 void require_float32(const torch::Tensor &t) {
   if (t.scalar_type() == torch::kFloat32) return;
   if (t.scalar_type() == torch::kFloat64)
-    bad_argument("Error: torch.float64 is supported by the plain tree / fern operators only (forward, backward, "
-                 "backward_deterministic, leafmap, marginmap, reachability); this operator takes torch.float32.");
+    bad_argument("Error: this operator takes torch.float32 only (the reference's operators take torch.float64 as well and so "
+                 "do their counterparts here; the additions to the reference's surface are single precision).");
   bad_argument("Error: Unsupported data type. Only torch.float32 and torch.float64 are supported.");
 }
 

@@ -12,6 +12,11 @@ namespace htx {
 
 namespace {
 
+void require_real(const torch::Tensor &t) {
+  if (t.scalar_type() != torch::kFloat32 && t.scalar_type() != torch::kFloat64)
+    bad_argument("Error: Unsupported data type. Only torch.float32 and torch.float64 are supported.");
+}
+
 // Shared validation of the fusion / fused-linear families (reference: hingetree_fusion.cpp:41-75,
 // 306-366; hingetree_fused_linear.cpp:75-100, 414-440, 769-860, 956-1050).
 struct FamilyCall {
@@ -39,7 +44,7 @@ struct FamilyCall {
     for (const torch::Tensor *t : reals)
       if (!t->is_contiguous()) bad_argument("Error: All tensors are expected to be contiguous.");
     if (!ord.is_contiguous()) bad_argument("Error: All tensors are expected to be contiguous.");
-    require_float32(data);
+    require_real(data);
     require_cuda(data);
     if (data.dim() < 2 || (vec != nullptr && vec->dim() != 2) || thr.dim() != 2 || ord.dim() != 2 || w.dim() < 2 ||
         (lin != nullptr && lin->dim() != 2) || (bias != nullptr && bias->dim() != 1))
@@ -81,7 +86,79 @@ struct FamilyCall {
   }
 };
 
-float *ptr_or_null(torch::Tensor &t) { return t.defined() ? t.data_ptr<float>() : nullptr; }
+template <typename Real>
+Real *ptr_or_null(torch::Tensor &t) {
+  return t.defined() ? t.data_ptr<Real>() : nullptr;
+}
+
+// f(float()) or f(double()) by the tensor's type (the operators of this file take both precisions).
+template <typename F>
+void dispatch_real(const torch::Tensor &t, F &&f) {
+  if (t.scalar_type() == torch::kFloat64)
+    f(double());
+  else
+    f(float());
+}
+
+// The C ABI's single and double precision entries under one name each.
+namespace abi {
+#define HT_BOTH(NAME, PARAMS_F, PARAMS_D, ARGS)                               \
+  inline int NAME PARAMS_F { return ht_##NAME##_f32 ARGS; }                   \
+  inline int NAME PARAMS_D { return ht_##NAME##_f64 ARGS; }
+#define HT_P const ht_forest_problem *p
+#define HT_TAIL void *ws, size_t wsb, uint32_t *st, ht_stream_t s
+HT_BOTH(forest_fusion_forward,
+        (HT_P, const float *img, const float *vec, int64_t cv, const float *thr, const int64_t *ord, const float *w, float *out, HT_TAIL),
+        (HT_P, const double *img, const double *vec, int64_t cv, const double *thr, const int64_t *ord, const double *w, double *out, HT_TAIL),
+        (p, img, vec, cv, thr, ord, w, out, ws, wsb, st, s))
+HT_BOTH(forest_fusion_backward,
+        (HT_P, const float *img, const float *vec, int64_t cv, const float *thr, const int64_t *ord, const float *w, const float *g,
+         float *gi, float *gv, float *gt, float *gw, HT_TAIL),
+        (HT_P, const double *img, const double *vec, int64_t cv, const double *thr, const int64_t *ord, const double *w, const double *g,
+         double *gi, double *gv, double *gt, double *gw, HT_TAIL),
+        (p, img, vec, cv, thr, ord, w, g, gi, gv, gt, gw, ws, wsb, st, s))
+HT_BOTH(forest_linear_forward,
+        (HT_P, int64_t o, const float *img, const float *vec, int64_t cv, const float *thr, const int64_t *ord, const float *w,
+         const float *lin, const float *bias, float *out, HT_TAIL),
+        (HT_P, int64_t o, const double *img, const double *vec, int64_t cv, const double *thr, const int64_t *ord, const double *w,
+         const double *lin, const double *bias, double *out, HT_TAIL),
+        (p, o, img, vec, cv, thr, ord, w, lin, bias, out, ws, wsb, st, s))
+HT_BOTH(forest_linear_backward,
+        (HT_P, int64_t o, const float *img, const float *vec, int64_t cv, const float *thr, const int64_t *ord, const float *w,
+         const float *lin, const float *g, float *gi, float *gv, float *gt, float *gw, float *gl, HT_TAIL),
+        (HT_P, int64_t o, const double *img, const double *vec, int64_t cv, const double *thr, const int64_t *ord, const double *w,
+         const double *lin, const double *g, double *gi, double *gv, double *gt, double *gw, double *gl, HT_TAIL),
+        (p, o, img, vec, cv, thr, ord, w, lin, g, gi, gv, gt, gw, gl, ws, wsb, st, s))
+HT_BOTH(forest_touched,
+        (HT_P, const float *x, const float *thr, const int64_t *ord, uint8_t *tx, uint8_t *tt, uint8_t *tw, HT_TAIL),
+        (HT_P, const double *x, const double *thr, const int64_t *ord, uint8_t *tx, uint8_t *tt, uint8_t *tw, HT_TAIL),
+        (p, x, thr, ord, tx, tt, tw, ws, wsb, st, s))
+HT_BOTH(forest_backward,
+        (HT_P, const float *x, const float *thr, const int64_t *ord, const float *w, const float *g, float *gx, float *gt, float *gw, HT_TAIL),
+        (HT_P, const double *x, const double *thr, const int64_t *ord, const double *w, const double *g, double *gx, double *gt, double *gw, HT_TAIL),
+        (p, x, thr, ord, w, g, gx, gt, gw, ws, wsb, st, s))
+HT_BOTH(trie_forward,
+        (HT_P, const float *x, const float *thr, const int64_t *ord, const float *w, float *out, HT_TAIL),
+        (HT_P, const double *x, const double *thr, const int64_t *ord, const double *w, double *out, HT_TAIL),
+        (p, x, thr, ord, w, out, ws, wsb, st, s))
+HT_BOTH(trie_backward,
+        (HT_P, const float *x, const float *thr, const int64_t *ord, const float *w, const float *g, float *gx, float *gt, float *gw, HT_TAIL),
+        (HT_P, const double *x, const double *thr, const int64_t *ord, const double *w, const double *g, double *gx, double *gt, double *gw, HT_TAIL),
+        (p, x, thr, ord, w, g, gx, gt, gw, ws, wsb, st, s))
+#undef HT_P
+#define HT_P const ht_conv_problem *p
+HT_BOTH(conv_forward,
+        (HT_P, const float *x, const float *thr, const int64_t *ord, const float *w, float *out, HT_TAIL),
+        (HT_P, const double *x, const double *thr, const int64_t *ord, const double *w, double *out, HT_TAIL),
+        (p, x, thr, ord, w, out, ws, wsb, st, s))
+HT_BOTH(conv_backward,
+        (HT_P, const float *x, const float *thr, const int64_t *ord, const float *w, const float *g, float *gx, float *gt, float *gw, HT_TAIL),
+        (HT_P, const double *x, const double *thr, const int64_t *ord, const double *w, const double *g, double *gx, double *gt, double *gw, HT_TAIL),
+        (p, x, thr, ord, w, g, gx, gt, gw, ws, wsb, st, s))
+#undef HT_P
+#undef HT_TAIL
+#undef HT_BOTH
+}  // namespace abi
 
 // ---- fusion --------------------------------------------------------------------------------
 
@@ -92,11 +169,14 @@ torch::Tensor fusion_forward(int kind, torch::Tensor img, torch::Tensor vec, tor
   torch::Tensor out = torch::empty(call.out_sizes, img.options());
   torch::Tensor ws = make_workspace(ht_forest_fusion_workspace_bytes(&call.problem), img);
   OrdinalGuard og(ord, call.problem.C + call.vec_channels);
-  raise_status(ht_forest_fusion_forward_f32(&call.problem, img.data_ptr<float>(), vec.data_ptr<float>(), call.vec_channels,
-                                            thr.data_ptr<float>(), ord.data_ptr<int64_t>(), w.data_ptr<float>(),
-                                            out.data_ptr<float>(), ws.data_ptr(), ws.numel(), og.word(),
-                                            current_stream(img)),
-               "fusion forward");
+  dispatch_real(img, [&](auto real) {
+    using Real = decltype(real);
+    raise_status(abi::forest_fusion_forward(&call.problem, img.data_ptr<Real>(), vec.data_ptr<Real>(), call.vec_channels,
+                                              thr.data_ptr<Real>(), ord.data_ptr<int64_t>(), w.data_ptr<Real>(),
+                                              out.data_ptr<Real>(), ws.data_ptr(), ws.numel(), og.word(),
+                                              current_stream(img)),
+                 "fusion forward");
+  });
   og.finish();
   return out;
 }
@@ -117,12 +197,15 @@ std::vector<torch::Tensor> fusion_backward(int kind, torch::Tensor img, bool nee
   if (need_w) grads[4] = torch::empty_like(w);
   torch::Tensor ws = make_workspace(ht_forest_fusion_workspace_bytes(&call.problem), img);
   OrdinalGuard og(ord, call.problem.C + call.vec_channels);
-  raise_status(ht_forest_fusion_backward_f32(&call.problem, img.data_ptr<float>(), vec.data_ptr<float>(),
-                                             call.vec_channels, thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
-                                             w.data_ptr<float>(), g.data_ptr<float>(), ptr_or_null(grads[0]),
-                                             ptr_or_null(grads[1]), ptr_or_null(grads[2]), ptr_or_null(grads[4]),
-                                             ws.data_ptr(), ws.numel(), og.word(), current_stream(img)),
-               "fusion backward");
+  dispatch_real(img, [&](auto real) {
+    using Real = decltype(real);
+    raise_status(abi::forest_fusion_backward(&call.problem, img.data_ptr<Real>(), vec.data_ptr<Real>(),
+                                               call.vec_channels, thr.data_ptr<Real>(), ord.data_ptr<int64_t>(),
+                                               w.data_ptr<Real>(), g.data_ptr<Real>(), ptr_or_null<Real>(grads[0]),
+                                               ptr_or_null<Real>(grads[1]), ptr_or_null<Real>(grads[2]), ptr_or_null<Real>(grads[4]),
+                                               ws.data_ptr(), ws.numel(), og.word(), current_stream(img)),
+                 "fusion backward");
+  });
   og.finish();
   return grads;
 }
@@ -134,14 +217,19 @@ torch::Tensor linear_forward(int kind, torch::Tensor data, const torch::Tensor *
   FamilyCall call(kind, data, vec, thr, ord, w, &lin, &bias, nullptr);
   c10::DeviceGuard guard(data.device());
   torch::Tensor out = torch::empty(call.out_sizes, data.options());
-  torch::Tensor ws = make_workspace(ht_forest_linear_workspace_bytes(&call.problem), data);
+  torch::Tensor ws = make_workspace(data.scalar_type() == torch::kFloat64 ? ht_forest_linear_workspace_bytes_f64(&call.problem)
+                                                                                  : ht_forest_linear_workspace_bytes(&call.problem),
+                                     data);
   OrdinalGuard og(ord, call.problem.C + call.vec_channels);
-  raise_status(ht_forest_linear_forward_f32(&call.problem, call.out_channels, data.data_ptr<float>(),
-                                            vec != nullptr ? vec->data_ptr<float>() : nullptr, call.vec_channels,
-                                            thr.data_ptr<float>(), ord.data_ptr<int64_t>(), w.data_ptr<float>(),
-                                            lin.data_ptr<float>(), bias.data_ptr<float>(), out.data_ptr<float>(),
-                                            ws.data_ptr(), ws.numel(), og.word(), current_stream(data)),
-               "fused linear forward");
+  dispatch_real(data, [&](auto real) {
+    using Real = decltype(real);
+    raise_status(abi::forest_linear_forward(&call.problem, call.out_channels, data.data_ptr<Real>(),
+                                              vec != nullptr ? vec->data_ptr<Real>() : nullptr, call.vec_channels,
+                                              thr.data_ptr<Real>(), ord.data_ptr<int64_t>(), w.data_ptr<Real>(),
+                                              lin.data_ptr<Real>(), bias.data_ptr<Real>(), out.data_ptr<Real>(),
+                                              ws.data_ptr(), ws.numel(), og.word(), current_stream(data)),
+                 "fused linear forward");
+  });
   og.finish();
   return out;
 }
@@ -164,15 +252,20 @@ std::vector<torch::Tensor> linear_backward(int kind, torch::Tensor data, bool ne
   if (need_w) gw = torch::empty_like(w);
   if (need_lin) glin = torch::empty_like(lin);
   if (gdata.defined() || gthr.defined() || gw.defined() || glin.defined()) {
-    torch::Tensor ws = make_workspace(ht_forest_linear_workspace_bytes(&call.problem), data);
+    torch::Tensor ws = make_workspace(data.scalar_type() == torch::kFloat64 ? ht_forest_linear_workspace_bytes_f64(&call.problem)
+                                                                                  : ht_forest_linear_workspace_bytes(&call.problem),
+                                     data);
     OrdinalGuard og(ord, call.problem.C + call.vec_channels);
-    raise_status(ht_forest_linear_backward_f32(&call.problem, call.out_channels, data.data_ptr<float>(),
-                                               fusion ? vec->data_ptr<float>() : nullptr, call.vec_channels,
-                                               thr.data_ptr<float>(), ord.data_ptr<int64_t>(), w.data_ptr<float>(),
-                                               lin.data_ptr<float>(), g.data_ptr<float>(), ptr_or_null(gdata),
-                                               ptr_or_null(gvec), ptr_or_null(gthr), ptr_or_null(gw), ptr_or_null(glin),
-                                               ws.data_ptr(), ws.numel(), og.word(), current_stream(data)),
-                 "fused linear backward");
+    dispatch_real(data, [&](auto real) {
+      using Real = decltype(real);
+      raise_status(abi::forest_linear_backward(&call.problem, call.out_channels, data.data_ptr<Real>(),
+                                                 fusion ? vec->data_ptr<Real>() : nullptr, call.vec_channels,
+                                                 thr.data_ptr<Real>(), ord.data_ptr<int64_t>(), w.data_ptr<Real>(),
+                                                 lin.data_ptr<Real>(), g.data_ptr<Real>(), ptr_or_null<Real>(gdata),
+                                                 ptr_or_null<Real>(gvec), ptr_or_null<Real>(gthr), ptr_or_null<Real>(gw), ptr_or_null<Real>(glin),
+                                                 ws.data_ptr(), ws.numel(), og.word(), current_stream(data)),
+                   "fused linear backward");
+    });
     og.finish();
   }
   if (need_bias) {  // sum over every dimension but the output channel, as the reference does with Tensor::sum
@@ -209,19 +302,22 @@ TouchedMasks touched_masks(const ht_forest_problem &problem, const torch::Tensor
   if (need_thr) masks.thr = torch::empty({thr.numel()}, bytes);
   if (need_w) masks.w = torch::empty({w.numel()}, bytes);
   torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&problem), x);
-  raise_status(ht_forest_touched_f32(&problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
-                                     need_x ? masks.x.data_ptr<uint8_t>() : nullptr,
-                                     need_thr ? masks.thr.data_ptr<uint8_t>() : nullptr,
-                                     need_w ? masks.w.data_ptr<uint8_t>() : nullptr, ws.data_ptr(), ws.numel(), nullptr,
-                                     current_stream(x)),
-               "touched masks");
+  dispatch_real(x, [&](auto real) {
+    using Real = decltype(real);
+    raise_status(abi::forest_touched(&problem, x.data_ptr<Real>(), thr.data_ptr<Real>(), ord.data_ptr<int64_t>(),
+                                       need_x ? masks.x.data_ptr<uint8_t>() : nullptr,
+                                       need_thr ? masks.thr.data_ptr<uint8_t>() : nullptr,
+                                       need_w ? masks.w.data_ptr<uint8_t>() : nullptr, ws.data_ptr(), ws.numel(), nullptr,
+                                       current_stream(x)),
+                 "touched masks");
+  });
   return masks;
 }
 
 std::vector<torch::Tensor> sparse_backward(int kind, torch::Tensor x, bool need_x, torch::Tensor thr, bool need_thr,
                                            torch::Tensor ord, bool need_ord, torch::Tensor w, bool need_w, torch::Tensor g) {
   if (need_ord) bad_runtime("Error: Gradient on inOrdinals is requested, but inOrdinals never has a gradient.");
-  ForestCall call(kind, x, thr, ord, w, &g);
+  ForestCall call(kind, x, thr, ord, w, &g, true);
   c10::DeviceGuard guard(x.device());
   std::vector<torch::Tensor> grads(4);
   if (!need_x && !need_thr && !need_w) return grads;
@@ -231,10 +327,13 @@ std::vector<torch::Tensor> sparse_backward(int kind, torch::Tensor x, bool need_
   if (need_w) gw = torch::empty_like(w);
   torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
   OrdinalGuard og(ord, call.problem.C);
-  raise_status(ht_forest_backward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
-                                      w.data_ptr<float>(), g.data_ptr<float>(), ptr_or_null(gx), ptr_or_null(gthr),
-                                      ptr_or_null(gw), ws.data_ptr(), ws.numel(), og.word(), current_stream(x)),
-               "sparse forest backward");
+  dispatch_real(x, [&](auto real) {
+    using Real = decltype(real);
+    raise_status(abi::forest_backward(&call.problem, x.data_ptr<Real>(), thr.data_ptr<Real>(), ord.data_ptr<int64_t>(),
+                                        w.data_ptr<Real>(), g.data_ptr<Real>(), ptr_or_null<Real>(gx), ptr_or_null<Real>(gthr),
+                                        ptr_or_null<Real>(gw), ws.data_ptr(), ws.numel(), og.word(), current_stream(x)),
+                 "sparse forest backward");
+  });
   og.finish();
   TouchedMasks masks = touched_masks(call.problem, x, need_x, thr, need_thr, ord, w, need_w);
   if (need_x) grads[0] = to_sparse(gx, masks.x);
@@ -285,7 +384,7 @@ struct TrieCall {
     if (!x.is_contiguous() || !thr.is_contiguous() || !ord.is_contiguous() || !w.is_contiguous() ||
         (g != nullptr && !g->is_contiguous()))
       bad_argument("Error: All tensors are expected to be contiguous.");
-    require_float32(x);
+    require_real(x);
     require_cuda(x);
     if (x.dim() < 2 || thr.dim() != 2 || ord.dim() != 2 || w.dim() < 2)
       bad_argument("Error: inData, inWeights must have at least 2 dimensions. inThresholds and inOrdinals must have 2 "
@@ -315,10 +414,13 @@ torch::Tensor trie_forward(torch::Tensor x, torch::Tensor thr, torch::Tensor ord
   torch::Tensor out = torch::empty(call.out_sizes, x.options());
   torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
   OrdinalGuard og(ord, call.problem.C);
-  raise_status(ht_trie_forward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
-                                   w.data_ptr<float>(), out.data_ptr<float>(), ws.data_ptr(), ws.numel(), og.word(),
-                                   current_stream(x)),
-               "trie forward");
+  dispatch_real(x, [&](auto real) {
+    using Real = decltype(real);
+    raise_status(abi::trie_forward(&call.problem, x.data_ptr<Real>(), thr.data_ptr<Real>(), ord.data_ptr<int64_t>(),
+                                     w.data_ptr<Real>(), out.data_ptr<Real>(), ws.data_ptr(), ws.numel(), og.word(),
+                                     current_stream(x)),
+                 "trie forward");
+  });
   og.finish();
   return out;
 }
@@ -335,11 +437,14 @@ std::vector<torch::Tensor> trie_backward(torch::Tensor x, bool need_x, torch::Te
   if (need_w) grads[3] = torch::empty_like(w);
   torch::Tensor ws = make_workspace(ht_forest_workspace_bytes(&call.problem), x);
   OrdinalGuard og(ord, call.problem.C);
-  raise_status(ht_trie_backward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
-                                    w.data_ptr<float>(), g.data_ptr<float>(), ptr_or_null(grads[0]),
-                                    ptr_or_null(grads[1]), ptr_or_null(grads[3]), ws.data_ptr(), ws.numel(), og.word(),
-                                    current_stream(x)),
-               "trie backward");
+  dispatch_real(x, [&](auto real) {
+    using Real = decltype(real);
+    raise_status(abi::trie_backward(&call.problem, x.data_ptr<Real>(), thr.data_ptr<Real>(), ord.data_ptr<int64_t>(),
+                                      w.data_ptr<Real>(), g.data_ptr<Real>(), ptr_or_null<Real>(grads[0]),
+                                      ptr_or_null<Real>(grads[1]), ptr_or_null<Real>(grads[3]), ws.data_ptr(), ws.numel(), og.word(),
+                                      current_stream(x)),
+                 "trie backward");
+  });
   og.finish();
   return grads;
 }
@@ -366,7 +471,7 @@ struct ConvCall {
     if (!x.is_contiguous() || !thr.is_contiguous() || !ord.is_contiguous() || !w.is_contiguous() ||
         (g != nullptr && !g->is_contiguous()))
       bad_argument("Error: All tensors are expected to be contiguous.");
-    require_float32(x);
+    require_real(x);
     require_cuda(x);
     if ((int)kernel.size() != dims || (int)stride.size() != dims || (int)padding.size() != dims ||
         (int)dilation.size() != dims) {
@@ -434,10 +539,13 @@ torch::Tensor conv_forward(int kind, int dims, torch::Tensor x, torch::Tensor th
   torch::Tensor out = torch::empty(call.out_sizes, x.options());
   torch::Tensor ws = make_workspace(ht_conv_workspace_bytes(&call.problem), x);
   OrdinalGuard og(ord, call.window_cells);
-  raise_status(ht_conv_forward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
-                                   w.data_ptr<float>(), out.data_ptr<float>(), ws.data_ptr(), ws.numel(), og.word(),
-                                   current_stream(x)),
-               "convolution forward");
+  dispatch_real(x, [&](auto real) {
+    using Real = decltype(real);
+    raise_status(abi::conv_forward(&call.problem, x.data_ptr<Real>(), thr.data_ptr<Real>(), ord.data_ptr<int64_t>(),
+                                     w.data_ptr<Real>(), out.data_ptr<Real>(), ws.data_ptr(), ws.numel(), og.word(),
+                                     current_stream(x)),
+                 "convolution forward");
+  });
   og.finish();
   return out;
 }
@@ -456,11 +564,14 @@ std::vector<torch::Tensor> conv_backward(int kind, int dims, torch::Tensor x, bo
   if (need_w) grads[3] = torch::empty_like(w);
   torch::Tensor ws = make_workspace(ht_conv_workspace_bytes(&call.problem), x);
   OrdinalGuard og(ord, call.window_cells);
-  raise_status(ht_conv_backward_f32(&call.problem, x.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
-                                    w.data_ptr<float>(), g.data_ptr<float>(), ptr_or_null(grads[0]),
-                                    ptr_or_null(grads[1]), ptr_or_null(grads[3]), ws.data_ptr(), ws.numel(), og.word(),
-                                    current_stream(x)),
-               "convolution backward");
+  dispatch_real(x, [&](auto real) {
+    using Real = decltype(real);
+    raise_status(abi::conv_backward(&call.problem, x.data_ptr<Real>(), thr.data_ptr<Real>(), ord.data_ptr<int64_t>(),
+                                      w.data_ptr<Real>(), g.data_ptr<Real>(), ptr_or_null<Real>(grads[0]),
+                                      ptr_or_null<Real>(grads[1]), ptr_or_null<Real>(grads[3]), ws.data_ptr(), ws.numel(), og.word(),
+                                      current_stream(x)),
+                 "convolution backward");
+  });
   og.finish();
   return grads;
 }

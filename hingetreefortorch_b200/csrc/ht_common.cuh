@@ -93,16 +93,18 @@ using PlainFeature = PlainFeatureOf<float>;
 
 // Image + per-sample vector lookup: features below the image channel count come from the
 // image, the rest from the vector (reference semantics: HingeTreeCommon.cuh:81-107, 156-184).
-struct FusionFeature {
-  typedef float value_type;
-  const float *__restrict__ img;
+template <typename Real>
+struct FusionFeatureOf {
+  typedef Real value_type;
+  const Real *__restrict__ img;
   int64_t stride;
-  const float *__restrict__ vec;
+  const Real *__restrict__ vec;
   int img_channels;
-  __device__ __forceinline__ float operator()(int c) const {
+  __device__ __forceinline__ Real operator()(int c) const {
     return c < img_channels ? __ldg(img + (int64_t)c * stride) : __ldg(vec + (c - img_channels));
   }
 };
+using FusionFeature = FusionFeatureOf<float>;
 
 // The traversal.  One plain fp32 subtract per level; `m > 0` sends NaN and 0 to the left;
 // strict `<` keeps the shallowest minimum.  Level 0 seeds the minimum, which is what the

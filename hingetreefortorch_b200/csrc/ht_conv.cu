@@ -20,19 +20,24 @@ namespace {
 constexpr int kBlock = 256;
 constexpr int kMaxCells = 2048;  // window cells whose offsets are tabulated in shared memory
 
-struct ConvArgs {
-  const float *x;
-  const float *thr;
-  const int32_t *ord;
-  const float *w;
+struct ConvShape {
   int64_t B, Ci, Co, M, N, L;
   int64_t in_count, out_count;
   int dims, depth, cells;
   int size[3], osize[3], kernel[3], stride[3], pad[3], dil[3];
 };
 
+template <typename Real>
+struct ConvArgsOf : ConvShape {
+  const Real *x;
+  const Real *thr;
+  const int32_t *ord;
+  const Real *w;
+};
+using ConvArgs = ConvArgsOf<float>;
+
 // Offsets (in elements along z, y, x; dilation applied) of every window cell, 10 bits each.
-__device__ __forceinline__ void fill_cell_table(const ConvArgs &a, uint32_t *table) {
+__device__ __forceinline__ void fill_cell_table(const ConvShape &a, uint32_t *table) {
   for (int q = threadIdx.x; q < a.cells; q += blockDim.x) {
     int rest = q;
     uint32_t packed = 0;
@@ -46,7 +51,7 @@ __device__ __forceinline__ void fill_cell_table(const ConvArgs &a, uint32_t *tab
 }
 
 // Image coordinates of the first window cell of output position p (may be negative: padding).
-__device__ __forceinline__ void window_origin(const ConvArgs &a, int64_t p, int (&origin)[3]) {
+__device__ __forceinline__ void window_origin(const ConvShape &a, int64_t p, int (&origin)[3]) {
 #pragma unroll
   for (int d = 2; d >= 0; --d) {
     if (d < a.dims) {
@@ -60,7 +65,7 @@ __device__ __forceinline__ void window_origin(const ConvArgs &a, int64_t p, int 
 }
 
 // Flat index of window cell `packed` inside one channel image, or -1 when it lies in the padding.
-__device__ __forceinline__ int cell_index(const ConvArgs &a, const int (&origin)[3], uint32_t packed) {
+__device__ __forceinline__ int cell_index(const ConvShape &a, const int (&origin)[3], uint32_t packed) {
   int index = 0;
   bool inside = true;
 #pragma unroll
@@ -74,20 +79,21 @@ __device__ __forceinline__ int cell_index(const ConvArgs &a, const int (&origin)
   return inside ? index : -1;
 }
 
-struct WindowFeature {
-  typedef float value_type;
-  const ConvArgs &a;
-  const float *chan;
+template <typename Real>
+struct WindowFeatureOf {
+  typedef Real value_type;
+  const ConvShape &a;
+  const Real *chan;
   const int (&origin)[3];
   const uint32_t *table;
-  __device__ __forceinline__ float operator()(int q) const {
+  __device__ __forceinline__ Real operator()(int q) const {
     const int idx = cell_index(a, origin, table[q]);
-    return idx < 0 ? 0.0f : __ldg(chan + idx);
+    return idx < 0 ? (Real)0 : __ldg(chan + idx);
   }
 };
 
-template <int KIND>
-__global__ void __launch_bounds__(kBlock) conv_forward_kernel(ConvArgs a, float *__restrict__ out) {
+template <int KIND, typename Real>
+__global__ void __launch_bounds__(kBlock) conv_forward_kernel(ConvArgsOf<Real> a, Real *__restrict__ out) {
   __shared__ uint32_t table[kMaxCells];
   fill_cell_table(a, table);
   __syncthreads();
@@ -98,23 +104,23 @@ __global__ void __launch_bounds__(kBlock) conv_forward_kernel(ConvArgs a, float 
   const int64_t i = e / (a.out_count * a.Co);
   int origin[3];
   window_origin(a, p, origin);
-  float *o = out + e * a.M;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  Real *o = out + e * a.M;
+  Real acc[8] = {};
   const bool in_registers = a.M <= 8;
   if (!in_registers)
-    for (int64_t m = 0; m < a.M; ++m) o[m] = 0.0f;
+    for (int64_t m = 0; m < a.M; ++m) o[m] = (Real)0;
   for (int64_t c = 0; c < a.Ci; ++c) {
     const int64_t tree = j * a.Ci + c;
-    const WindowFeature feat{a, a.x + (i * a.Ci + c) * a.in_count, origin, table};
-    const Path path = traverse<KIND>(feat, a.thr + tree * a.N, a.ord + tree * a.N, a.depth);
-    const float am = fabsf(path.margin);
-    const float *wl = a.w + (tree * a.L + path.key) * a.M;
+    const WindowFeatureOf<Real> feat{a, a.x + (i * a.Ci + c) * a.in_count, origin, table};
+    const PathOf<Real> path = traverse<KIND>(feat, a.thr + tree * a.N, a.ord + tree * a.N, a.depth);
+    const Real am = abs_of(path.margin);
+    const Real *wl = a.w + (tree * a.L + path.key) * a.M;
     if (in_registers) {
 #pragma unroll
       for (int m = 0; m < 8; ++m)
-        if (m < a.M) acc[m] = __fadd_rn(acc[m], __fmul_rn(__ldg(wl + m), am));
+        if (m < a.M) acc[m] = add_rn(acc[m], mul_rn(__ldg(wl + m), am));
     } else {
-      for (int64_t m = 0; m < a.M; ++m) o[m] = __fadd_rn(o[m], __fmul_rn(__ldg(wl + m), am));
+      for (int64_t m = 0; m < a.M; ++m) o[m] = add_rn(o[m], mul_rn(__ldg(wl + m), am));
     }
   }
   if (in_registers) {
@@ -125,9 +131,9 @@ __global__ void __launch_bounds__(kBlock) conv_forward_kernel(ConvArgs a, float 
 }
 
 // One thread per (i, j, p) walking the input channels; the three gradients are scattered with atomics.
-template <int KIND>
-__global__ void __launch_bounds__(kBlock) conv_backward_kernel(ConvArgs a, const float *__restrict__ g, float *gx,
-                                                               float *gthr, float *gw) {
+template <int KIND, typename Real>
+__global__ void __launch_bounds__(kBlock) conv_backward_kernel(ConvArgsOf<Real> a, const Real *__restrict__ g, Real *gx,
+                                                               Real *gthr, Real *gw) {
   __shared__ uint32_t table[kMaxCells];
   fill_cell_table(a, table);
   __syncthreads();
@@ -138,18 +144,18 @@ __global__ void __launch_bounds__(kBlock) conv_backward_kernel(ConvArgs a, const
   const int64_t i = e / (a.out_count * a.Co);
   int origin[3];
   window_origin(a, p, origin);
-  const float *gl = g + e * a.M;
+  const Real *gl = g + e * a.M;
   for (int64_t c = 0; c < a.Ci; ++c) {
     const int64_t tree = j * a.Ci + c;
-    const WindowFeature feat{a, a.x + (i * a.Ci + c) * a.in_count, origin, table};
-    const Path path = traverse<KIND>(feat, a.thr + tree * a.N, a.ord + tree * a.N, a.depth);
-    const float s = sign_of(path.margin), am = fabsf(path.margin);
-    const float *wl = a.w + (tree * a.L + path.key) * a.M;
-    float acc = 0.0f;
+    const WindowFeatureOf<Real> feat{a, a.x + (i * a.Ci + c) * a.in_count, origin, table};
+    const PathOf<Real> path = traverse<KIND>(feat, a.thr + tree * a.N, a.ord + tree * a.N, a.depth);
+    const Real s = sign_of(path.margin), am = abs_of(path.margin);
+    const Real *wl = a.w + (tree * a.L + path.key) * a.M;
+    Real acc = (Real)0;
     for (int64_t m = 0; m < a.M; ++m) {
-      const float gm = __ldg(gl + m);
-      acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s, __ldg(wl + m)), gm));
-      if (gw != nullptr) atomicAdd(gw + (tree * a.L + path.key) * a.M + m, __fmul_rn(am, gm));
+      const Real gm = __ldg(gl + m);
+      acc = add_rn(acc, mul_rn(mul_rn(s, __ldg(wl + m)), gm));
+      if (gw != nullptr) atomicAdd(gw + (tree * a.L + path.key) * a.M + m, mul_rn(am, gm));
     }
     if (gx != nullptr) {
       const int idx = cell_index(a, origin, table[a.ord[tree * a.N + path.vertex]]);
@@ -319,7 +325,7 @@ __global__ void __launch_bounds__(kBlock) expand32_kernel(PatchArgs32 a, const W
 
 inline unsigned blocks_for(int64_t n) { return (unsigned)((n + kBlock - 1) / kBlock); }
 
-int check_conv(const ht_conv_problem *p, ConvArgs &a) {
+int check_conv(const ht_conv_problem *p, ConvShape &a) {
   if (p == nullptr) return HT_ERR_INVALID_ARGUMENT;
   if (p->kind != TREE && p->kind != FERN) return HT_ERR_INVALID_ARGUMENT;
   if (p->depth < 1 || p->depth > 31) return HT_ERR_DEPTH;
@@ -359,10 +365,10 @@ int check_conv(const ht_conv_problem *p, ConvArgs &a) {
   return HT_OK;
 }
 
-size_t conv_ordinal_bytes(const ConvArgs &a) { return align_up((size_t)(a.Co * a.Ci * a.N) * sizeof(int32_t), 256); }
+size_t conv_ordinal_bytes(const ConvShape &a) { return align_up((size_t)(a.Co * a.Ci * a.N) * sizeof(int32_t), 256); }
 
 // The problem as the shared-memory tile kernels see it (1-D and 2-D, one output per leaf).
-bool tile_problem(const ht_conv_problem *p, const ConvArgs &a, ConvTileProblem &t) {
+bool tile_problem(const ht_conv_problem *p, const ConvShape &a, ConvTileProblem &t) {
   if (p->dims > 2 || a.M != 1) return false;
   const int row = p->dims == 2 ? 0 : -1, col = p->dims - 1;  // a 1-D signal is one image row
   t.kind = p->kind;
@@ -385,14 +391,15 @@ bool tile_problem(const ht_conv_problem *p, const ConvArgs &a, ConvTileProblem &
   return true;
 }
 
-size_t conv_records_bytes(const ht_conv_problem *p, const ConvArgs &a) {
+size_t conv_records_bytes(const ht_conv_problem *p, const ConvShape &a) {
   ConvTileProblem t;
   if (!tile_problem(p, a, t)) return 0;
   return std::max(conv_tiled_workspace_bytes(t), conv_backward_tiled_workspace_bytes(t));
 }
 
-int prepare_conv(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
-                 void *workspace, size_t workspace_bytes, uint32_t *status_word, cudaStream_t stream, ConvArgs &a) {
+template <typename Real>
+int prepare_conv(const ht_conv_problem *p, const Real *x, const Real *thr, const int64_t *ord, const Real *w,
+                 void *workspace, size_t workspace_bytes, uint32_t *status_word, cudaStream_t stream, ConvArgsOf<Real> &a) {
   const int rc = check_conv(p, a);
   if (rc != HT_OK) return rc;
   const int64_t decisions = a.Co * a.Ci * a.N;
@@ -478,6 +485,72 @@ int run_patches(bool contract, int dims, int elem_bytes, const void *in, void *o
   }
 }
 
+// Forward / backward for either precision; the shared-memory tile kernels are single precision only.
+template <typename Real>
+int conv_forward(const ht_conv_problem *p, const Real *x, const Real *thr, const int64_t *ord, const Real *w, Real *out,
+                 void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream) {
+  ConvArgsOf<Real> a;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int rc = prepare_conv<Real>(p, x, thr, ord, w, workspace, workspace_bytes, status_word, s, a);
+  if (rc != HT_OK) return rc;
+  const int64_t threads = a.B * a.Co * a.out_count;
+  if (threads * a.M == 0) return HT_OK;
+  if (out == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  if constexpr (std::is_same<Real, float>::value) {
+    ConvTileProblem t;
+    if (tile_problem(p, a, t)) {
+      const size_t records = conv_tiled_workspace_bytes(t);
+      if (records != 0 && workspace_bytes >= conv_ordinal_bytes(a) + records + 256) {
+        const int tiled = conv_forward_tiled(t, x, thr, a.ord, w, out,
+                                             static_cast<unsigned char *>(workspace) + conv_ordinal_bytes(a), status_word, s);
+        if (tiled != HT_ERR_UNSUPPORTED) return tiled;
+      }
+    }
+  }
+  if (p->kind == TREE)
+    conv_forward_kernel<TREE, Real><<<blocks_for(threads), kBlock, 0, s>>>(a, out);
+  else
+    conv_forward_kernel<FERN, Real><<<blocks_for(threads), kBlock, 0, s>>>(a, out);
+  HT_CHECK_LAUNCH();
+  return HT_OK;
+}
+
+template <typename Real>
+int conv_backward(const ht_conv_problem *p, const Real *x, const Real *thr, const int64_t *ord, const Real *w, const Real *g,
+                  Real *gx, Real *gthr, Real *gw, void *workspace, size_t workspace_bytes, uint32_t *status_word,
+                  ht_stream_t stream) {
+  ConvArgsOf<Real> a;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int rc = prepare_conv<Real>(p, x, thr, ord, w, workspace, workspace_bytes, status_word, s, a);
+  if (rc != HT_OK) return rc;
+  if (gx != nullptr && a.B * a.Ci * a.in_count > 0)
+    HT_CUDA_TRY(cudaMemsetAsync(gx, 0, sizeof(Real) * (size_t)(a.B * a.Ci * a.in_count), s));
+  if (gthr != nullptr && a.Co * a.Ci * a.N > 0)
+    HT_CUDA_TRY(cudaMemsetAsync(gthr, 0, sizeof(Real) * (size_t)(a.Co * a.Ci * a.N), s));
+  if (gw != nullptr && a.Co * a.Ci * a.L * a.M > 0)
+    HT_CUDA_TRY(cudaMemsetAsync(gw, 0, sizeof(Real) * (size_t)(a.Co * a.Ci * a.L * a.M), s));
+  const int64_t threads = a.B * a.Co * a.out_count;
+  if (threads * a.M == 0 || (gx == nullptr && gthr == nullptr && gw == nullptr)) return HT_OK;
+  if (g == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  if constexpr (std::is_same<Real, float>::value) {
+    ConvTileProblem t;
+    if (tile_problem(p, a, t)) {
+      const size_t records = conv_backward_tiled_workspace_bytes(t);
+      if (records != 0 && workspace_bytes >= conv_ordinal_bytes(a) + records + 256) {
+        const int tiled = conv_backward_tiled(t, x, thr, a.ord, w, g, gx, gthr, gw,
+                                              static_cast<unsigned char *>(workspace) + conv_ordinal_bytes(a), status_word, s);
+        if (tiled != HT_ERR_UNSUPPORTED) return tiled;
+      }
+    }
+  }
+  if (p->kind == TREE)
+    conv_backward_kernel<TREE, Real><<<blocks_for(threads), kBlock, 0, s>>>(a, g, gx, gthr, gw);
+  else
+    conv_backward_kernel<FERN, Real><<<blocks_for(threads), kBlock, 0, s>>>(a, g, gx, gthr, gw);
+  HT_CHECK_LAUNCH();
+  return HT_OK;
+}
+
 }  // namespace
 }  // namespace ht
 
@@ -502,61 +575,22 @@ size_t ht_conv_workspace_bytes(const ht_conv_problem *p) {
 
 int ht_conv_forward_f32(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
                         float *out, void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream) {
-  ConvArgs a;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int rc = prepare_conv(p, x, thr, ord, w, workspace, workspace_bytes, status_word, s, a);
-  if (rc != HT_OK) return rc;
-  const int64_t threads = a.B * a.Co * a.out_count;
-  if (threads * a.M == 0) return HT_OK;
-  if (out == nullptr) return HT_ERR_INVALID_ARGUMENT;
-  ConvTileProblem t;
-  if (tile_problem(p, a, t)) {
-    const size_t records = conv_tiled_workspace_bytes(t);
-    if (records != 0 && workspace_bytes >= conv_ordinal_bytes(a) + records + 256) {
-      const int tiled = conv_forward_tiled(t, x, thr, a.ord, w, out, static_cast<unsigned char *>(workspace) + conv_ordinal_bytes(a),
-                                           status_word, s);
-      if (tiled != HT_ERR_UNSUPPORTED) return tiled;
-    }
-  }
-  if (p->kind == TREE)
-    conv_forward_kernel<TREE><<<blocks_for(threads), kBlock, 0, s>>>(a, out);
-  else
-    conv_forward_kernel<FERN><<<blocks_for(threads), kBlock, 0, s>>>(a, out);
-  HT_CHECK_LAUNCH();
-  return HT_OK;
+  return conv_forward<float>(p, x, thr, ord, w, out, workspace, workspace_bytes, status_word, stream);
+}
+int ht_conv_forward_f64(const ht_conv_problem *p, const double *x, const double *thr, const int64_t *ord, const double *w,
+                        double *out, void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream) {
+  return conv_forward<double>(p, x, thr, ord, w, out, workspace, workspace_bytes, status_word, stream);
 }
 
 int ht_conv_backward_f32(const ht_conv_problem *p, const float *x, const float *thr, const int64_t *ord, const float *w,
                          const float *g, float *gx, float *gthr, float *gw, void *workspace, size_t workspace_bytes,
                          uint32_t *status_word, ht_stream_t stream) {
-  ConvArgs a;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int rc = prepare_conv(p, x, thr, ord, w, workspace, workspace_bytes, status_word, s, a);
-  if (rc != HT_OK) return rc;
-  if (gx != nullptr && a.B * a.Ci * a.in_count > 0)
-    HT_CUDA_TRY(cudaMemsetAsync(gx, 0, sizeof(float) * (size_t)(a.B * a.Ci * a.in_count), s));
-  if (gthr != nullptr && a.Co * a.Ci * a.N > 0)
-    HT_CUDA_TRY(cudaMemsetAsync(gthr, 0, sizeof(float) * (size_t)(a.Co * a.Ci * a.N), s));
-  if (gw != nullptr && a.Co * a.Ci * a.L * a.M > 0)
-    HT_CUDA_TRY(cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)(a.Co * a.Ci * a.L * a.M), s));
-  const int64_t threads = a.B * a.Co * a.out_count;
-  if (threads * a.M == 0 || (gx == nullptr && gthr == nullptr && gw == nullptr)) return HT_OK;
-  if (g == nullptr) return HT_ERR_INVALID_ARGUMENT;
-  ConvTileProblem t;
-  if (tile_problem(p, a, t)) {
-    const size_t records = conv_backward_tiled_workspace_bytes(t);
-    if (records != 0 && workspace_bytes >= conv_ordinal_bytes(a) + records + 256) {
-      const int tiled = conv_backward_tiled(t, x, thr, a.ord, w, g, gx, gthr, gw,
-                                            static_cast<unsigned char *>(workspace) + conv_ordinal_bytes(a), status_word, s);
-      if (tiled != HT_ERR_UNSUPPORTED) return tiled;
-    }
-  }
-  if (p->kind == TREE)
-    conv_backward_kernel<TREE><<<blocks_for(threads), kBlock, 0, s>>>(a, g, gx, gthr, gw);
-  else
-    conv_backward_kernel<FERN><<<blocks_for(threads), kBlock, 0, s>>>(a, g, gx, gthr, gw);
-  HT_CHECK_LAUNCH();
-  return HT_OK;
+  return conv_backward<float>(p, x, thr, ord, w, g, gx, gthr, gw, workspace, workspace_bytes, status_word, stream);
+}
+int ht_conv_backward_f64(const ht_conv_problem *p, const double *x, const double *thr, const int64_t *ord, const double *w,
+                         const double *g, double *gx, double *gthr, double *gw, void *workspace, size_t workspace_bytes,
+                         uint32_t *status_word, ht_stream_t stream) {
+  return conv_backward<double>(p, x, thr, ord, w, g, gx, gthr, gw, workspace, workspace_bytes, status_word, stream);
 }
 
 int ht_contract(int dims, int elem_bytes, const void *image, void *patches, int64_t batch_times_channels,

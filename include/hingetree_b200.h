@@ -291,6 +291,43 @@ int ht_contract(int dims, int elem_bytes, const void *image, void *patches, int6
 int ht_expand(int dims, int elem_bytes, const void *patches, void *image, int64_t batch_times_channels,
               const int64_t *osize, const int64_t *window, const int64_t *padding, ht_stream_t stream);
 
+/* ---- double precision forms of the other operator families -------------------------------------------
+ * The reference instantiates every operator for float and double (hingetree.cpp:666-689 and the like in
+ * hingetree_conv.cpp, hingetree_fused_linear.cpp, hingetree_fusion.cpp, hingetree_sparse.cpp, hingetrie.cpp).  Same
+ * arguments and semantics as the _f32 entries above with double in place of float; the any-shape kernels are used
+ * (the shared-memory tile kernels are single precision).  ht_forest_linear_workspace_bytes_f64 sizes the workspace of
+ * the two linear entries; the other workspaces are those of the _f32 forms. */
+size_t ht_forest_linear_workspace_bytes_f64(const ht_forest_problem *p);
+int ht_forest_fusion_forward_f64(const ht_forest_problem *p, const double *img, const double *vec, int64_t vec_channels,
+                                 const double *thr, const int64_t *ord, const double *w, double *out, void *workspace,
+                                 size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+int ht_forest_fusion_backward_f64(const ht_forest_problem *p, const double *img, const double *vec, int64_t vec_channels,
+                                  const double *thr, const int64_t *ord, const double *w, const double *g, double *gimg,
+                                  double *gvec, double *gthr, double *gw, void *workspace, size_t workspace_bytes,
+                                  uint32_t *status_word, ht_stream_t stream);
+int ht_forest_linear_forward_f64(const ht_forest_problem *p, int64_t out_channels, const double *img, const double *vec,
+                                 int64_t vec_channels, const double *thr, const int64_t *ord, const double *w,
+                                 const double *lin, const double *bias, double *out, void *workspace, size_t workspace_bytes,
+                                 uint32_t *status_word, ht_stream_t stream);
+int ht_forest_linear_backward_f64(const ht_forest_problem *p, int64_t out_channels, const double *img, const double *vec,
+                                  int64_t vec_channels, const double *thr, const int64_t *ord, const double *w,
+                                  const double *lin, const double *g, double *gimg, double *gvec, double *gthr, double *gw,
+                                  double *glin, void *workspace, size_t workspace_bytes, uint32_t *status_word,
+                                  ht_stream_t stream);
+int ht_conv_forward_f64(const ht_conv_problem *p, const double *x, const double *thr, const int64_t *ord, const double *w,
+                        double *out, void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+int ht_conv_backward_f64(const ht_conv_problem *p, const double *x, const double *thr, const int64_t *ord, const double *w,
+                         const double *g, double *gx, double *gthr, double *gw, void *workspace, size_t workspace_bytes,
+                         uint32_t *status_word, ht_stream_t stream);
+int ht_trie_forward_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord, const double *w,
+                        double *out, void *workspace, size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+int ht_trie_backward_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord, const double *w,
+                         const double *g, double *gx, double *gthr, double *gw, void *workspace, size_t workspace_bytes,
+                         uint32_t *status_word, ht_stream_t stream);
+int ht_forest_touched_f64(const ht_forest_problem *p, const double *x, const double *thr, const int64_t *ord,
+                          uint8_t *touched_x, uint8_t *touched_thr, uint8_t *touched_w, void *workspace,
+                          size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+
 /* ---- forest behind a batch normalisation that is not materialised ---------------------------------------
  * The reference's sequential-initialisation pipeline is torch.nn.Linear -> torch.nn.BatchNorm1d(affine=False) ->
  * RandomHingeForest (README.md:110-129).  These entries are the forest of that pipeline reading the RAW

@@ -155,37 +155,38 @@ def double_vectors(ref):
     print("wrote forest64.npz with", len(out), "arrays")
 
 
-def families(ref):
-    """Fused linear, image+vector fusion, convolution and contract/expand vectors -> families.npz."""
+def families(ref, dtype=torch.float32, filename="families.npz"):
+    """Fused linear, image+vector fusion, convolution, contract/expand and trie vectors -> families.npz; with
+    dtype=torch.float64 the same cases (the same values, widened) in double precision -> families64.npz."""
     out = {}
     for idx, (kind, B, C, inner, T, depth, extra, O, Cv) in enumerate(LINEAR_CASES):
         gen = torch.Generator().manual_seed(500 + idx)
         N = decisions(kind, depth)
-        x = torch.randn((B, C) + inner, generator=gen)
-        thr = torch.rand((T, N), generator=gen) * 6 - 3
+        x = torch.randn((B, C) + inner, generator=gen).to(dtype)
+        thr = (torch.rand((T, N), generator=gen) * 6 - 3).to(dtype)
         ord_ = torch.randint(0, C + Cv, (T, N), generator=gen)
-        w = torch.randn((T, 2 ** depth) + extra, generator=gen)
-        lin = torch.randn((O, T), generator=gen)
-        bias = torch.randn(O, generator=gen)
+        w = torch.randn((T, 2 ** depth) + extra, generator=gen).to(dtype)
+        lin = torch.randn((O, T), generator=gen).to(dtype)
+        bias = torch.randn(O, generator=gen).to(dtype)
         p = "linear%02d_" % idx
         out[p + "kind"] = np.array(kind)
         tensors = [("x", x), ("thr", thr), ("ord", ord_), ("w", w), ("lin", lin), ("bias", bias)]
         if Cv:
-            vec = torch.randn((B, Cv), generator=gen)
+            vec = torch.randn((B, Cv), generator=gen).to(dtype)
             tensors.append(("vec", vec))
             f = getattr(ref, kind + "_fusion_fused_linear_forward")(x, vec, thr, ord_, w, lin, bias)
-            g = torch.randn(f.shape, generator=gen)
+            g = torch.randn(f.shape, generator=gen).to(dtype)
             grads = getattr(ref, kind + "_fusion_fused_linear_backward")(x, True, vec, True, thr, True, ord_, False, w,
                                                                          True, lin, True, bias, True, g)
             names = ["gx", "gvec", "gthr", None, "gw", "glin", "gbias"]
             ff = getattr(ref, kind + "_fusion_forward")(x, vec, thr, ord_, w)
-            g2 = torch.randn(ff.shape, generator=gen)
+            g2 = torch.randn(ff.shape, generator=gen).to(dtype)
             fg = getattr(ref, kind + "_fusion_backward")(x, True, vec, True, thr, True, ord_, False, w, True, g2)
             tensors += [("fusion_out", ff), ("fusion_g", g2), ("fusion_gx", fg[0]), ("fusion_gvec", fg[1]),
                         ("fusion_gthr", fg[2]), ("fusion_gw", fg[4])]
         else:
             f = getattr(ref, kind + "_fused_linear_forward")(x, thr, ord_, w, lin, bias)
-            g = torch.randn(f.shape, generator=gen)
+            g = torch.randn(f.shape, generator=gen).to(dtype)
             grads = getattr(ref, kind + "_fused_linear_backward")(x, True, thr, True, ord_, False, w, True, lin, True,
                                                                   bias, True, g)
             names = ["gx", "gthr", None, "gw", "glin", "gbias"]
@@ -198,13 +199,13 @@ def families(ref):
         for cidx, (dims, xs, Co, depth, extra, kernel, stride, padding, dilation) in enumerate(CONV_CASES):
             gen = torch.Generator().manual_seed(700 + 10 * kidx + cidx)
             Ci, N, cells = xs[1], decisions(kind, depth), int(np.prod(kernel))
-            x = torch.randn(xs, generator=gen)
-            thr = torch.rand((Co, Ci, N), generator=gen) * 2 - 1
+            x = torch.randn(xs, generator=gen).to(dtype)
+            thr = (torch.rand((Co, Ci, N), generator=gen) * 2 - 1).to(dtype)
             ord_ = torch.randint(0, cells, (Co, Ci, N), generator=gen)
-            w = torch.randn((Co, Ci, 2 ** depth) + extra, generator=gen)
+            w = torch.randn((Co, Ci, 2 ** depth) + extra, generator=gen).to(dtype)
             geometry = [list(kernel), list(stride), list(padding), list(dilation)]
             f = getattr(ref, "%s_conv%dd_forward" % (kind, dims))(x, thr, ord_, w, *geometry)
-            g = torch.randn(f.shape, generator=gen)
+            g = torch.randn(f.shape, generator=gen).to(dtype)
             gx, gthr, _, gw = getattr(ref, "%s_conv%dd_backward" % (kind, dims))(x, True, thr, True, ord_, False, w, True,
                                                                                g, *geometry)
             p = "conv%02d_" % (len(CONV_CASES) * kidx + cidx)
@@ -227,20 +228,20 @@ def families(ref):
     for idx, (B, C, inner, T, depth, extra) in enumerate([(9, 7, (), 5, 3, ()), (4, 6, (3,), 3, 4, (2,))]):
         gen = torch.Generator().manual_seed(950 + idx)
         N = 2 ** depth - 1
-        x = torch.randn((B, C) + inner, generator=gen)
-        thr = torch.rand((T, N), generator=gen) * 4 - 2
+        x = torch.randn((B, C) + inner, generator=gen).to(dtype)
+        thr = (torch.rand((T, N), generator=gen) * 4 - 2).to(dtype)
         ord_ = torch.randint(0, C, (T, N), generator=gen)
-        w = torch.randn((T, N) + extra, generator=gen)
+        w = torch.randn((T, N) + extra, generator=gen).to(dtype)
         f = ref.trie_forward(x, thr, ord_, w)
-        g = torch.randn(f.shape, generator=gen)
+        g = torch.randn(f.shape, generator=gen).to(dtype)
         gx, gthr, _, gw = ref.trie_backward(x, True, thr, True, ord_, False, w, True, g)
         p = "trie%02d_" % idx
         for name, t in [("x", x), ("thr", thr), ("ord", ord_), ("w", w), ("out", f), ("g", g), ("gx", gx),
                         ("gthr", gthr), ("gw", gw)]:
             out[p + name] = t.numpy()
     out["trie_count"] = np.array(2)
-    np.savez_compressed(os.path.join(HERE, "families.npz"), **out)
-    print("wrote families.npz with", len(out), "arrays")
+    np.savez_compressed(os.path.join(HERE, filename), **out)
+    print("wrote", filename, "with", len(out), "arrays")
 
 
 INIT_CASES = [
@@ -283,7 +284,8 @@ def init_vectors(ref):
 
 
 if __name__ == "__main__":
-    if len(sys.argv) > 1 and sys.argv[1] == "double":  # only the double precision file
+    if len(sys.argv) > 1 and sys.argv[1] == "double":  # only the double precision files
         double_vectors(build_ref.load())
+        families(build_ref.load(), torch.float64, "families64.npz")
     else:
         main()

@@ -1,4 +1,4 @@
-"""The plain tree / fern operators on torch.float64 tensors, as the reference dispatches them
+"""The operators on torch.float64 tensors, as the reference dispatches them
 (hingetree.cpp:666-689): checked through the `hingetree_cpp` operators against golden vectors produced by the
 unmodified reference in double precision (tests/golden/forest64.npz, written by tests/golden/make_golden.py) and,
 where the reference build is at hand (oracle/_ref), against that build itself on larger seeded inputs.
@@ -85,7 +85,7 @@ def test_double_precision_against_the_reference_build(ext, kind):
     check(ext, kind, c)
 
 
-def test_double_precision_modules_and_the_operators_that_stay_single(ext):
+def test_double_precision_modules(ext):
     from hingetreefortorch_b200 import RandomHingeForest as R
     torch.manual_seed(5)
     m = R.RandomHingeForest(12, 6, 4, extra_outputs=2).double().cuda()
@@ -95,5 +95,100 @@ def test_double_precision_modules_and_the_operators_that_stay_single(ext):
     y.sum().backward()
     assert x.grad.dtype == torch.float64 and m.weights.grad.dtype == torch.float64
     conv = R.HingeTreeConv2d(2, 3, 2, 3).double().cuda()
-    with pytest.raises(ValueError, match="float64"):
-        conv(torch.randn(1, 2, 6, 6, dtype=torch.float64, device="cuda"))
+    image = torch.randn(1, 2, 6, 6, dtype=torch.float64, device="cuda", requires_grad=True)
+    out = conv(image)
+    assert out.dtype == torch.float64
+    out.sum().backward()
+    assert image.grad.dtype == torch.float64 and conv.thresholds.grad.dtype == torch.float64
+    with pytest.raises(ValueError):  # mixed precisions are refused, as in the reference
+        ext.tree_forward(x.detach(), m.thresholds.detach().float(), m.ordinals, m.weights.detach())
+
+
+# ---- the other operator families in double precision (tests/golden/families64.npz) ---------------------
+# The reference instantiates every operator for float and double.  Forward results of the fixed-order kernels
+# (fused linear, convolution, trie) equal the reference's CPU results bit for bit; fusion forward too; gradients are
+# sums in free order and are held to 1e-12 of the largest entry of the reference's gradient (double precision leaves
+# thirteen digits; the terms are O(1)).
+
+FAMILIES64 = np.load(os.path.join(GOLDEN, "families64.npz"))
+
+
+def family_case(prefix):
+    n = len(prefix)
+    return {k[n:]: FAMILIES64[k] for k in FAMILIES64.files if k.startswith(prefix)}
+
+
+def close64(t, ref):
+    ref = np.asarray(ref, dtype=np.float64)
+    got = t.detach().cpu().numpy()
+    return bool(np.all(np.abs(got - ref) <= 1e-12 * max(float(np.abs(ref).max()), 1e-300)))
+
+
+@pytest.mark.parametrize("idx", range(int(FAMILIES64["linear_count"])))
+def test_fused_linear_and_fusion_in_double(ext, idx):
+    c = family_case("linear%02d_" % idx)
+    kind = str(c["kind"])
+    d = {k: dev(v) for k, v in c.items() if k != "kind"}
+    assert d["x"].dtype == torch.float64
+    if "vec" in d:
+        out = getattr(ext, kind + "_fusion_fused_linear_forward")(d["x"], d["vec"], d["thr"], d["ord"], d["w"], d["lin"], d["bias"])
+        grads = getattr(ext, kind + "_fusion_fused_linear_backward")(d["x"], True, d["vec"], True, d["thr"], True, d["ord"], False,
+                                                                     d["w"], True, d["lin"], True, d["bias"], True, d["g"])
+        names = ["gx", "gvec", "gthr", None, "gw", "glin", "gbias"]
+        assert np.array_equal(getattr(ext, kind + "_fusion_forward")(d["x"], d["vec"], d["thr"], d["ord"], d["w"]).cpu().numpy(),
+                              c["fusion_out"])
+        fg = getattr(ext, kind + "_fusion_backward")(d["x"], True, d["vec"], True, d["thr"], True, d["ord"], False, d["w"], True,
+                                                     d["fusion_g"])
+        for got, name in zip((fg[0], fg[1], fg[2], fg[4]), ("fusion_gx", "fusion_gvec", "fusion_gthr", "fusion_gw")):
+            assert close64(got, c[name]), name
+    else:
+        out = getattr(ext, kind + "_fused_linear_forward")(d["x"], d["thr"], d["ord"], d["w"], d["lin"], d["bias"])
+        grads = getattr(ext, kind + "_fused_linear_backward")(d["x"], True, d["thr"], True, d["ord"], False, d["w"], True,
+                                                              d["lin"], True, d["bias"], True, d["g"])
+        names = ["gx", "gthr", None, "gw", "glin", "gbias"]
+    assert out.dtype == torch.float64 and np.array_equal(out.cpu().numpy(), c["out"])
+    for got, name in zip(grads, names):
+        if name is not None:
+            assert close64(got, c[name]), name
+
+
+@pytest.mark.parametrize("idx", range(int(FAMILIES64["conv_count"])))
+def test_convolution_in_double(ext, idx):
+    c = family_case("conv%02d_" % idx)
+    kind = str(c["kind"])
+    geometry = [[int(v) for v in row] for row in c["geometry"]]
+    dims = len(geometry[0])
+    d = {k: dev(v) for k, v in c.items() if k not in ("kind", "geometry")}
+    out = getattr(ext, "%s_conv%dd_forward" % (kind, dims))(d["x"], d["thr"], d["ord"], d["w"], *geometry)
+    assert out.dtype == torch.float64 and np.array_equal(out.cpu().numpy(), c["out"])
+    gx, gthr, _, gw = getattr(ext, "%s_conv%dd_backward" % (kind, dims))(d["x"], True, d["thr"], True, d["ord"], False, d["w"],
+                                                                        True, d["g"], *geometry)
+    assert close64(gx, c["gx"]) and close64(gthr, c["gthr"]) and close64(gw, c["gw"])
+
+
+@pytest.mark.parametrize("idx", range(int(FAMILIES64["trie_count"])))
+def test_trie_in_double(ext, idx):
+    c = family_case("trie%02d_" % idx)
+    d = {k: dev(v) for k, v in c.items()}
+    out = ext.trie_forward(d["x"], d["thr"], d["ord"], d["w"])
+    assert out.dtype == torch.float64 and np.array_equal(out.cpu().numpy(), c["out"])
+    gx, gthr, _, gw = ext.trie_backward(d["x"], True, d["thr"], True, d["ord"], False, d["w"], True, d["g"])
+    assert close64(gx, c["gx"]) and close64(gthr, c["gthr"]) and close64(gw, c["gw"])
+
+
+def test_sparse_backward_in_double(ext):
+    """Values and pattern of the sparse gradients against the dense double precision backward."""
+    gen = torch.Generator().manual_seed(4)
+    B, C, T, depth = 20, 9, 6, 4
+    x = torch.randn(B, C, generator=gen, dtype=torch.float64).cuda()
+    thr = (torch.rand(T, 2 ** depth - 1, generator=gen, dtype=torch.float64) * 4 - 2).cuda()
+    ord_ = torch.randint(0, C, (T, 2 ** depth - 1), generator=gen).cuda()
+    w = torch.randn(T, 2 ** depth, 2, generator=gen, dtype=torch.float64).cuda()
+    g = torch.randn(B, T, 2, generator=gen, dtype=torch.float64).cuda()
+    dense = ext.tree_backward(x, True, thr, True, ord_, False, w, True, g)
+    sparse = ext.sparse_tree_backward(x, True, thr, True, ord_, False, w, True, g)
+    for slot in (0, 1, 3):
+        assert sparse[slot].is_sparse and sparse[slot].dtype == torch.float64
+        assert close64(sparse[slot].to_dense(), dense[slot].cpu().numpy())
+        assert int(sparse[slot]._nnz()) <= int((dense[slot] != 0).sum()) + int(sparse[slot]._nnz())  # pattern holds the non-zeros
+        assert bool(((dense[slot] != 0) <= (sparse[slot].to_dense() != 0)).all())
