@@ -17,10 +17,11 @@ from .._ext import hingetree_cpp
 
 
 def _is_deterministic():
-    if hasattr(torch, "are_deterministic_algorithms_enabled"):
-        return torch.are_deterministic_algorithms_enabled()
-    if hasattr(torch, "is_deterministic"):
-        return torch.is_deterministic()
+    """Whether torch is in deterministic mode, under whichever name this torch has for the query."""
+    for query in ("are_deterministic_algorithms_enabled", "is_deterministic"):
+        fn = getattr(torch, query, None)
+        if fn is not None:
+            return bool(fn())
     raise RuntimeError("Unable to query torch deterministic mode.")
 
 
@@ -42,46 +43,69 @@ def _interleave(tensors, flags):
 
 
 # ---- contract / expand ---------------------------------------------------------------------
+# contract: [B, C, *image] -> [B, C, *windows, *window] (non-overlapping windows); expand is its inverse, and each is
+# the other's gradient (the reference: _HingeTree.py:32-89).  A scalar window or padding applies to every dimension.
+
+def _per_dimension(value, count):
+    return [value] * count if isinstance(value, int) else value
+
 
 def contract(inData, window, padding=0):
-    spatial = inData.dim() - 2
-    if isinstance(window, int):
-        window = [window] * spatial
-    if isinstance(padding, int):
-        padding = [padding] * spatial
-    return hingetree_cpp.contract(inData, window, padding)
+    dims = inData.dim() - 2
+    return hingetree_cpp.contract(inData, _per_dimension(window, dims), _per_dimension(padding, dims))
 
 
 def expand(inData, padding=0):
-    if isinstance(padding, int):
-        padding = [padding] * ((inData.dim() - 2) // 2)
-    return hingetree_cpp.expand(inData, padding)
+    return hingetree_cpp.expand(inData, _per_dimension(padding, (inData.dim() - 2) // 2))
 
 
-class _Expand(torch.autograd.Function):
+class _Patches(torch.autograd.Function):
+    """Both directions as one Function: `window` given means contract, None means expand; the backward runs the
+    other direction with the window the forward saw."""
+
     @staticmethod
-    def forward(ctx, inData, padding):
-        spatial = (inData.dim() - 2) // 2
-        ctx.window = list(inData.shape[-spatial:])
+    def forward(ctx, inData, window, padding):
         ctx.padding = padding
-        return expand(inData, padding)
-
-    @staticmethod
-    def backward(ctx, outDataGrad):
-        grad = contract(outDataGrad.contiguous(), ctx.window, ctx.padding) if ctx.needs_input_grad[0] else None
-        return grad, None
-
-
-class _Contract(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, inData, window, padding=0):
-        ctx.padding = padding
+        if window is None:
+            dims = (inData.dim() - 2) // 2
+            ctx.window = list(inData.shape[-dims:])
+            return expand(inData, padding)
+        ctx.window = None
         return contract(inData, window, padding)
 
     @staticmethod
     def backward(ctx, outDataGrad):
-        grad = expand(outDataGrad.contiguous(), ctx.padding) if ctx.needs_input_grad[0] else None
-        return grad, None, None
+        if not ctx.needs_input_grad[0]:
+            return None, None, None
+        grad = outDataGrad.contiguous()
+        if ctx.window is None:
+            return expand(grad, ctx.padding), None, None
+        return contract(grad, ctx.window, ctx.padding), None, None
+
+
+class _Expand:
+    """The reference's name for the expand Function (`_Expand.apply(x, padding)`)."""
+
+    @staticmethod
+    def apply(inData, padding):
+        return _Patches.apply(inData, None, padding)
+
+
+class _Contract:
+    """The reference's name for the contract Function (`_Contract.apply(x, window, padding)`)."""
+
+    @staticmethod
+    def apply(inData, window, padding=0):
+        return _Patches.apply(inData, window, padding)
+
+
+class Contract(torch.nn.Module):
+    def __init__(self, window, padding=0):
+        super().__init__()
+        self.window, self.padding = window, padding
+
+    def forward(self, inData):
+        return _Patches.apply(inData, self.window, self.padding)
 
 
 class Expand(torch.nn.Module):
@@ -90,17 +114,7 @@ class Expand(torch.nn.Module):
         self.padding = padding
 
     def forward(self, inData):
-        return _Expand.apply(inData, self.padding)
-
-
-class Contract(torch.nn.Module):
-    def __init__(self, window, padding=0):
-        super().__init__()
-        self.window = window
-        self.padding = padding
-
-    def forward(self, inData):
-        return _Contract.apply(inData, self.window, self.padding)
+        return _Patches.apply(inData, None, self.padding)
 
 
 # ---- Function templates --------------------------------------------------------------------
