@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(const
   };
 
   int it = 0;
-  if (!SAVE && tma_store) {
+  if (tma_store) {
     // The loop of the benchmark shapes, with nothing in it that the full groups of a forest with the
     // weights in its records do not need: one register addresses the warp's four consecutive records,
     // and the buffer goes back with one atomic (it wraps to zero with the last warp, which refills).
@@ -253,10 +253,40 @@ __global__ void __launch_bounds__(kThreads, 1) forest_forward_tiled_kernel(const
         poisoned = true;
         if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
       }
-      const uint32_t rec[4] = {params_addr + buffer * (uint32_t)G * lay.bytes + warp_records, 0u, 0u, 0u};
-      uint32_t unused[4];
+      const uint32_t first_record = params_addr + buffer * (uint32_t)G * lay.bytes + warp_records;
       float result[4] = {0.f, 0.f, 0.f, 0.f};
-      if (!poisoned) walk<KIND, DEPTH, OrdT, 4, WREC, true>(rec, xl_addr, x_stride, result, unused);
+      if constexpr (SAVE) {
+        // the walk of the backward (signed margin, deciding vertex, path): the same |margin| * leaf weight leaves as
+        // the result, and the traversal itself goes to the evaluation records, from registers (consecutive lanes
+        // are consecutive samples: 128 and 64 contiguous bytes per tree)
+        using WhereT = typename std::conditional<(DEPTH <= 8), unsigned short, uint32_t>::type;
+        const int64_t sample = row0 + sample_group * 32 + lane;
+        const int64_t at = record_index(sample, (int64_t)(group0 + it) * G + slot * 4, a.T);
+        uint32_t rec[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) rec[u] = first_record + (uint32_t)u * lay.bytes;
+        Walked wk[4];
+        if (!poisoned) {
+          walk_full<KIND, DEPTH, OrdT, 4, lay.paired>(rec, xl_addr, x_stride, wk);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            result[u] = __fmul_rn(fabsf(wk[u].nm), lds_f32(rec[u] + 4u * wk[u].path + (lay.w - 4u * (1u << DEPTH))));
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) wk[u] = Walked{0.0f, 1u, 1u << DEPTH};
+        }
+        if (sample < a.B) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            __stcs(a.save_margin + at + u * kRecordBlock, wk[u].nm);
+            store_where<WhereT>(a.save_where, at + u * kRecordBlock, wk[u].v, __brev(wk[u].path - (1u << DEPTH)) >> (32 - DEPTH));
+          }
+        }
+      } else {
+        const uint32_t rec[4] = {first_record, 0u, 0u, 0u};
+        uint32_t unused[4];
+        if (!poisoned) walk<KIND, DEPTH, OrdT, 4, WREC, true>(rec, xl_addr, x_stride, result, unused);
+      }
       done_with_buffer(it);
       if (store_issuer) tma::wait_stores_read();  // the previous box has been read out of the staging area
       named_barrier(1 + sample_group, group_threads);
