@@ -154,15 +154,29 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(cons
     const float *src = a.x + row * C * a.K + k;
     for (int c = tid / S; c < C; c += c_step) xs[c * S + t] = inside ? __ldg(src + (int64_t)c * a.K) : 0.0f;
   } else if ((C & 3) == 0) {
+    // two 16-byte loads in flight per thread before the first is stored (see the forward kernel)
     const int quads = C >> 2;
-    for (int idx = tid; idx < S * quads; idx += kThreads) {
-      const int s = idx % S, q = idx / S;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row0 + s < a.B) v = __ldg(reinterpret_cast<const float4 *>(a.x + (row0 + s) * C) + q);
-      xs[(4 * q + 0) * S + s] = v.x;
-      xs[(4 * q + 1) * S + s] = v.y;
-      xs[(4 * q + 2) * S + s] = v.z;
-      xs[(4 * q + 3) * S + s] = v.w;
+    const int total = S * quads;
+    for (int idx0 = tid; idx0 < total; idx0 += 2 * kThreads) {
+      float4 v[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int idx = idx0 + u * kThreads;
+        const int s = idx % S, q = idx / S;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < total && row0 + s < a.B) v[u] = __ldg(reinterpret_cast<const float4 *>(a.x + (row0 + s) * C) + q);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int idx = idx0 + u * kThreads;
+        if (idx < total) {
+          const int s = idx % S, q = idx / S;
+          xs[(4 * q + 0) * S + s] = v[u].x;
+          xs[(4 * q + 1) * S + s] = v[u].y;
+          xs[(4 * q + 2) * S + s] = v[u].z;
+          xs[(4 * q + 3) * S + s] = v[u].w;
+        }
+      }
     }
   } else {
     for (int idx = tid; idx < S * C; idx += kThreads) {
