@@ -31,11 +31,10 @@ class _LinearBatchNorm(torch.autograd.Function):
         z, total, total_sq = hingetree_cpp.linear_tf32_stats(x, w)
         rows = x.shape[0]
         if given_mean is None:
-            mean = total / rows
-            var = (total_sq / rows - mean * mean).clamp_min_(0.0)
+            mean, var, invstd = hingetree_cpp.batchnorm_statistics(total, total_sq, rows, eps)
         else:
             mean, var = given_mean, given_var
-        invstd = torch.rsqrt(var + eps)
+            invstd = torch.rsqrt(var + eps)
         y = torch.batch_norm_elemt(z, None, None, mean, invstd, eps)
         ctx.batch_statistics = given_mean is None
         ctx.save_for_backward(x, w, z, mean, invstd)
@@ -105,9 +104,7 @@ class _LinearBatchNormForest(torch.autograd.Function):
         x, w = x.contiguous(), w.contiguous()
         z, total, total_sq = hingetree_cpp.linear_tf32_stats(x, w)
         rows = x.shape[0]
-        mean = total / rows
-        var = (total_sq / rows - mean * mean).clamp_min_(0.0)
-        invstd = torch.rsqrt(var + eps)
+        mean, var, invstd = hingetree_cpp.batchnorm_statistics(total, total_sq, rows, eps)
         op = hingetree_cpp.fern_normalised_forward if fern else hingetree_cpp.tree_normalised_forward
         out = op(z, mean, invstd, thresholds, ordinals, weights)
         ctx.fern = fern

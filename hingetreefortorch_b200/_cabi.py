@@ -35,7 +35,7 @@ SYMBOLS = [
     "ht_forest_linear_forward_f64", "ht_forest_linear_backward_f64", "ht_conv_forward_f64", "ht_conv_backward_f64",
     "ht_trie_forward_f64", "ht_trie_backward_f64", "ht_forest_touched_f64",
     "ht_forest_normalised_workspace_bytes", "ht_forest_normalised_forward_f32", "ht_forest_normalised_backward_f32",
-    "ht_batchnorm_input_grad_f32",
+    "ht_batchnorm_input_grad_f32", "ht_batchnorm_statistics_f32",
     "ht_init_medians_workspace_bytes", "ht_init_medians_f32", "ht_init_medians_f64", "ht_thresholds_f32", "ht_thresholds_f64",
 ]
 

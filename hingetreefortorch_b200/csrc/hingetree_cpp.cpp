@@ -448,6 +448,23 @@ void check_statistics(const torch::Tensor &z, const torch::Tensor &mean, const t
 }
 }  // namespace
 
+// {mean, biased variance, 1 / sqrt(variance + eps)} of the columns from their sums and sums of squares over `rows` rows.
+std::vector<torch::Tensor> batchnorm_statistics(torch::Tensor sum, torch::Tensor sumsq, int64_t rows, double eps) {
+  if (sum.scalar_type() != torch::kFloat32 || sumsq.scalar_type() != torch::kFloat32 || sum.dim() != 1 ||
+      sumsq.sizes() != sum.sizes() || sum.device() != sumsq.device() || !sum.is_contiguous() || !sumsq.is_contiguous())
+    bad_argument("Error: sum and sumsq are expected to be contiguous torch.float32 vectors of the same length on one device.");
+  require_cuda(sum);
+  if (rows < 1) bad_argument("Error: rows must be positive.");
+  c10::DeviceGuard guard(sum.device());
+  torch::Tensor out = torch::empty({3, sum.size(0)}, sum.options());
+  const int64_t C = sum.size(0);
+  raise_status(ht_batchnorm_statistics_f32(sum.data_ptr<float>(), sumsq.data_ptr<float>(), rows, C, (float)eps,
+                                           out.data_ptr<float>(), out.data_ptr<float>() + C, out.data_ptr<float>() + 2 * C,
+                                           current_stream(sum)),
+               "batch normalisation statistics");
+  return {out[0], out[1], out[2]};
+}
+
 torch::Tensor forest_normalised_forward(int kind, torch::Tensor z, torch::Tensor mean, torch::Tensor invstd, torch::Tensor thr,
                                         torch::Tensor ord, torch::Tensor w) {
   ForestCall call(kind, z, thr, ord, w, nullptr);
@@ -796,6 +813,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_backward_scratch_limit", &set_backward_scratch_limit,
         "Upper bound in bytes on the scratch a default-mode backward call allocates for its per-evaluation records "
         "(12 bytes per tree evaluation); above it the gradients are scattered with atomics instead. Default: no bound.");
+  m.def("batchnorm_statistics", &batchnorm_statistics,
+        "[mean, biased variance, 1 / sqrt(variance + eps)] per column from the columns' sums and sums of squares over `rows` rows.");
   m.def("linear_tf32_stats", &linear_tf32_stats,
         "z = x @ w.T on the tensor cores (TF32 products, fp32 accumulation) and the column sums of z and z*z: "
         "[z, sum, sumsq]. K and N must be multiples of 4.");

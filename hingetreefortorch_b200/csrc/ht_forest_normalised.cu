@@ -147,6 +147,19 @@ __global__ void __launch_bounds__(kNormBlock) input_grad_sparse_kernel(const int
   atomicAdd(dz + i * C + c, __ldg(invstd + c) * v);
 }
 
+// mean, biased variance and 1 / sqrt(variance + eps) of every column from its sum and sum of squares.
+__global__ void __launch_bounds__(kNormBlock) statistics_kernel(const float *__restrict__ sum, const float *__restrict__ sumsq,
+                                                               int64_t C, float inv_rows, float eps, float *__restrict__ mean,
+                                                               float *__restrict__ var, float *__restrict__ invstd) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float m = __fmul_rn(sum[c], inv_rows);
+  const float v = fmaxf(__fsub_rn(__fmul_rn(sumsq[c], inv_rows), __fmul_rn(m, m)), 0.0f);
+  mean[c] = m;
+  var[c] = v;
+  invstd[c] = rsqrtf(__fadd_rn(v, eps));
+}
+
 int check(const ht_forest_problem *p, NormalisedArgs &a) {
   if (p == nullptr) return HT_ERR_INVALID_ARGUMENT;
   if (p->kind != TREE && p->kind != FERN) return HT_ERR_INVALID_ARGUMENT;
@@ -261,5 +274,16 @@ extern "C" int ht_batchnorm_input_grad_f32(const float *z, const float *mean, co
     input_grad_sparse_kernel<<<norm_blocks(B * T), kNormBlock, 0, stream>>>(column, value, invstd, dz, B, C, T);
     HT_CHECK_LAUNCH();
   }
+  return HT_OK;
+}
+
+extern "C" int ht_batchnorm_statistics_f32(const float *sum, const float *sumsq, int64_t rows, int64_t C, float eps, float *mean,
+                                           float *var, float *invstd, ht_stream_t stream_) {
+  if (rows < 1 || C < 0) return HT_ERR_INVALID_ARGUMENT;
+  if (C == 0) return HT_OK;
+  if (sum == nullptr || sumsq == nullptr || mean == nullptr || var == nullptr || invstd == nullptr) return HT_ERR_INVALID_ARGUMENT;
+  statistics_kernel<<<norm_blocks(C), kNormBlock, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(sum, sumsq, C, 1.0f / (float)rows, eps,
+                                                                                              mean, var, invstd);
+  HT_CHECK_LAUNCH();
   return HT_OK;
 }

@@ -347,6 +347,11 @@ int ht_forest_normalised_backward_f32(const ht_forest_problem *p, const float *z
                                       const float *thr, const int64_t *ord, const float *w, const float *g, float *gthr,
                                       float *gw, int32_t *column, float *value, float *sum_g, float *sum_gy, void *workspace,
                                       size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+/* mean[c] = sum[c] / rows, var[c] = max(sumsq[c] / rows - mean[c]^2, 0) (the biased variance batch normalisation
+ * normalises with), invstd[c] = 1 / sqrt(var[c] + eps): the step between ht_linear_tf32_stats_f32 and the entries above,
+ * as one launch. */
+int ht_batchnorm_statistics_f32(const float *sum, const float *sumsq, int64_t rows, int64_t C, float eps, float *mean,
+                                float *var, float *invstd, ht_stream_t stream);
 /* Gradient with respect to z of y = (z - mean) * invstd with batch statistics (training mode, no affine part):
  * dz[i, c] = invstd[c] * (gy[i, c] - sum_g[c] / B - y[i, c] * sum_gy[c] / B), gy given by the records above: one pass
  * over z for the dense part, one over the records (the formula of torch's batch-norm backward,
