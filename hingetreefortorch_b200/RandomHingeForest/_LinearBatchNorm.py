@@ -106,18 +106,18 @@ class _LinearBatchNormForest(torch.autograd.Function):
         rows = x.shape[0]
         mean, var, invstd = hingetree_cpp.batchnorm_statistics(total, total_sq, rows, eps)
         op = hingetree_cpp.fern_normalised_forward if fern else hingetree_cpp.tree_normalised_forward
-        out = op(z, mean, invstd, thresholds, ordinals, weights)
+        out, margin, where = op(z, mean, invstd, thresholds, ordinals, weights, True)  # the traversal is kept
         ctx.fern = fern
-        ctx.save_for_backward(x, w, z, mean, invstd, thresholds, ordinals, weights)
+        ctx.save_for_backward(x, w, z, mean, invstd, thresholds, ordinals, weights, margin, where)
         ctx.mark_non_differentiable(mean, var)
         return out, mean, var
 
     @staticmethod
     def backward(ctx, grad_out, _grad_mean, _grad_var):
-        x, w, z, mean, invstd, thresholds, ordinals, weights = ctx.saved_tensors
+        x, w, z, mean, invstd, thresholds, ordinals, weights, margin, where = ctx.saved_tensors
         op = hingetree_cpp.fern_normalised_backward if ctx.fern else hingetree_cpp.tree_normalised_backward
         grad_z, grad_thr, grad_weights = op(z, mean, invstd, thresholds, ctx.needs_input_grad[2], ordinals, weights,
-                                            ctx.needs_input_grad[4], grad_out.contiguous())
+                                            ctx.needs_input_grad[4], grad_out.contiguous(), margin, where)
         previous = torch.backends.cuda.matmul.allow_tf32
         torch.backends.cuda.matmul.allow_tf32 = True
         try:

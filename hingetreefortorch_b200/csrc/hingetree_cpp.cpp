@@ -465,32 +465,45 @@ std::vector<torch::Tensor> batchnorm_statistics(torch::Tensor sum, torch::Tensor
   return {out[0], out[1], out[2]};
 }
 
-torch::Tensor forest_normalised_forward(int kind, torch::Tensor z, torch::Tensor mean, torch::Tensor invstd, torch::Tensor thr,
-                                        torch::Tensor ord, torch::Tensor w) {
+// Returns {out, margin, where}: with `keep` the forward leaves its traversal (signed margin; deciding vertex and leaf
+// key) for forest_normalised_backward, else the two are empty tensors.
+std::vector<torch::Tensor> forest_normalised_forward(int kind, torch::Tensor z, torch::Tensor mean, torch::Tensor invstd,
+                                                     torch::Tensor thr, torch::Tensor ord, torch::Tensor w, bool keep) {
   ForestCall call(kind, z, thr, ord, w, nullptr);
   check_statistics(z, mean, invstd);
   c10::DeviceGuard guard(z.device());
+  const int64_t B = call.problem.B, T = call.problem.T;
   torch::Tensor out = torch::empty(call.out_sizes, z.options());
+  torch::Tensor margin = torch::empty({keep ? B : 0, T}, z.options());
+  torch::Tensor where = torch::empty({keep ? B : 0, T, 2}, z.options().dtype(torch::kInt32));
   torch::Tensor ws = make_workspace(ht_forest_normalised_workspace_bytes(&call.problem), z);
   OrdinalGuard og(ord, call.problem.C);
   raise_status(ht_forest_normalised_forward_f32(&call.problem, z.data_ptr<float>(), mean.data_ptr<float>(),
                                                 invstd.data_ptr<float>(), thr.data_ptr<float>(), ord.data_ptr<int64_t>(),
-                                                w.data_ptr<float>(), out.data_ptr<float>(), ws.data_ptr(), ws.numel(), og.word(),
-                                                current_stream(z)),
+                                                w.data_ptr<float>(), out.data_ptr<float>(),
+                                                keep && B * T > 0 ? margin.data_ptr<float>() : nullptr,
+                                                keep && B * T > 0 ? where.data_ptr() : nullptr, ws.data_ptr(), ws.numel(),
+                                                og.word(), current_stream(z)),
                "forest forward on normalised activations");
   og.finish();
-  return out;
+  return {out, margin, where};
 }
 
 // Returns {dz, gthr or None, gw or None}: the gradient with respect to the RAW activations (through the
-// normalisation with batch statistics) and the forest's parameter gradients.
+// normalisation with batch statistics) and the forest's parameter gradients.  margin / where: what the forward kept
+// (empty tensors: the trees are walked again).
 std::vector<torch::Tensor> forest_normalised_backward(int kind, torch::Tensor z, torch::Tensor mean, torch::Tensor invstd,
                                                       torch::Tensor thr, bool need_thr, torch::Tensor ord, torch::Tensor w,
-                                                      bool need_w, torch::Tensor g) {
+                                                      bool need_w, torch::Tensor g, torch::Tensor margin, torch::Tensor where) {
   ForestCall call(kind, z, thr, ord, w, &g);
   check_statistics(z, mean, invstd);
   c10::DeviceGuard guard(z.device());
   const int64_t B = call.problem.B, C = call.problem.C, T = call.problem.T;
+  const bool kept = margin.defined() && margin.numel() > 0;
+  if (kept && (margin.scalar_type() != torch::kFloat32 || where.scalar_type() != torch::kInt32 || margin.numel() != B * T ||
+               where.numel() != 2 * B * T || margin.device() != z.device() || where.device() != z.device() ||
+               !margin.is_contiguous() || !where.is_contiguous()))
+    bad_argument("Error: margin / where are not what the forward of this call kept.");
   torch::Tensor gthr = need_thr ? torch::empty_like(thr) : torch::Tensor();
   torch::Tensor gw = need_w ? torch::empty_like(w) : torch::Tensor();
   torch::Tensor column = torch::empty({B, T}, z.options().dtype(torch::kInt32));
@@ -503,7 +516,8 @@ std::vector<torch::Tensor> forest_normalised_backward(int kind, torch::Tensor z,
                    &call.problem, z.data_ptr<float>(), mean.data_ptr<float>(), invstd.data_ptr<float>(), thr.data_ptr<float>(),
                    ord.data_ptr<int64_t>(), w.data_ptr<float>(), g.data_ptr<float>(), need_thr ? gthr.data_ptr<float>() : nullptr,
                    need_w ? gw.data_ptr<float>() : nullptr, column.data_ptr<int32_t>(), value.data_ptr<float>(),
-                   sums.data_ptr<float>(), sums.data_ptr<float>() + C, ws.data_ptr(), ws.numel(), og.word(), current_stream(z)),
+                   sums.data_ptr<float>(), sums.data_ptr<float>() + C, kept ? margin.data_ptr<float>() : nullptr,
+                   kept ? where.data_ptr() : nullptr, ws.data_ptr(), ws.numel(), og.word(), current_stream(z)),
                "forest backward on normalised activations");
   raise_status(ht_batchnorm_input_grad_f32(z.data_ptr<float>(), mean.data_ptr<float>(), invstd.data_ptr<float>(),
                                            sums.data_ptr<float>(), sums.data_ptr<float>() + C, column.data_ptr<int32_t>(),
@@ -776,13 +790,20 @@ using namespace htx;
     return forest_backward_saved(KIND, det, x, nx, t, nt, o, no, w, nw, g, saved);                                  \
   });                                                                                                               \
   m.def(prefix "_normalised_forward", [](torch::Tensor z, torch::Tensor mean, torch::Tensor invstd, torch::Tensor t,  \
-                                         torch::Tensor o, torch::Tensor w) {                                        \
-    return forest_normalised_forward(KIND, z, mean, invstd, t, o, w);                                               \
-  });                                                                                                               \
+                                         torch::Tensor o, torch::Tensor w, bool keep) {                             \
+    return forest_normalised_forward(KIND, z, mean, invstd, t, o, w, keep);                                         \
+  }, pybind11::arg("z"), pybind11::arg("mean"), pybind11::arg("invstd"), pybind11::arg("thresholds"),              \
+     pybind11::arg("ordinals"), pybind11::arg("weights"), pybind11::arg("keep") = false);                         \
   m.def(prefix "_normalised_backward", [](torch::Tensor z, torch::Tensor mean, torch::Tensor invstd, torch::Tensor t, \
-                                          bool nt, torch::Tensor o, torch::Tensor w, bool nw, torch::Tensor g) {     \
-    return forest_normalised_backward(KIND, z, mean, invstd, t, nt, o, w, nw, g);                                   \
-  });                                                                                                               \
+                                          bool nt, torch::Tensor o, torch::Tensor w, bool nw, torch::Tensor g,       \
+                                          c10::optional<torch::Tensor> margin, c10::optional<torch::Tensor> where) { \
+    return forest_normalised_backward(KIND, z, mean, invstd, t, nt, o, w, nw, g,                                    \
+                                      margin.has_value() ? *margin : torch::Tensor(),                              \
+                                      where.has_value() ? *where : torch::Tensor());                               \
+  }, pybind11::arg("z"), pybind11::arg("mean"), pybind11::arg("invstd"), pybind11::arg("thresholds"),              \
+     pybind11::arg("need_thresholds"), pybind11::arg("ordinals"), pybind11::arg("weights"),                       \
+     pybind11::arg("need_weights"), pybind11::arg("grad"), pybind11::arg("margin") = pybind11::none(),            \
+     pybind11::arg("where") = pybind11::none());                                                                  \
   m.def(prefix "_check_thresholds", [](torch::Tensor t, torch::Tensor o, torch::Tensor w) {                         \
     return thresholds_utility(KIND, false, t, o, w);                                                                \
   });                                                                                                               \

@@ -51,13 +51,21 @@ __global__ void __launch_bounds__(kNormBlock) compact_ordinals_kernel(const int6
   packed[e] = (int32_t)c;
 }
 
+// save_margin / save_where (both or neither): the signed margin and the pair (deciding vertex, leaf key) of every
+// (sample, tree), 12 bytes, so that the backward need not read z and walk again.
 template <int KIND>
-__global__ void __launch_bounds__(kNormBlock) normalised_forward_kernel(NormalisedArgs a, float *__restrict__ out) {
+__global__ void __launch_bounds__(kNormBlock) normalised_forward_kernel(NormalisedArgs a, float *__restrict__ out,
+                                                                       float *__restrict__ save_margin,
+                                                                       uint2 *__restrict__ save_where) {
   const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= a.B * a.T) return;
   const int64_t i = e / a.T, j = e - i * a.T;
   const NormalisedFeature feat{a.z + i * a.C, a.mean, a.invstd};
   const Path p = traverse<KIND>(feat, a.thr + j * a.N, a.ord + j * a.N, a.depth);
+  if (save_margin != nullptr) {
+    save_margin[e] = p.margin;
+    save_where[e] = make_uint2(p.vertex, p.key);
+  }
   const float am = fabsf(p.margin);
   const float *wl = a.w + (j * a.L + p.key) * a.M;
   float *o = out + e * a.M;
@@ -70,12 +78,22 @@ __global__ void __launch_bounds__(kNormBlock) normalised_forward_kernel(Normalis
 template <int KIND>
 __global__ void __launch_bounds__(kNormBlock) normalised_backward_kernel(NormalisedArgs a, const float *__restrict__ g, float *gthr,
                                                                         float *gw, int32_t *__restrict__ column,
-                                                                        float *__restrict__ value, float *sum_g, float *sum_gy) {
+                                                                        float *__restrict__ value, float *sum_g, float *sum_gy,
+                                                                        const float *__restrict__ saved_margin,
+                                                                        const uint2 *__restrict__ saved_where) {
   const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= a.B * a.T) return;
   const int64_t i = e / a.T, j = e - i * a.T;
   const NormalisedFeature feat{a.z + i * a.C, a.mean, a.invstd};
-  const Path p = traverse<KIND>(feat, a.thr + j * a.N, a.ord + j * a.N, a.depth);
+  Path p;
+  if (saved_margin != nullptr) {  // the forward kept its traversal
+    const uint2 where = saved_where[e];
+    p.margin = saved_margin[e];
+    p.vertex = where.x;
+    p.key = where.y;
+  } else {
+    p = traverse<KIND>(feat, a.thr + j * a.N, a.ord + j * a.N, a.depth);
+  }
   const float s = sign_of(p.margin), am = fabsf(p.margin);
   const float *wl = a.w + (j * a.L + p.key) * a.M;
   const float *gl = g + e * a.M;
@@ -91,7 +109,9 @@ __global__ void __launch_bounds__(kNormBlock) normalised_backward_kernel(Normali
   value[e] = acc;
   if (acc != 0.0f) {
     atomicAdd(sum_g + c, acc);
-    atomicAdd(sum_gy + c, __fmul_rn(acc, feat(c)));
+    // the normalised feature at the deciding vertex: read again, or margin + threshold (a rounding apart)
+    const float y = saved_margin != nullptr ? __fadd_rn(p.margin, __ldg(a.thr + j * a.N + p.vertex)) : feat(c);
+    atomicAdd(sum_gy + c, __fmul_rn(acc, y));
   }
 }
 
@@ -187,9 +207,11 @@ extern "C" size_t ht_forest_normalised_workspace_bytes(const ht_forest_problem *
 }
 
 extern "C" int ht_forest_normalised_forward_f32(const ht_forest_problem *p, const float *z, const float *mean, const float *invstd,
-                                                const float *thr, const int64_t *ord, const float *w, float *out, void *workspace,
-                                                size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream_) {
+                                                const float *thr, const int64_t *ord, const float *w, float *out,
+                                                float *save_margin, void *save_where, void *workspace, size_t workspace_bytes,
+                                                uint32_t *status_word, ht_stream_t stream_) {
   NormalisedArgs a = {};
+  if ((save_margin == nullptr) != (save_where == nullptr)) return HT_ERR_INVALID_ARGUMENT;
   const int rc = check(p, a);
   if (rc != HT_OK) return rc;
   if (a.B == 0 || a.T == 0) return HT_OK;
@@ -207,9 +229,9 @@ extern "C" int ht_forest_normalised_forward_f32(const ht_forest_problem *p, cons
   a.w = w;
   a.ord = packed;
   if (p->kind == TREE)
-    normalised_forward_kernel<TREE><<<norm_blocks(a.B * a.T), kNormBlock, 0, stream>>>(a, out);
+    normalised_forward_kernel<TREE><<<norm_blocks(a.B * a.T), kNormBlock, 0, stream>>>(a, out, save_margin, static_cast<uint2 *>(save_where));
   else
-    normalised_forward_kernel<FERN><<<norm_blocks(a.B * a.T), kNormBlock, 0, stream>>>(a, out);
+    normalised_forward_kernel<FERN><<<norm_blocks(a.B * a.T), kNormBlock, 0, stream>>>(a, out, save_margin, static_cast<uint2 *>(save_where));
   HT_CHECK_LAUNCH();
   return HT_OK;
 }
@@ -217,9 +239,10 @@ extern "C" int ht_forest_normalised_forward_f32(const ht_forest_problem *p, cons
 extern "C" int ht_forest_normalised_backward_f32(const ht_forest_problem *p, const float *z, const float *mean, const float *invstd,
                                                  const float *thr, const int64_t *ord, const float *w, const float *g, float *gthr,
                                                  float *gw, int32_t *column, float *value, float *sum_g, float *sum_gy,
-                                                 void *workspace, size_t workspace_bytes, uint32_t *status_word,
-                                                 ht_stream_t stream_) {
+                                                 const float *saved_margin, const void *saved_where, void *workspace,
+                                                 size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream_) {
   NormalisedArgs a = {};
+  if ((saved_margin == nullptr) != (saved_where == nullptr)) return HT_ERR_INVALID_ARGUMENT;
   const int rc = check(p, a);
   if (rc != HT_OK) return rc;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
@@ -243,9 +266,11 @@ extern "C" int ht_forest_normalised_backward_f32(const ht_forest_problem *p, con
   a.w = w;
   a.ord = packed;
   if (p->kind == TREE)
-    normalised_backward_kernel<TREE><<<norm_blocks(a.B * a.T), kNormBlock, 0, stream>>>(a, g, gthr, gw, column, value, sum_g, sum_gy);
+    normalised_backward_kernel<TREE><<<norm_blocks(a.B * a.T), kNormBlock, 0, stream>>>(
+        a, g, gthr, gw, column, value, sum_g, sum_gy, saved_margin, static_cast<const uint2 *>(saved_where));
   else
-    normalised_backward_kernel<FERN><<<norm_blocks(a.B * a.T), kNormBlock, 0, stream>>>(a, g, gthr, gw, column, value, sum_g, sum_gy);
+    normalised_backward_kernel<FERN><<<norm_blocks(a.B * a.T), kNormBlock, 0, stream>>>(
+        a, g, gthr, gw, column, value, sum_g, sum_gy, saved_margin, static_cast<const uint2 *>(saved_where));
   HT_CHECK_LAUNCH();
   return HT_OK;
 }

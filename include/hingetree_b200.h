@@ -336,16 +336,20 @@ int ht_forest_touched_f64(const ht_forest_problem *p, const double *x, const dou
  * on the materialised normalisation bit for bit.  No reference counterpart.
  * workspace: ht_forest_normalised_workspace_bytes(p) bytes. */
 size_t ht_forest_normalised_workspace_bytes(const ht_forest_problem *p);
+/* save_margin [B, T] floats and save_where [B, T] pairs of uint32 (both or neither): where the forward leaves the signed
+ * margin and (deciding vertex, leaf key) of every evaluation for the backward below, which then does not walk again. */
 int ht_forest_normalised_forward_f32(const ht_forest_problem *p, const float *z, const float *mean, const float *invstd,
-                                     const float *thr, const int64_t *ord, const float *w, float *out, void *workspace,
-                                     size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
+                                     const float *thr, const int64_t *ord, const float *w, float *out, float *save_margin,
+                                     void *save_where, void *workspace, size_t workspace_bytes, uint32_t *status_word,
+                                     ht_stream_t stream);
 /* Backward of the same: gthr [T, N] and gw [T, L, M] (either may be NULL) as ht_forest_backward_f32 gives them
  * (default mode: atomics), and the gradient with respect to the normalised activations y in the form it has —
  * one entry per (sample, tree): column[B, T] (the feature the deciding vertex tests) and value[B, T] — with the two
  * column sums the normalisation's backward needs: sum_g[c] = sum_i gy[i, c], sum_gy[c] = sum_i gy[i, c] * y[i, c]. */
 int ht_forest_normalised_backward_f32(const ht_forest_problem *p, const float *z, const float *mean, const float *invstd,
                                       const float *thr, const int64_t *ord, const float *w, const float *g, float *gthr,
-                                      float *gw, int32_t *column, float *value, float *sum_g, float *sum_gy, void *workspace,
+                                      float *gw, int32_t *column, float *value, float *sum_g, float *sum_gy,
+                                      const float *saved_margin, const void *saved_where, void *workspace,
                                       size_t workspace_bytes, uint32_t *status_word, ht_stream_t stream);
 /* mean[c] = sum[c] / rows, var[c] = max(sumsq[c] / rows - mean[c]^2, 0) (the biased variance batch normalisation
  * normalises with), invstd[c] = 1 / sqrt(var[c] + eps): the step between ht_linear_tf32_stats_f32 and the entries above,

@@ -113,9 +113,12 @@ def test_forest_on_unmaterialised_normalisation(kind, extra):
     invstd = torch.rsqrt(z.var(0, unbiased=False) + 1e-5)
     y = torch.batch_norm_elemt(z, None, None, mean, invstd, 1e-5)
     plain = getattr(ext, kind + "_forward")(y, thr, ord_, w)
-    fused = getattr(ext, kind + "_normalised_forward")(z, mean, invstd, thr, ord_, w)
-    assert torch.equal(fused, plain)
+    fused, no_margin, no_where = getattr(ext, kind + "_normalised_forward")(z, mean, invstd, thr, ord_, w)
+    assert torch.equal(fused, plain) and no_margin.numel() == 0 and no_where.numel() == 0
+    kept_out, margin, where = getattr(ext, kind + "_normalised_forward")(z, mean, invstd, thr, ord_, w, True)
+    assert torch.equal(kept_out, plain) and margin.shape == (B, T) and where.shape == (B, T, 2)
     dz, gthr, gw = getattr(ext, kind + "_normalised_backward")(z, mean, invstd, thr, True, ord_, w, True, g)
+    kept = getattr(ext, kind + "_normalised_backward")(z, mean, invstd, thr, True, ord_, w, True, g, margin, where)
     want = ho.backward(kind, y.cpu().numpy(), thr.cpu().numpy(), ord_.cpu().numpy(), w.cpu().numpy(), g.cpu().numpy())
     mags = ho.backward_magnitudes(kind, y.cpu().numpy(), thr.cpu().numpy(), ord_.cpu().numpy(), w.cpu().numpy(), g.cpu().numpy())
     assert grad_close(gthr, want[1], mags[1]) and grad_close(gw, want[2], mags[2])
@@ -125,6 +128,9 @@ def test_forest_on_unmaterialised_normalisation(kind, extra):
     want_dz = torch.batch_norm_backward_elemt(gy, z, mean, invstd, None, sum_dy, sum_dy_xmu, count)
     scale = float(want_dz.abs().max())
     assert float((dz - want_dz).abs().max()) <= 2e-5 * scale
+    # from the kept traversal: the same parameter gradients (same terms; sums in free order), the same dz to a rounding
+    assert grad_close(kept[1], want[1], mags[1]) and grad_close(kept[2], want[2], mags[2])
+    assert float((kept[0] - want_dz).abs().max()) <= 2e-5 * scale
     only = getattr(ext, kind + "_normalised_backward")(z, mean, invstd, thr, False, ord_, w, False, g)
     assert only[1] is None and only[2] is None and float((only[0] - want_dz).abs().max()) <= 2e-5 * scale
 
