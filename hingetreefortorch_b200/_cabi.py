@@ -242,9 +242,9 @@ class Forest:
     def backward(self, x, thr, ord_, w, g, need=(True, True, True), outs=None, saved=False):
         """saved=True: the last call on this object was forward(save=True) on the same tensors."""
         import torch
-        if outs is None:
-            outs = (torch.empty_like(x) if need[0] else None, torch.empty_like(thr) if need[1] else None,
-                    torch.empty_like(w) if need[2] else None)
+        if outs is None:  # NaN-filled: an element the library fails to write shows in every comparison
+            outs = (torch.full_like(x, float("nan")) if need[0] else None, torch.full_like(thr, float("nan")) if need[1] else None,
+                    torch.full_like(w, float("nan")) if need[2] else None)
         problem = self._with_flags(HT_SAVED_FORWARD) if saved else self.problem
         _check(library().ht_forest_backward_f32(ctypes.byref(problem), _ptr(x), _ptr(thr), _ptr(ord_), _ptr(w),
                                                 _ptr(g), _ptr(outs[0]), _ptr(outs[1]), _ptr(outs[2]), *self._tail(x)))

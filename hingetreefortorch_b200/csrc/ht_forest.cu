@@ -505,9 +505,12 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
   if (rc != HT_OK) return rc;
   if (g == nullptr && pr.evals * p->M > 0) return HT_ERR_INVALID_ARGUMENT;
   const ForestArgs &a = pr.args;
-  const int crc = clear_gradients(pr, gx, gthr, gw);
+  // The parameter gradients are sums into cleared memory on every path.  The x gradient is cleared only for the
+  // paths that add into it: from a kept traversal it is written tile by tile, every element once.
+  int crc = clear_gradients(pr, static_cast<float *>(nullptr), gthr, gw);
   if (crc != HT_OK) return crc;
-  if (pr.evals * a.M == 0 || (gx == nullptr && gthr == nullptr && gw == nullptr)) return HT_OK;
+  if (pr.evals * a.M == 0 || (gx == nullptr && gthr == nullptr && gw == nullptr))
+    return clear_gradients(pr, gx, static_cast<float *>(nullptr), static_cast<float *>(nullptr));
 
   {
     // Tile kernels when the shape qualifies; with room for the evaluation records in the workspace
@@ -521,6 +524,8 @@ int ht_forest_backward_f32(const ht_forest_problem *p, const float *x, const flo
       const int src = backward_saved(p, a.ord, w, g, gx, gthr, gw, eval_records, pr.stream);
       if (src != HT_ERR_UNSUPPORTED) return src;
     }
+    crc = clear_gradients(pr, gx, static_cast<float *>(nullptr), static_cast<float *>(nullptr));
+    if (crc != HT_OK) return crc;
     const int trc = backward_tiled(p, x, thr, a.ord, w, g, gx, gthr, gw, ws + ordinals_bytes(p), eval_records,
                                    status_word, pr.stream);
     if (trc != HT_ERR_UNSUPPORTED) return trc;
