@@ -175,6 +175,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
   const int oy = oy0 + tile_row, ox = ox0 + lane;
   const bool position_valid = oy < a.Ho && ox < a.Wo;
   const int slot_threads = TY * 32, tid_in_slot = tile_row * 32 + lane;
+  const bool bins_wanted = a.gthr != nullptr || a.gw != nullptr;
+  const int64_t g_plane = (int64_t)a.Ho * a.Wo;
+  const float *g_here = a.g + b * a.Co * g_plane + (position_valid ? (int64_t)oy * a.Wo + ox : 0);
   bool poisoned = false;
 
   for (int it = 0; it < num_groups; ++it) {
@@ -192,18 +195,33 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
     if (active && !poisoned) {
       const uint32_t base_addr = params_addr + (uint32_t)(it & 1) * buffer_bytes + (uint32_t)slot * (uint32_t)JJ * lay.bytes;
       const uint32_t x_addr = origin_addr + (uint32_t)c * patch_bytes;
-      for (int jl = 0; jl < count_j; jl += 4) {
+      const float *g_chunk = g_here + (int64_t)j_first * g_plane;  // upstream gradient of channel j_first at this position
+      for (int jl = 0; jl < count_j; jl += 4, g_chunk += 4 * g_plane) {
         uint32_t rec[4];
         float gval[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           rec[u] = base_addr + (uint32_t)min(jl + u, count_j - 1) * lay.bytes;
           gval[u] = 0.0f;
-          if (position_valid && jl + u < count_j)
-            gval[u] = __ldg(a.g + ((b * a.Co + j_first + jl + u) * a.Ho + oy) * (int64_t)a.Wo + ox);
+          if (position_valid && jl + u < count_j) gval[u] = __ldg(g_chunk + u * g_plane);
         }
         Walked wk[4];
         walk_full<KIND, DEPTH, OrdT, 4>(rec, x_addr, 4u, wk);
+        if (!bins_wanted) {
+          // The image gradient alone (the parameter gradients came from the kernel further down).  A walk past the
+          // last output channel repeats that channel's record with a zero upstream gradient and adds a zero.
+          if (position_valid) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float wg = __fmul_rn(lds_f32(rec[u] + 4u * wk[u].path + (lay.w - 4u * kL)), gval[u]);
+              const float dx = wk[u].nm < 0.0f ? wg : (wk[u].nm > 0.0f ? -wg : __fmul_rn(0.0f, wg));
+              const uint32_t off = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * wk[u].v + (lay.ord - (uint32_t)sizeof(OrdT)));
+              const uint32_t cell_addr = my_cells_addr + (uint32_t)cell_of[off] * 128u;
+              sts_f32(cell_addr, __fadd_rn(lds_f32(cell_addr), dx));
+            }
+          }
+          continue;
+        }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           if (jl + u < count_j) {  // the same for the whole warp; lanes off the output contribute zeros
@@ -245,11 +263,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
 
     // The slot's warps have all added to this group's bins: send the touched ones out and clear
     // them.  The buffer is used again two groups on, after the slot has met at this barrier once more.
-    if (TY == 1)
+    if (!bins_wanted)
+      ;  // no bins in use
+    else if (TY == 1)
       __syncwarp();  // the slot is this warp alone
     else
       named_barrier(1 + slot, slot_threads);
-    if (active) {
+    if (active && bins_wanted) {
       for (int e = tid_in_slot; e < count_j * kBins; e += slot_threads) {
         const float v = my_bins[e];
         if (v != 0.0f) {
@@ -295,6 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
 struct ParamGradPlan {
   int R;        // tile rows
   int columns;  // lanes' columns per bin: 16, 8 or 4
+  int staged;   // input channels whose patches are staged together
   int patch_h, patch_w, ord_bytes;
   RecordLayout rec;
   size_t smem;
@@ -313,9 +334,13 @@ bool make_param_plan(const ConvTileProblem &p, ParamGradPlan &plan) {
   plan.patch_w = shape.w;
   plan.ord_bytes = shape.far <= 255 ? 1 : 2;
   plan.rec = record_layout(p.kind, p.depth, (uint32_t)plan.ord_bytes);
-  plan.smem = align_up((size_t)shape.h * shape.w * 4, 128) + 2 * (size_t)kWarps * plan.rec.bytes +
-              (size_t)kWarps * bins_per_tree * plan.columns * 4 + 64;
-  return plan.smem <= kSmemBudget;
+  // Every warp waits while patches are staged, so as many input channels as fit (16 at most) are staged at a time.
+  for (plan.staged = (int)std::min<int64_t>(p.Ci, 16); plan.staged >= 1; --plan.staged) {
+    plan.smem = align_up((size_t)plan.staged * shape.h * shape.w * 4, 128) + 2 * (size_t)kWarps * plan.rec.bytes +
+                (size_t)kWarps * bins_per_tree * plan.columns * 4 + 64;
+    if (plan.smem <= kSmemBudget) return true;
+  }
+  return false;
 }
 
 struct ParamGradArgs {
@@ -325,7 +350,7 @@ struct ParamGradArgs {
   float *gthr, *gw;
   uint32_t *status_word;
   int Ci, Co, H, W, Ho, Wo, sy, sx, py, px;
-  int R, columns, patch_h, patch_w, tiles_x, row_blocks;
+  int R, columns, staged, patch_h, patch_w, tiles_x, row_blocks;
 };
 
 template <int KIND, int DEPTH, typename OrdT>
@@ -338,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
   const int R = a.R, columns = a.columns;
   const int patch_elems = a.patch_h * a.patch_w;
   float *patch = reinterpret_cast<float *>(smem);
-  unsigned char *params = smem + (((size_t)patch_elems * 4 + 127) & ~(size_t)127);
+  unsigned char *params = smem + (((size_t)a.staged * patch_elems * 4 + 127) & ~(size_t)127);
   float *bins = reinterpret_cast<float *>(params + 2 * (size_t)kWarps * lay.bytes);  // [kWarps][kBins][columns]
   uint64_t *full = reinterpret_cast<uint64_t *>(bins + (size_t)kWarps * kBins * columns);
   uint32_t *finished = reinterpret_cast<uint32_t *>(full + 2);
@@ -385,19 +410,21 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
   const uint32_t row_bytes = (uint32_t)(a.sy * a.patch_w) * 4u;
   const uint32_t my_bins_addr = smem_addr(bins) + (uint32_t)(warp * kBins * columns + lane % columns) * 4u;
   const uint32_t bin_bytes = (uint32_t)columns * 4u;
-  const int turns = 32 / columns, my_turn = lane / columns;
+  const int turns = 32 / columns, group = lane / columns;
   const int rows_here = min(R, a.Ho - oy0);
   const float *image = a.x + b * a.Ci * (int64_t)a.H * a.W;
+  const bool want_thr = a.gthr != nullptr, want_w = a.gw != nullptr;
   bool poisoned = false;
 
   for (int it = 0; it < num_groups; ++it) {
     const int c = it / my_rounds;
-    if (it % my_rounds == 0) {  // next input channel: every warp is done with the previous patch
+    if (it % (my_rounds * a.staged) == 0) {  // next input channels: every warp is done with the previous patches
       __syncthreads();
-      stage_patches(patch, image + (int64_t)c * a.H * a.W, 1, a.H, a.W, oy0 * a.sy - a.py, ox0 * a.sx - a.px, a.patch_h,
-                    a.patch_w);
+      stage_patches(patch, image + (int64_t)c * a.H * a.W, min(a.staged, a.Ci - c), a.H, a.W, oy0 * a.sy - a.py,
+                    ox0 * a.sx - a.px, a.patch_h, a.patch_w);
       __syncthreads();
     }
+    const uint32_t channel_addr = lane_addr + (uint32_t)(c % a.staged) * (uint32_t)patch_elems * 4u;
     if (!poisoned && !mbar_wait(&full[it & 1], (uint32_t)((it >> 1) & 1))) {
       poisoned = true;
       if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
@@ -412,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           rec[u] = record;
-          x_addr[u] = lane_addr + (uint32_t)(row0 + u) * row_bytes;
+          x_addr[u] = channel_addr + (uint32_t)(row0 + u) * row_bytes;
           gval[u] = (row0 + u < rows_here && ox < a.Wo) ? __ldg(g_rows + (int64_t)(row0 + u) * a.Wo) : 0.0f;
         }
         Walked wk[4];
@@ -430,26 +457,57 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
           at_thr[u] = my_bins_addr + (wk[u].v - 1u) * bin_bytes;
           at_w[u] = my_bins_addr + (kN + wk[u].path - kL) * bin_bytes;
         }
-        for (int turn = 0; turn < turns; ++turn) {  // lanes that share a column take turns
-          if (turn == my_turn) {
+        // Lanes that share a column (32 / columns of them, `group` apart) must not update it together.  Every term
+        // is added, zeros included: a test per term costs a divergent branch each, more than the addition it would
+        // save.  (The four bins of one kind may coincide, so a lane's updates of one kind stay in order.)
+        if (want_thr && want_w) {
+          // A threshold bin and a leaf bin never coincide: while the even group of a pair adds its threshold terms
+          // the odd group adds its leaf terms, then they swap.  With two groups nobody idles.
+          auto add_one_kind = [&](bool thr_now) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              if (a.gthr != nullptr && term_thr[u] != 0.0f) sts_f32(at_thr[u], __fadd_rn(lds_f32(at_thr[u]), term_thr[u]));
-              if (a.gw != nullptr && term_w[u] != 0.0f) sts_f32(at_w[u], __fadd_rn(lds_f32(at_w[u]), term_w[u]));
+              const uint32_t at = thr_now ? at_thr[u] : at_w[u];
+              sts_f32(at, __fadd_rn(lds_f32(at), thr_now ? term_thr[u] : term_w[u]));
+            }
+          };
+          if (turns == 2) {
+            add_one_kind(group == 0);
+            __syncwarp();
+            add_one_kind(group != 0);
+            __syncwarp();
+          } else {
+            for (int phase = 0; phase < turns; ++phase) {
+              if ((group >> 1) == (phase >> 1)) add_one_kind(((group ^ phase) & 1) == 0);
+              __syncwarp();
             }
           }
-          __syncwarp();
+        } else {
+          for (int turn = 0; turn < turns; ++turn) {
+            if (turn == group) {
+              if (want_thr) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) sts_f32(at_thr[u], __fadd_rn(lds_f32(at_thr[u]), term_thr[u]));
+              } else if (want_w) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) sts_f32(at_w[u], __fadd_rn(lds_f32(at_w[u]), term_w[u]));
+              }
+            }
+            __syncwarp();
+          }
         }
       }
       // sum the columns of every bin, clear them, send the touched bins out
       const int64_t tree = (int64_t)j * a.Ci + c;
-      float *warp_bins = bins + (size_t)warp * kBins * columns;
+      const uint32_t warp_bins_addr = smem_addr(bins) + (uint32_t)(warp * kBins * columns) * 4u;
+      const int quads = columns >> 2;  // columns is 16, 8 or 4: a bin is 1 to 4 aligned 16-byte pieces
       for (int bin = lane; bin < kBins; bin += 32) {
         float sum = 0.0f;
-        for (int k = 0; k < columns; ++k) {
-          const int col = (k + lane) % columns;  // rotated so that the lanes spread over the banks
-          sum += warp_bins[bin * columns + col];
-          warp_bins[bin * columns + col] = 0.0f;
+        for (int k = 0; k < quads; ++k) {
+          const int quad = (k + lane) & (quads - 1);  // rotated so that the lanes spread over the banks
+          const uint32_t at = warp_bins_addr + (uint32_t)(bin * columns + 4 * quad) * 4u;
+          const uint4 v = lds_b128(at);
+          sum += (__uint_as_float(v.x) + __uint_as_float(v.y)) + (__uint_as_float(v.z) + __uint_as_float(v.w));
+          sts_b128(at, 0.0f, 0.0f, 0.0f, 0.0f);
         }
         if (sum != 0.0f) {
           if (bin < (int)kN)
@@ -600,6 +658,7 @@ int conv_backward_tiled(const ConvTileProblem &p, const float *x, const float *t
     pa.px = p.px;
     pa.R = pplan.R;
     pa.columns = pplan.columns;
+    pa.staged = pplan.staged;
     pa.patch_h = pplan.patch_h;
     pa.patch_w = pplan.patch_w;
     pa.tiles_x = tiles_x;
