@@ -35,11 +35,85 @@ using namespace conv_tile;
 
 namespace {
 
+// ---- records with one 8-byte entry per vertex --------------------------------------------------------
+//
+// The backward's traversal needs the threshold and the patch offset of every vertex it visits, from addresses
+// that differ from lane to lane.  In this form of the record vertex v (1-based; ferns: level + 1) has the
+// entry {threshold, offset as a 32-bit word} at byte 8 v (bytes 0..7 are unused), so that one address and one
+// 8-byte load bring both; the leaf weights follow in path order as in the other records.  Larger than the
+// packed form (8 against 5 or 6 bytes a vertex): the plans below take it where it fits.
+__host__ __device__ constexpr RecordLayout vertex_pair_layout(int kind, int depth) {
+  const uint32_t n = kind == FERN ? (uint32_t)depth : (1u << depth) - 1u;
+  const uint32_t w = round16(8u * (n + 1u));
+  return RecordLayout{0u, 4u, w, round16(w + 4u * (1u << depth)), false};
+}
+
+__global__ void repack_vertex_pairs_kernel(const float *__restrict__ thr, const int32_t *__restrict__ ord,
+                                           const float *__restrict__ w, unsigned char *__restrict__ records, int kind,
+                                           int depth, int64_t T, RecordLayout lay, RecordMap map) {
+  const int64_t N = threshold_count(kind, depth);
+  const int64_t L = ((int64_t)1) << depth;
+  const int64_t per_tree = N + L;
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= T * per_tree) return;
+  const int64_t j = e / per_tree;
+  const int64_t r = e - j * per_tree;
+  unsigned char *rec = records + map.slot(j) * lay.bytes;
+  if (r < N) {
+    float t = thr[j * N + r];
+    t = t == 0.0f ? 0.0f : t;  // -0 becomes +0
+    uint2 entry;
+    entry.x = __float_as_uint(t);
+    entry.y = map.feature((uint32_t)ord[j * N + r]);
+    reinterpret_cast<uint2 *>(rec)[r + 1] = entry;
+    if (r == 0) reinterpret_cast<uint2 *>(rec)[0] = make_uint2(0u, 0u);
+  } else {
+    const int64_t h = r - N;
+    reinterpret_cast<float *>(rec + lay.w)[h] = w[j * L + (int64_t)bit_reverse((uint32_t)h, depth)];
+  }
+}
+
+template <uint32_t OFFSET>
+__device__ __forceinline__ uint2 lds_b64_at(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFFSET));
+  return v;
+}
+
+// walk_full on records of that form: rec[u] and x_addr[u] are the record and the window origin of the u-th walk.
+template <int KIND, int DEPTH, int NT>
+__device__ __forceinline__ void walk_vertex_pairs(const uint32_t (&rec)[NT], const uint32_t (&x_addr)[NT],
+                                                  Walked (&out)[NT]) {
+  uint32_t v[NT];
+#pragma unroll
+  for (int u = 0; u < NT; ++u) v[u] = 1u;
+  static_for<0, DEPTH>([&](auto level) {
+    constexpr int l = decltype(level)::value;
+    static_for<0, NT>([&](auto walk_index) {
+      constexpr int u = decltype(walk_index)::value;
+      uint2 entry;
+      if constexpr (KIND == FERN)
+        entry = lds_b64_at<8u * (uint32_t)(l + 1)>(rec[u]);
+      else
+        entry = lds_b64_at<0u>(rec[u] + 8u * v[u]);
+      const float nm = __uint_as_float(entry.x) - lds_f32(x_addr[u] + 4u * entry.y);
+      if (l == 0 || fabsf(nm) < fabsf(out[u].nm)) {
+        out[u].nm = nm;
+        out[u].v = KIND == FERN ? (uint32_t)(l + 1) : v[u];
+      }
+      v[u] = __funnelshift_l(__float_as_uint(nm), v[u], 1);
+    });
+  });
+#pragma unroll
+  for (int u = 0; u < NT; ++u) out[u].path = v[u];
+}
+
 struct ConvBwdPlan {
   int TY;  // tile rows; slots = kWarps / TY input channels in progress
   int JJ;  // output channels per parameter group
   int patch_h, patch_w, cells, table_len;
   int ord_bytes;
+  bool pairs;  // records with one 8-byte entry per vertex
   RecordLayout rec;
   size_t smem;
 };
@@ -65,7 +139,8 @@ __host__ __device__ inline Carve carve(int Ci, int patch_elems, int slots, int J
   return c;
 }
 
-bool make_plan(const ConvTileProblem &p, ConvBwdPlan &plan) {
+bool make_plan(const ConvTileProblem &p, ConvBwdPlan &plan, bool pairs) {
+  plan.pairs = pairs;
   if (p.depth > 10 || p.Ci < 1 || p.Co < 1 || p.B < 1 || p.Ho < 1 || p.Wo < 1) return false;
   if ((double)p.B * p.Ho * p.Wo * (double)p.Co * p.Ci < 1048576.0) return false;
   const int bins_per_tree = (int)(threshold_count(p.kind, p.depth) + (((int64_t)1) << p.depth));
@@ -80,7 +155,7 @@ bool make_plan(const ConvTileProblem &p, ConvBwdPlan &plan) {
     plan.patch_w = shape.w;
     plan.table_len = (int)shape.far + 1;
     plan.ord_bytes = shape.far <= 255 ? 1 : 2;
-    plan.rec = record_layout(p.kind, p.depth, (uint32_t)plan.ord_bytes);
+    plan.rec = pairs ? vertex_pair_layout(p.kind, p.depth) : record_layout(p.kind, p.depth, (uint32_t)plan.ord_bytes);
     const int slots = kWarps / TY;
     for (int JJ = 16; JJ >= 4; JJ >>= 1) {
       plan.JJ = JJ;
@@ -102,10 +177,18 @@ struct ConvBwdArgs {
   RecordMap map;
 };
 
-template <int KIND, int DEPTH, typename OrdT>
+// The window-cell offset that vertex v of the record tests.
+template <typename OrdT, bool PAIRS>
+__device__ __forceinline__ uint32_t offset_of_vertex(uint32_t rec, uint32_t v, uint32_t ord_at) {
+  if (PAIRS) return lds_b32(rec + 8u * v + 4u);
+  return lds_ord<OrdT>(rec + (uint32_t)sizeof(OrdT) * v + (ord_at - (uint32_t)sizeof(OrdT)));
+}
+
+// PAIRS: the records have one 8-byte entry per vertex (OrdT is then unused).
+template <int KIND, int DEPTH, typename OrdT, bool PAIRS>
 __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+  constexpr RecordLayout lay = PAIRS ? vertex_pair_layout(KIND, DEPTH) : record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
   constexpr uint32_t kN = KIND == FERN ? DEPTH : (1u << DEPTH) - 1u;
   constexpr uint32_t kL = 1u << DEPTH;
   constexpr int kBins = (int)(kN + kL);  // per tree: threshold bins, then leaf bins in path order
@@ -206,7 +289,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
           if (position_valid && jl + u < count_j) gval[u] = __ldg(g_chunk + u * g_plane);
         }
         Walked wk[4];
-        walk_full<KIND, DEPTH, OrdT, 4>(rec, x_addr, 4u, wk);
+        if constexpr (PAIRS) {
+          const uint32_t origins[4] = {x_addr, x_addr, x_addr, x_addr};
+          walk_vertex_pairs<KIND, DEPTH, 4>(rec, origins, wk);
+        } else {
+          walk_full<KIND, DEPTH, OrdT, 4>(rec, x_addr, 4u, wk);
+        }
         if (!bins_wanted) {
           // The image gradient alone (the parameter gradients came from the kernel further down).  A walk past the
           // last output channel repeats that channel's record with a zero upstream gradient and adds a zero.
@@ -215,7 +303,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
             for (int u = 0; u < 4; ++u) {
               const float wg = __fmul_rn(lds_f32(rec[u] + 4u * wk[u].path + (lay.w - 4u * kL)), gval[u]);
               const float dx = wk[u].nm < 0.0f ? wg : (wk[u].nm > 0.0f ? -wg : __fmul_rn(0.0f, wg));
-              const uint32_t off = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * wk[u].v + (lay.ord - (uint32_t)sizeof(OrdT)));
+              const uint32_t off = offset_of_vertex<OrdT, PAIRS>(rec[u], wk[u].v, lay.ord);
               const uint32_t cell_addr = my_cells_addr + (uint32_t)cell_of[off] * 128u;
               sts_f32(cell_addr, __fadd_rn(lds_f32(cell_addr), dx));
             }
@@ -233,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
             if (!position_valid) dx = dw = 0.0f;
             float *tree_bins = my_bins + (jl + u) * kBins;
             if (a.gx != nullptr && position_valid) {
-              const uint32_t off = lds_ord<OrdT>(rec[u] + (uint32_t)sizeof(OrdT) * wk[u].v + (lay.ord - (uint32_t)sizeof(OrdT)));
+              const uint32_t off = offset_of_vertex<OrdT, PAIRS>(rec[u], wk[u].v, lay.ord);
               const uint32_t cell_addr = my_cells_addr + (uint32_t)cell_of[off] * 128u;
               sts_f32(cell_addr, __fadd_rn(lds_f32(cell_addr), dx));
             }
@@ -317,11 +405,16 @@ struct ParamGradPlan {
   int columns;  // lanes' columns per bin: 16, 8 or 4
   int staged;   // input channels whose patches are staged together
   int patch_h, patch_w, ord_bytes;
+  bool pairs;
   RecordLayout rec;
   size_t smem;
 };
 
-bool make_param_plan(const ConvTileProblem &p, ParamGradPlan &plan) {
+// Record groups in flight or in use: with three, a warp runs up to two groups ahead of the slowest before it waits.
+constexpr int kParamBuffers = 3;
+
+bool make_param_plan(const ConvTileProblem &p, ParamGradPlan &plan, bool pairs) {
+  plan.pairs = pairs;
   if (p.depth > 7 || p.Ci < 1 || p.Co < 1 || p.B < 1 || p.Ho < 1 || p.Wo < 1) return false;
   if ((double)p.B * p.Ho * p.Wo * (double)p.Co * p.Ci < 1048576.0) return false;
   const int bins_per_tree = (int)(threshold_count(p.kind, p.depth) + (((int64_t)1) << p.depth));
@@ -333,10 +426,10 @@ bool make_param_plan(const ConvTileProblem &p, ParamGradPlan &plan) {
   plan.patch_h = shape.h;
   plan.patch_w = shape.w;
   plan.ord_bytes = shape.far <= 255 ? 1 : 2;
-  plan.rec = record_layout(p.kind, p.depth, (uint32_t)plan.ord_bytes);
+  plan.rec = pairs ? vertex_pair_layout(p.kind, p.depth) : record_layout(p.kind, p.depth, (uint32_t)plan.ord_bytes);
   // Every warp waits while patches are staged, so as many input channels as fit (16 at most) are staged at a time.
   for (plan.staged = (int)std::min<int64_t>(p.Ci, 16); plan.staged >= 1; --plan.staged) {
-    plan.smem = align_up((size_t)plan.staged * shape.h * shape.w * 4, 128) + 2 * (size_t)kWarps * plan.rec.bytes +
+    plan.smem = align_up((size_t)plan.staged * shape.h * shape.w * 4, 128) + kParamBuffers * (size_t)kWarps * plan.rec.bytes +
                 (size_t)kWarps * bins_per_tree * plan.columns * 4 + 64;
     if (plan.smem <= kSmemBudget) return true;
   }
@@ -353,10 +446,10 @@ struct ParamGradArgs {
   int R, columns, staged, patch_h, patch_w, tiles_x, row_blocks;
 };
 
-template <int KIND, int DEPTH, typename OrdT>
+template <int KIND, int DEPTH, typename OrdT, bool PAIRS>
 __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel(ParamGradArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr RecordLayout lay = record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
+  constexpr RecordLayout lay = PAIRS ? vertex_pair_layout(KIND, DEPTH) : record_layout(KIND, DEPTH, (uint32_t)sizeof(OrdT));
   constexpr uint32_t kN = KIND == FERN ? DEPTH : (1u << DEPTH) - 1u;
   constexpr uint32_t kL = 1u << DEPTH;
   constexpr int kBins = (int)(kN + kL);  // threshold bins, then leaf bins in path order
@@ -364,9 +457,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
   const int patch_elems = a.patch_h * a.patch_w;
   float *patch = reinterpret_cast<float *>(smem);
   unsigned char *params = smem + (((size_t)a.staged * patch_elems * 4 + 127) & ~(size_t)127);
-  float *bins = reinterpret_cast<float *>(params + 2 * (size_t)kWarps * lay.bytes);  // [kWarps][kBins][columns]
+  float *bins = reinterpret_cast<float *>(params + kParamBuffers * (size_t)kWarps * lay.bytes);  // [kWarps][kBins][columns]
   uint64_t *full = reinterpret_cast<uint64_t *>(bins + (size_t)kWarps * kBins * columns);
-  uint32_t *finished = reinterpret_cast<uint32_t *>(full + 2);
+  uint32_t *finished = reinterpret_cast<uint32_t *>(full + kParamBuffers);
 
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -389,19 +482,19 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
     const int c = it / my_rounds;
     const int j_first = (round0 + it % my_rounds) * kWarps;
     const uint32_t bytes = (uint32_t)min(kWarps, a.Co - j_first) * lay.bytes;
-    uint64_t *bar = &full[it & 1];
+    uint64_t *bar = &full[it % kParamBuffers];
     mbar_expect_tx(bar, bytes);
-    bulk_load(params_addr + (uint32_t)(it & 1) * buffer_bytes, a.records + ((int64_t)c * a.Co + j_first) * lay.bytes, bytes,
+    bulk_load(params_addr + (uint32_t)(it % kParamBuffers) * buffer_bytes, a.records + ((int64_t)c * a.Co + j_first) * lay.bytes, bytes,
               bar);
   };
   if (tid == 0) {
-    mbar_init(&full[0], 1);
-    mbar_init(&full[1], 1);
-    finished[0] = 0;
-    finished[1] = 0;
+    for (int k = 0; k < kParamBuffers; ++k) {
+      mbar_init(&full[k], 1);
+      finished[k] = 0;
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    if (num_groups > 0) issue(0);
-    if (num_groups > 1) issue(1);
+    for (int k = 0; k < kParamBuffers; ++k)
+      if (k < num_groups) issue(k);
   }
   for (int i = tid; i < kWarps * kBins * columns; i += kThreads) bins[i] = 0.0f;
 
@@ -425,13 +518,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
       __syncthreads();
     }
     const uint32_t channel_addr = lane_addr + (uint32_t)(c % a.staged) * (uint32_t)patch_elems * 4u;
-    if (!poisoned && !mbar_wait(&full[it & 1], (uint32_t)((it >> 1) & 1))) {
+    if (!poisoned && !mbar_wait(&full[it % kParamBuffers], (uint32_t)((it / kParamBuffers) & 1))) {
       poisoned = true;
       if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
     }
     const int j = (round0 + it % my_rounds) * kWarps + warp;
     if (j < a.Co && !poisoned) {
-      const uint32_t record = params_addr + (uint32_t)(it & 1) * buffer_bytes + (uint32_t)warp * lay.bytes;
+      const uint32_t record = params_addr + (uint32_t)(it % kParamBuffers) * buffer_bytes + (uint32_t)warp * lay.bytes;
       const float *g_rows = a.g + ((b * a.Co + j) * a.Ho + oy0) * (int64_t)a.Wo + ox;
       for (int row0 = 0; row0 < rows_here; row0 += 4) {
         uint32_t rec[4], x_addr[4];
@@ -443,7 +536,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
           gval[u] = (row0 + u < rows_here && ox < a.Wo) ? __ldg(g_rows + (int64_t)(row0 + u) * a.Wo) : 0.0f;
         }
         Walked wk[4];
-        walk_full<KIND, DEPTH, OrdT, 4>(rec, x_addr, 4u, wk);
+        if constexpr (PAIRS)
+          walk_vertex_pairs<KIND, DEPTH, 4>(rec, x_addr, wk);
+        else
+          walk_full<KIND, DEPTH, OrdT, 4>(rec, x_addr, 4u, wk);
         float term_thr[4], term_w[4];
         uint32_t at_thr[4], at_w[4];
 #pragma unroll
@@ -520,11 +616,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
     __syncwarp();
     if (lane == 0) {
       __threadfence_block();
-      const uint32_t before = atomicAdd(&finished[it & 1], 1u);
+      const uint32_t before = atomicAdd(&finished[it % kParamBuffers], 1u);
       if (before == kWarps - 1) {
-        atomicExch(&finished[it & 1], 0u);
+        atomicExch(&finished[it % kParamBuffers], 0u);
         __threadfence_block();
-        if (it + 2 < num_groups) issue(it + 2);
+        if (it + kParamBuffers < num_groups) issue(it + kParamBuffers);
       }
     }
   }
@@ -540,9 +636,11 @@ int launch_params_one(Kernel kernel, const ParamGradPlan &plan, const ParamGradA
 
 template <int KIND, int DEPTH>
 int launch_params_depth(const ParamGradPlan &plan, const ParamGradArgs &a, dim3 grid, cudaStream_t stream) {
+  if (plan.pairs)
+    return launch_params_one(conv_backward_params_tiled_kernel<KIND, DEPTH, uint32_t, true>, plan, a, grid, stream);
   if (plan.ord_bytes == 1)
-    return launch_params_one(conv_backward_params_tiled_kernel<KIND, DEPTH, uint8_t>, plan, a, grid, stream);
-  return launch_params_one(conv_backward_params_tiled_kernel<KIND, DEPTH, uint16_t>, plan, a, grid, stream);
+    return launch_params_one(conv_backward_params_tiled_kernel<KIND, DEPTH, uint8_t, false>, plan, a, grid, stream);
+  return launch_params_one(conv_backward_params_tiled_kernel<KIND, DEPTH, uint16_t, false>, plan, a, grid, stream);
 }
 
 template <int KIND>
@@ -574,8 +672,9 @@ int launch_one(Kernel kernel, const ConvBwdPlan &plan, const ConvBwdArgs &a, dim
 
 template <int KIND, int DEPTH>
 int launch_depth(const ConvBwdPlan &plan, const ConvBwdArgs &a, dim3 grid, cudaStream_t stream) {
-  if (plan.ord_bytes == 1) return launch_one(conv_backward_tiled_kernel<KIND, DEPTH, uint8_t>, plan, a, grid, stream);
-  return launch_one(conv_backward_tiled_kernel<KIND, DEPTH, uint16_t>, plan, a, grid, stream);
+  if (plan.pairs) return launch_one(conv_backward_tiled_kernel<KIND, DEPTH, uint32_t, true>, plan, a, grid, stream);
+  if (plan.ord_bytes == 1) return launch_one(conv_backward_tiled_kernel<KIND, DEPTH, uint8_t, false>, plan, a, grid, stream);
+  return launch_one(conv_backward_tiled_kernel<KIND, DEPTH, uint16_t, false>, plan, a, grid, stream);
 }
 
 template <int KIND>
@@ -600,11 +699,30 @@ int launch_kind(int depth, const ConvBwdPlan &plan, const ConvBwdArgs &a, dim3 g
   }
 }
 
+// Both kernels read one set of records.  The form with 8-byte vertex entries is taken when it costs neither kernel
+// anything: the same tile and group sizes for the image-gradient kernel, and the parameter kernel still available.
+bool choose_plans(const ConvTileProblem &p, ConvBwdPlan &plan, ParamGradPlan &pplan, bool &with_params) {
+  if (!make_plan(p, plan, false)) return false;
+  auto shared_records = [&]() { return pplan.patch_w == plan.patch_w && (plan.pairs || pplan.ord_bytes == plan.ord_bytes); };
+  with_params = make_param_plan(p, pplan, false) && shared_records();
+  ConvBwdPlan wide;
+  ParamGradPlan wide_params;
+  if (make_plan(p, wide, true) && wide.TY == plan.TY && wide.JJ == plan.JJ &&
+      (!with_params || (make_param_plan(p, wide_params, true) && wide_params.patch_w == wide.patch_w &&
+                        wide_params.staged == pplan.staged))) {
+    plan = wide;
+    if (with_params) pplan = wide_params;
+  }
+  return true;
+}
+
 }  // namespace
 
 size_t conv_backward_tiled_workspace_bytes(const ConvTileProblem &p) {
   ConvBwdPlan plan;
-  if (!make_plan(p, plan)) return 0;
+  ParamGradPlan pplan;
+  bool with_params;
+  if (!choose_plans(p, plan, pplan, with_params)) return 0;
   return align_up((size_t)(p.Co * p.Ci) * plan.rec.bytes, 256);
 }
 
@@ -612,7 +730,9 @@ int conv_backward_tiled(const ConvTileProblem &p, const float *x, const float *t
                         const float *g, float *gx, float *gthr, float *gw, void *records, uint32_t *status_word,
                         cudaStream_t stream) {
   ConvBwdPlan plan;
-  if (!make_plan(p, plan)) return HT_ERR_UNSUPPORTED;
+  ParamGradPlan pplan;
+  bool with_params;
+  if (!choose_plans(p, plan, pplan, with_params)) return HT_ERR_UNSUPPORTED;
   const int tiles_x = (p.Wo + kTileColumns - 1) / kTileColumns, tiles_y = (p.Ho + plan.TY - 1) / plan.TY;
   const int64_t ctas = p.B * tiles_x * tiles_y;
   if (ctas > 0x7fffffff) return HT_ERR_UNSUPPORTED;
@@ -628,7 +748,9 @@ int conv_backward_tiled(const ConvTileProblem &p, const float *x, const float *t
   map.column_step = p.dx;
   map.inner = p.Ci;  // tree (j, c) goes to record c * Co + j
   map.outer_count = p.Co;
-  if (plan.ord_bytes == 1)
+  if (plan.pairs)
+    repack_vertex_pairs_kernel<<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p.kind, p.depth, trees, plan.rec, map);
+  else if (plan.ord_bytes == 1)
     repack_records_kernel<uint8_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p.kind, p.depth, trees, plan.rec, map);
   else
     repack_records_kernel<uint16_t><<<pack_grid, 256, 0, stream>>>(thr, ord, w, rec, p.kind, p.depth, trees, plan.rec, map);
@@ -636,9 +758,7 @@ int conv_backward_tiled(const ConvTileProblem &p, const float *x, const float *t
 
   // Shallow trees: the parameter gradients come from the kernel built for them, and the kernel
   // below is left with the image gradient.
-  ParamGradPlan pplan;
-  if ((gthr != nullptr || gw != nullptr) && make_param_plan(p, pplan) && pplan.patch_w == plan.patch_w &&
-      pplan.ord_bytes == plan.ord_bytes) {
+  if ((gthr != nullptr || gw != nullptr) && with_params) {
     ParamGradArgs pa;
     pa.x = x;
     pa.records = rec;
