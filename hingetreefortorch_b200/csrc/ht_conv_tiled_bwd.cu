@@ -263,9 +263,14 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
   const float *g_here = a.g + b * a.Co * g_plane + (position_valid ? (int64_t)oy * a.Wo + ox : 0);
   bool poisoned = false;
 
+  // chunk = it % j_chunks and block = it / j_chunks, counted instead of divided
+  int chunk = -1, block = 0;
   for (int it = 0; it < num_groups; ++it) {
-    const int c_first = (block0 + it / j_chunks) * slots;
-    const int chunk = it % j_chunks;
+    if (++chunk == j_chunks) {
+      chunk = 0;
+      ++block;
+    }
+    const int c_first = (block0 + block) * slots;
     const int j_first = chunk * JJ;
     const int count_c = min(slots, a.Ci - c_first), count_j = min(JJ, a.Co - j_first);
     const int c = c_first + slot;
@@ -302,7 +307,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               const float wg = __fmul_rn(lds_f32(rec[u] + 4u * wk[u].path + (lay.w - 4u * kL)), gval[u]);
-              const float dx = wk[u].nm < 0.0f ? wg : (wk[u].nm > 0.0f ? -wg : __fmul_rn(0.0f, wg));
+              const float dx = signed_term(wk[u].nm, wg);
               const uint32_t off = offset_of_vertex<OrdT, PAIRS>(rec[u], wk[u].v, lay.ord);
               const uint32_t cell_addr = my_cells_addr + (uint32_t)cell_of[off] * 128u;
               sts_f32(cell_addr, __fadd_rn(lds_f32(cell_addr), dx));
@@ -316,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
             const float wv = lds_f32(rec[u] + 4u * wk[u].path + (lay.w - 4u * kL));
             const float wg = __fmul_rn(wv, gval[u]);
             // sign(margin) * w * g with margin = -nm
-            float dx = wk[u].nm < 0.0f ? wg : (wk[u].nm > 0.0f ? -wg : __fmul_rn(0.0f, wg));
+            float dx = signed_term(wk[u].nm, wg);
             float dw = __fmul_rn(fabsf(wk[u].nm), gval[u]);
             if (!position_valid) dx = dw = 0.0f;
             float *tree_bins = my_bins + (jl + u) * kBins;
@@ -395,10 +400,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
 // long chains of colliding updates.  This kernel gives every warp ONE tree and lets it walk that
 // tree over all R x 32 positions of the tile itself (4 rows in flight): a lane adds its terms into
 // its own column of the warp's bin array [bin][column] with plain loads and stores — lanes that
-// share a column (32 / kColumns of them) take turns — and only after the last row the columns are
-// summed and each touched bin leaves as one global reduction.  No atomics on shared memory, and
-// R x 32 evaluations per tree and CTA share one flush.  The image patch of the current input
-// channel only is staged (all warps work on the same channel), so R can be large.
+// share a column (32 / columns of them) never update it together: one group adds its threshold
+// terms while its neighbour adds its leaf terms, then they swap — and only after the last row the
+// columns are summed (16 bytes at a time) and each touched bin leaves as one global reduction.  No
+// atomics on shared memory, and R x 32 evaluations per tree and CTA share one flush.  All warps work
+// on the same input channel, so only that channel's patch is needed and R can be large; the patches
+// of up to 16 channels are staged at a time, since every warp waits while that is done.  Records
+// come in three buffers: a warp runs up to two groups ahead of the slowest before it waits.
 
 struct ParamGradPlan {
   int R;        // tile rows
@@ -509,23 +517,30 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
   const bool want_thr = a.gthr != nullptr, want_w = a.gw != nullptr;
   bool poisoned = false;
 
-  for (int it = 0; it < num_groups; ++it) {
-    const int c = it / my_rounds;
-    if (it % (my_rounds * a.staged) == 0) {  // next input channels: every warp is done with the previous patches
+  // c: the group's input channel = it / my_rounds; round = it % my_rounds; channel_slot = c % a.staged (counted, not divided)
+  int c = 0, round = 0, channel_slot = 0;
+  for (int it = 0; it < num_groups; ++it, ++round) {
+    if (round == my_rounds) {
+      round = 0;
+      ++c;
+      if (++channel_slot == a.staged) channel_slot = 0;
+    }
+    if (round == 0 && channel_slot == 0) {  // next input channels: every warp is done with the previous patches
       __syncthreads();
       stage_patches(patch, image + (int64_t)c * a.H * a.W, min(a.staged, a.Ci - c), a.H, a.W, oy0 * a.sy - a.py,
                     ox0 * a.sx - a.px, a.patch_h, a.patch_w);
       __syncthreads();
     }
-    const uint32_t channel_addr = lane_addr + (uint32_t)(c % a.staged) * (uint32_t)patch_elems * 4u;
+    const uint32_t channel_addr = lane_addr + (uint32_t)channel_slot * (uint32_t)patch_elems * 4u;
     if (!poisoned && !mbar_wait(&full[it % kParamBuffers], (uint32_t)((it / kParamBuffers) & 1))) {
       poisoned = true;
       if (a.status_word != nullptr) atomicOr(a.status_word, HT_FLAG_PIPELINE_TIMEOUT);
     }
-    const int j = (round0 + it % my_rounds) * kWarps + warp;
+    const int j = (round0 + round) * kWarps + warp;
     if (j < a.Co && !poisoned) {
       const uint32_t record = params_addr + (uint32_t)(it % kParamBuffers) * buffer_bytes + (uint32_t)warp * lay.bytes;
-      const float *g_rows = a.g + ((b * a.Co + j) * a.Ho + oy0) * (int64_t)a.Wo + ox;
+      // lanes and rows off the output read the last valid element instead and have their terms cleared below
+      const float *g_rows = a.g + ((b * a.Co + j) * a.Ho + oy0) * (int64_t)a.Wo + min(ox, a.Wo - 1);
       for (int row0 = 0; row0 < rows_here; row0 += 4) {
         uint32_t rec[4], x_addr[4];
         float gval[4];
@@ -533,7 +548,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
         for (int u = 0; u < 4; ++u) {
           rec[u] = record;
           x_addr[u] = channel_addr + (uint32_t)(row0 + u) * row_bytes;
-          gval[u] = (row0 + u < rows_here && ox < a.Wo) ? __ldg(g_rows + (int64_t)(row0 + u) * a.Wo) : 0.0f;
+          gval[u] = __ldg(g_rows + (int64_t)min(row0 + u, rows_here - 1) * a.Wo);
         }
         Walked wk[4];
         if constexpr (PAIRS)
@@ -547,7 +562,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
           const float wv = lds_f32(record + 4u * wk[u].path + (lay.w - 4u * kL));
           const float wg = __fmul_rn(wv, gval[u]);
           // the threshold term is -sign(margin) * w * g with margin = -nm
-          term_thr[u] = wk[u].nm < 0.0f ? -wg : (wk[u].nm > 0.0f ? wg : __fmul_rn(-0.0f, wg));
+          term_thr[u] = -signed_term(wk[u].nm, wg);
           term_w[u] = __fmul_rn(fabsf(wk[u].nm), gval[u]);
           if (!(row0 + u < rows_here && ox < a.Wo)) term_thr[u] = term_w[u] = 0.0f;
           at_thr[u] = my_bins_addr + (wk[u].v - 1u) * bin_bytes;

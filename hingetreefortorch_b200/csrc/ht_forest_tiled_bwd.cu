@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(cons
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const float wg = __fmul_rn(lds_f32(rec[u] + 4u * wk[u].path + (lay.w - 4u * kL)), gval[u]);
-          const float dx = wk[u].nm < 0.0f ? wg : (wk[u].nm > 0.0f ? -wg : __fmul_rn(0.0f, wg));
+          const float dx = signed_term(wk[u].nm, wg);
           const uint32_t key = __brev(wk[u].path - kL) >> (32 - DEPTH);
           if (row_valid) {
             __stcs(a.evals.dx + at + u * kRecordBlock, dx);
@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_kernel(cons
         const float wv = lds_f32(rec + 4u * wk.path + (lay.w - 4u * kL));
         // sign(margin) * w * g with margin = -nm
         const float wg = __fmul_rn(wv, gv);
-        const float dx = wk.nm < 0.0f ? wg : (wk.nm > 0.0f ? -wg : __fmul_rn(0.0f, wg));
+        const float dx = signed_term(wk.nm, wg);
         if (RECORDS) {
           const uint32_t key = __brev(wk.path - kL) >> (32 - DEPTH);
           const int64_t at = my_records + j * kRecordBlock;
@@ -877,7 +877,7 @@ __global__ void __launch_bounds__(256) expand_saved_kernel(const __grid_constant
 #pragma unroll
       for (int u = 0; u < kSavedBatch; ++u) {
         const float wg = __fmul_rn(wv[u], gv[u]);
-        const float dx = nm[u] < 0.0f ? wg : (nm[u] > 0.0f ? -wg : __fmul_rn(0.0f, wg));
+        const float dx = signed_term(nm[u], wg);
         if (a.write_terms) {
           __stcs(terms_dx + u * kRecordBlock, dx);
           __stcs(terms_dw + u * kRecordBlock, __fmul_rn(fabsf(nm[u]), gv[u]));

@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 1) forest_backward_tiled_multi_kerne
       for (int u = 0; u < 4; ++u) {
         if (u < trees_here) {
           const float d = dots[lane * 4 + u];
-          const float dx = wk[u].nm < 0.0f ? d : (wk[u].nm > 0.0f ? -d : __fmul_rn(0.0f, d));  // margin = -nm
+          const float dx = signed_term(wk[u].nm, d);  // margin = -nm
           if (a.gx != nullptr) atomicAdd(a.gx + my_row * C + feature[u], dx);
           if (a.gthr != nullptr) atomicAdd(a.gthr + (col0 + t_first + u) * kN + (wk[u].v - 1u), -dx);
         }

@@ -369,6 +369,14 @@ struct Walked {
   uint32_t path; // 2^DEPTH + path bits, root first (most significant)
 };
 
+// sign(margin) * wg with margin = -nm: wg, -wg, or 0 * wg where the margin is zero or not a number.  Written with
+// both values at hand so that it compiles to selects (the nested conditional became a divergent branch per evaluation).
+__device__ __forceinline__ float signed_term(float nm, float wg) {
+  const float off_zero = nm < 0.0f ? wg : -wg;
+  const float at_zero = __fmul_rn(0.0f, wg);
+  return (nm < 0.0f || nm > 0.0f) ? off_zero : at_zero;
+}
+
 // rec[u] and x_addr[u]: record and feature base (shared-memory addresses) of the u-th walk in flight.
 // PAIRED: the records hold the feature indices in the paired form (see paired_ordinals).
 template <int KIND, int DEPTH, typename OrdT, int NT, bool PAIRED = false, bool WITH_FEATURE = false>
