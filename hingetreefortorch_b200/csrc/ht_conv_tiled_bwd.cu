@@ -425,7 +425,8 @@ bool make_param_plan(const ConvTileProblem &p, ParamGradPlan &plan, bool pairs) 
   plan.pairs = pairs;
   if (p.depth > 7 || p.Ci < 1 || p.Co < 1 || p.B < 1 || p.Ho < 1 || p.Wo < 1) return false;
   if ((double)p.B * p.Ho * p.Wo * (double)p.Co * p.Ci < 1048576.0) return false;
-  const int bins_per_tree = (int)(threshold_count(p.kind, p.depth) + (((int64_t)1) << p.depth));
+  // a warp's bins: 2^depth rows of {threshold bin, leaf bin}, `columns` lanes' columns each
+  const int bins_per_tree = 2 << p.depth;
   plan.columns = 16;
   while (plan.columns > 4 && bins_per_tree * plan.columns * 4 > 4096) plan.columns >>= 1;
   plan.R = std::min(16, (p.Ho + 3) & ~3);
@@ -465,8 +466,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
   const int patch_elems = a.patch_h * a.patch_w;
   float *patch = reinterpret_cast<float *>(smem);
   unsigned char *params = smem + (((size_t)a.staged * patch_elems * 4 + 127) & ~(size_t)127);
-  float *bins = reinterpret_cast<float *>(params + kParamBuffers * (size_t)kWarps * lay.bytes);  // [kWarps][kBins][columns]
-  uint64_t *full = reinterpret_cast<uint64_t *>(bins + (size_t)kWarps * kBins * columns);
+  // [kWarps][2^DEPTH rows][threshold bin | leaf bin][columns]: with 16 columns a row is the 32 banks, the lanes adding
+  // threshold terms use one half and the lanes adding leaf terms the other, and no two of them meet in a bank
+  float *bins = reinterpret_cast<float *>(params + kParamBuffers * (size_t)kWarps * lay.bytes);
+  uint64_t *full = reinterpret_cast<uint64_t *>(bins + (size_t)kWarps * 2 * kL * columns);
   uint32_t *finished = reinterpret_cast<uint32_t *>(full + kParamBuffers);
 
   const int tid = threadIdx.x;
@@ -504,13 +507,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
     for (int k = 0; k < kParamBuffers; ++k)
       if (k < num_groups) issue(k);
   }
-  for (int i = tid; i < kWarps * kBins * columns; i += kThreads) bins[i] = 0.0f;
+  for (int i = tid; i < kWarps * 2 * (int)kL * columns; i += kThreads) bins[i] = 0.0f;
 
   const int ox = ox0 + lane;
   const uint32_t lane_addr = smem_addr(patch) + (uint32_t)(lane * a.sx) * 4u;
   const uint32_t row_bytes = (uint32_t)(a.sy * a.patch_w) * 4u;
-  const uint32_t my_bins_addr = smem_addr(bins) + (uint32_t)(warp * kBins * columns + lane % columns) * 4u;
-  const uint32_t bin_bytes = (uint32_t)columns * 4u;
+  const uint32_t my_bins_addr = smem_addr(bins) + (uint32_t)(warp * 2 * (int)kL * columns + lane % columns) * 4u;
+  const uint32_t bin_bytes = (uint32_t)columns * 4u, row_bytes_of_bins = 2u * bin_bytes;
   const int turns = 32 / columns, group = lane / columns;
   const int rows_here = min(R, a.Ho - oy0);
   const float *image = a.x + b * a.Ci * (int64_t)a.H * a.W;
@@ -565,8 +568,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
           term_thr[u] = -signed_term(wk[u].nm, wg);
           term_w[u] = __fmul_rn(fabsf(wk[u].nm), gval[u]);
           if (!(row0 + u < rows_here && ox < a.Wo)) term_thr[u] = term_w[u] = 0.0f;
-          at_thr[u] = my_bins_addr + (wk[u].v - 1u) * bin_bytes;
-          at_w[u] = my_bins_addr + (kN + wk[u].path - kL) * bin_bytes;
+          at_thr[u] = my_bins_addr + (wk[u].v - 1u) * row_bytes_of_bins;
+          at_w[u] = my_bins_addr + bin_bytes + (wk[u].path - kL) * row_bytes_of_bins;
         }
         // Lanes that share a column (32 / columns of them, `group` apart) must not update it together.  Every term
         // is added, zeros included: a test per term costs a divergent branch each, more than the addition it would
@@ -609,13 +612,14 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_params_tiled_kernel
       }
       // sum the columns of every bin, clear them, send the touched bins out
       const int64_t tree = (int64_t)j * a.Ci + c;
-      const uint32_t warp_bins_addr = smem_addr(bins) + (uint32_t)(warp * kBins * columns) * 4u;
+      const uint32_t warp_bins_addr = smem_addr(bins) + (uint32_t)(warp * 2 * (int)kL * columns) * 4u;
       const int quads = columns >> 2;  // columns is 16, 8 or 4: a bin is 1 to 4 aligned 16-byte pieces
       for (int bin = lane; bin < kBins; bin += 32) {
         float sum = 0.0f;
         for (int k = 0; k < quads; ++k) {
           const int quad = (k + lane) & (quads - 1);  // rotated so that the lanes spread over the banks
-          const uint32_t at = warp_bins_addr + (uint32_t)(bin * columns + 4 * quad) * 4u;
+          const int piece = bin < (int)kN ? 2 * bin : 2 * (bin - (int)kN) + 1;  // threshold bins in the even halves of the rows
+          const uint32_t at = warp_bins_addr + (uint32_t)(piece * columns + 4 * quad) * 4u;
           const uint4 v = lds_b128(at);
           sum += (__uint_as_float(v.x) + __uint_as_float(v.y)) + (__uint_as_float(v.z) + __uint_as_float(v.w));
           sts_b128(at, 0.0f, 0.0f, 0.0f, 0.0f);
