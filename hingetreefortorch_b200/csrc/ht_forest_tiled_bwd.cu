@@ -559,14 +559,16 @@ __global__ void __launch_bounds__(512, 1) reduce_parameter_records_columns_kerne
 }
 
 // Default mode, trees whose bins fit 16 times into a sixth of the shared memory: ONE warp per CTA with
-// COLUMNS copies of the tree's bins, [bin][column].  With 32 columns a lane would own its column outright;
-// with 16 (the form launched), lanes l and l + 16 share one and take two turns.  Either way the lanes that
-// are active together hit distinct banks whatever bins they update, so every load and store is one
-// wavefront for up to 32 terms (the 8-column form above pays a wavefront per 8 terms and a conflict
-// on top).  A lane consumes its records four at a time: the eight bin loads are in flight together,
-// the sums are chained in record order (a later record that hits the bin of an earlier one of the four
-// continues from its sum), and the stores leave in order, so each lane's column holds exactly the
-// sequential sum of its terms.  The samples are split over gridDim.y; a CTA adds its column totals (in a
+// COLUMNS copies of the tree's bins, rows of {threshold bin r | leaf bin r} x COLUMNS.  With 32 columns a
+// lane would own its column outright; with 16 (the form launched) lanes l and l + 16 share one and never
+// update it together: while the lower half-warp adds its threshold terms the upper adds its leaf terms,
+// then they swap (taking turns instead left half the lanes idle in every instruction: 3.3 against 3.1 ms
+// on 2^30 records).  A row is the 32 banks, one half per kind, so the lanes that are active together hit
+// distinct banks whatever bins they update and every load and store is one wavefront for 32 terms (the
+// 8-column form above pays a wavefront per 8 terms and a conflict on top).  A lane consumes its records
+// four at a time: the bin loads of a kind are in flight together, the sums are chained in record order (a
+// later record that hits the bin of an earlier one of the four continues from its sum), and the stores
+// leave in order, so each lane's column holds exactly the sequential sum of its terms.  The samples are split over gridDim.y; a CTA adds its column totals (in a
 // fixed order per bin) to the gradient with one global reduction per bin, or stores them when there is one split.
 template <int COLUMNS, int CHUNKS, typename WT>
 __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(EvalRecords r, int64_t B, int64_t T, int N,
@@ -579,10 +581,16 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
   const unsigned lane = threadIdx.x;
   const int bins = N + L;
   const int64_t j = blockIdx.x;
-  for (int t = (int)lane; t < bins * COLUMNS; t += 32) all_bins[t] = 0.0f;
+  for (int t = (int)lane; t < 2 * L * COLUMNS; t += 32) all_bins[t] = 0.0f;  // L rows (N <= L)
   __syncwarp();
+  constexpr uint32_t kHalfBytes = COLUMNS * 4, kRowBytes = 2 * kHalfBytes;
   const uint32_t my_column = smem_addr(all_bins) + (lane % COLUMNS) * 4u;
   const int my_turn = (int)lane / COLUMNS;
+  // two lane groups: the kind a lane adds first (and second), as the half of the row it addresses
+  const bool thr_first = my_turn == 0;
+  const uint32_t first_half = my_column + (thr_first ? 0u : kHalfBytes), second_half = my_column + (thr_first ? kHalfBytes : 0u);
+  const bool first_wanted = thr_first ? gthr != nullptr : gw != nullptr;
+  const bool second_wanted = thr_first ? gw != nullptr : gthr != nullptr;
   const int64_t all_blocks = (B + kRecordBlock - 1) / kRecordBlock;
   const int64_t block_first = (int64_t)blockIdx.y * blocks_per_split;
   const int64_t block_last = min(all_blocks, block_first + blocks_per_split);
@@ -615,39 +623,60 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
     if (blk + kBlocksPerFetch < block_last) fetch(blk + kBlocksPerFetch, na, nb, nwh);
 #pragma unroll
     for (int q = 0; q < CHUNKS; q += 4) {
-      uint32_t at_thr[4], at_w[4];
+      // adds `term` of the lane's four records to the bins at `at`, in record order
+      auto add_four = [&](const uint32_t (&at)[4], const float (&term)[4], bool wanted) {
+        float sum[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sum[u] = lds_f32(at[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int e = 0; e < u; ++e) sum[u] = at[u] == at[e] ? sum[e] : sum[u];  // the latest earlier record on the same bin
+          sum[u] = __fadd_rn(sum[u], term[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (wanted) sts_f32(at[u], sum[u]);
+      };
+      uint32_t row_thr[4], row_w[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const uint32_t where = unpack_where<WT>(wh[q + u]);
-        at_thr[u] = my_column + min((where & 0xffffu) - 1u, (uint32_t)N - 1u) * (uint32_t)(COLUMNS * 4);  // clamped
-        at_w[u] = my_column + ((uint32_t)N + min(where >> 16, (uint32_t)L - 1u)) * (uint32_t)(COLUMNS * 4);
+        row_thr[u] = min((where & 0xffffu) - 1u, (uint32_t)N - 1u);  // clamped
+        row_w[u] = min(where >> 16, (uint32_t)L - 1u);
       }
+      if constexpr (kTurns == 2) {
+        uint32_t at_first[4], at_second[4];
+        float term_first[4], term_second[4];
 #pragma unroll
-      for (int turn = 0; turn < kTurns; ++turn) {
-        if (kTurns == 1 || turn == my_turn) {
-          float st[4], sw[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            st[u] = lds_f32(at_thr[u]);
-            sw[u] = lds_f32(at_w[u]);
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-#pragma unroll
-            for (int e = 0; e < u; ++e) {  // the latest earlier record of the four on the same bin, if any
-              st[u] = at_thr[u] == at_thr[e] ? st[e] : st[u];
-              sw[u] = at_w[u] == at_w[e] ? sw[e] : sw[u];
-            }
-            st[u] = __fadd_rn(st[u], -a[q + u]);
-            sw[u] = __fadd_rn(sw[u], b[q + u]);
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (gthr != nullptr) sts_f32(at_thr[u], st[u]);
-            if (gw != nullptr) sts_f32(at_w[u], sw[u]);
-          }
+        for (int u = 0; u < 4; ++u) {
+          at_first[u] = first_half + (thr_first ? row_thr[u] : row_w[u]) * kRowBytes;
+          at_second[u] = second_half + (thr_first ? row_w[u] : row_thr[u]) * kRowBytes;
+          term_first[u] = thr_first ? -a[q + u] : b[q + u];
+          term_second[u] = thr_first ? b[q + u] : -a[q + u];
         }
-        if (kTurns > 1) __syncwarp();
+        add_four(at_first, term_first, first_wanted);
+        __syncwarp();
+        add_four(at_second, term_second, second_wanted);
+        __syncwarp();
+      } else {
+        uint32_t at_thr[4], at_w[4];
+        float term_thr[4], term_w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          at_thr[u] = my_column + row_thr[u] * kRowBytes;
+          at_w[u] = my_column + kHalfBytes + row_w[u] * kRowBytes;
+          term_thr[u] = -a[q + u];
+          term_w[u] = b[q + u];
+        }
+#pragma unroll
+        for (int turn = 0; turn < kTurns; ++turn) {
+          if (kTurns == 1 || turn == my_turn) {
+            add_four(at_thr, term_thr, gthr != nullptr);
+            add_four(at_w, term_w, gw != nullptr);
+          }
+          if (kTurns > 1) __syncwarp();
+        }
       }
     }
 #pragma unroll
@@ -660,8 +689,9 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
   __syncwarp();
   for (int t = (int)lane; t < bins; t += 32) {
     float sum = 0.0f;
+    const int piece = t < N ? 2 * t : 2 * (t - N) + 1;  // threshold bins in the even halves of the rows
 #pragma unroll 8
-    for (int c = 0; c < COLUMNS; ++c) sum = __fadd_rn(sum, all_bins[t * COLUMNS + ((c + (int)lane) % COLUMNS)]);
+    for (int c = 0; c < COLUMNS; ++c) sum = __fadd_rn(sum, all_bins[piece * COLUMNS + ((c + (int)lane) % COLUMNS)]);
     float *dst = t < N ? (gthr == nullptr ? nullptr : gthr + j * N + t) : (gw == nullptr ? nullptr : gw + j * L + (t - N));
     if (dst == nullptr) continue;
     if (gridDim.y == 1)
@@ -973,10 +1003,9 @@ int reduce_parameters(const ht_forest_problem *p, const EvalRecords &evals, int6
   while (columns > 1 && (size_t)column_warps * (N + L) * columns * 4 > 200 * 1024) columns >>= 1;
   // bins that fit 16 times into a sixth of the shared memory: one warp per CTA, each column shared by two
   // lanes, samples split over gridDim.y so that the machine sees several waves of CTAs
-  const size_t bins = (size_t)(N + L);
-  const int private_columns = bins * 16 * 4 <= 36 * 1024 ? 16 : 0;
+  const int private_columns = 2 * (size_t)L * 16 * 4 <= 36 * 1024 ? 16 : 0;  // L rows of {threshold bin | leaf bin}
   if (private_columns != 0 && samples >= 64 * 1024) {
-    const size_t private_smem = bins * private_columns * 4;
+    const size_t private_smem = 2 * (size_t)L * private_columns * 4;
     const int64_t slots = 148 * (int64_t)(kSmemBudget / (private_smem + 1024));
     const int64_t all_blocks = (samples + kRecordBlock - 1) / kRecordBlock;
     int64_t splits = std::max<int64_t>(1, std::min<int64_t>((6 * slots + p->T - 1) / p->T, all_blocks / 16));
