@@ -802,6 +802,7 @@ __global__ void __launch_bounds__(256) reduce_x_records_kernel(EvalRecords r, co
 // memory: bulk copies) and the box [S samples x 16 trees] of the upstream gradient (a tiled TMA load, 64-byte
 // swizzle: a thread reads the 64 bytes of its own row without bank conflicts).
 constexpr int kSavedBatch = 16;  // trees per batch; the saving forward's tree groups are multiples of it
+constexpr int kJoin = 4;         // x-gradient terms of a thread whose column updates are in flight together (8: slower)
 
 __host__ __device__ inline size_t saved_table_bytes(int64_t N, int64_t L) { return (size_t)kSavedBatch * (size_t)(N + L) * 4; }
 
@@ -904,17 +905,34 @@ __global__ void __launch_bounds__(256) expand_saved_kernel(const __grid_constant
           c[u] = min(lds_b32(o_table + 4u * ((uint32_t)(u * N) + min((where & 0xffffu) - 1u, (uint32_t)N - 1u))),
                      (uint32_t)C - 1u);
       }
+      // The x-gradient terms join the thread's column kJoin at a time: their loads are in flight together, a term
+      // whose feature an earlier one of them had continues from that one's sum, and the stores leave in order
+      // (one dependent load-add-store per term cost a shared-memory round trip each).
 #pragma unroll
-      for (int u = 0; u < kSavedBatch; ++u) {
-        const float wg = __fmul_rn(wv[u], gv[u]);
-        const float dx = signed_term(nm[u], wg);
-        if (a.write_terms) {
-          __stcs(terms_dx + u * kRecordBlock, dx);
-          __stcs(terms_dw + u * kRecordBlock, __fmul_rn(fabsf(nm[u]), gv[u]));
+      for (int q = 0; q < kSavedBatch; q += kJoin) {
+        float dx[kJoin], sum[kJoin];
+        uint32_t at[kJoin];
+#pragma unroll
+        for (int u = 0; u < kJoin; ++u) {
+          const float wg = __fmul_rn(wv[q + u], gv[q + u]);
+          dx[u] = signed_term(nm[q + u], wg);
+          if (a.write_terms) {
+            __stcs(terms_dx + (q + u) * kRecordBlock, dx[u]);
+            __stcs(terms_dw + (q + u) * kRecordBlock, __fmul_rn(fabsf(nm[q + u]), gv[q + u]));
+          }
+          at[u] = column + c[q + u] * pitch;
         }
         if (a.gx != nullptr) {
-          const uint32_t at = column + c[u] * pitch;
-          sts_f32(at, __fadd_rn(lds_f32(at), dx));
+#pragma unroll
+          for (int u = 0; u < kJoin; ++u) sum[u] = lds_f32(at[u]);
+#pragma unroll
+          for (int u = 0; u < kJoin; ++u) {
+#pragma unroll
+            for (int e = 0; e < u; ++e) sum[u] = at[u] == at[e] ? sum[e] : sum[u];
+            sum[u] = __fadd_rn(sum[u], dx[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < kJoin; ++u) sts_f32(at[u], sum[u]);
         }
       }
     }
