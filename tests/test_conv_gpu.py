@@ -37,6 +37,10 @@ CONV_CASES = [
     (2, (1, 4, 60, 64), 80, 3, (), (3, 3), (1, 1), (6, 6), (6, 6)),
     # 1-D: one tile row
     (1, (4, 6, 3000), 16, 6, (), (7,), (1,), (3,), (1,)),
+    # depth 7: the parameter kernel with 4 columns per bin (8 lane groups); depth 8: beyond it, the image-gradient
+    # kernel collects the parameter gradients in its shared bins as well
+    (2, (2, 8, 48, 64), 24, 7, (), (3, 3), (1, 1), (1, 1), (1, 1)),
+    (2, (2, 8, 48, 64), 24, 8, (), (3, 3), (1, 1), (1, 1), (1, 1)),
 ]
 
 

@@ -247,6 +247,28 @@ def test_tile_kernel_backward(cabi, kind, shape):
     assert grad_close(only_x[0], rx, ax)
 
 
+@pytest.mark.parametrize("kind", ["tree", "fern"])
+@pytest.mark.parametrize("depth", [5, 8])
+def test_large_batch_parameter_reduction_with_some_gradients(cabi, kind, depth):
+    """From 65 536 samples on the default-mode parameter reduction keeps 16 lane-owned copies of a tree's bins and
+    lets the two half-warps add different kinds of terms: a ragged batch of that size, with all gradients and with
+    the threshold or the leaf-weight gradient alone."""
+    B, C, T = 65536 + 100, 16, 8
+    x, thr, ord_, w = random_forest_inputs(40 + depth, kind, B, C, (), T, depth, (), quantise=True)
+    g = np.random.default_rng(8).standard_normal((B, T)).astype(np.float32)
+    dx, dthr, dord, dw, dg = dev(x, thr, ord_, w, g)
+    rx, rthr, rw = ho.backward(kind, x, thr, ord_, w, g)
+    ax, athr, aw = ho.backward_magnitudes(kind, x, thr, ord_, w, g)
+    f = cabi.Forest(kind, dx, dw)
+    gx, gthr, gw = f.backward(dx, dthr, dord, dw, dg)
+    assert equal(gx, rx) and grad_close(gthr, rthr, athr) and grad_close(gw, rw, aw)
+    only_thr = f.backward(dx, dthr, dord, dw, dg, need=(False, True, False))
+    assert only_thr[0] is None and only_thr[2] is None and grad_close(only_thr[1], rthr, athr)
+    only_w = f.backward(dx, dthr, dord, dw, dg, need=(False, False, True))
+    assert only_w[0] is None and only_w[1] is None and grad_close(only_w[2], rw, aw)
+    assert f.ordinal_flags() == 0
+
+
 MULTI_OUTPUT_SHAPES = [
     # B, C, T, depth, M: tabular input with several outputs per leaf (tile kernel, weights read from global memory)
     (4096, 256, 20, 10, 10),
