@@ -598,11 +598,22 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
   float a[CHUNKS], b[CHUNKS], na[CHUNKS], nb[CHUNKS];
   uint32_t wh[CHUNKS], nwh[CHUNKS];
   auto fetch = [&](int64_t blk, float (&fa)[CHUNKS], float (&fb)[CHUNKS], uint32_t (&fw)[CHUNKS]) {
+    // whole fetches (all but the last of a split or of the batch) load without a test per chunk
+    const bool whole = blk + kBlocksPerFetch <= block_last && (blk + kBlocksPerFetch) * kRecordBlock <= B;
 #pragma unroll
     for (int h = 0; h < kBlocksPerFetch; ++h) {
       const int64_t first = ((blk + h) * T + j) * kRecordBlock + lane;
       const float *dxs = r.dx + first, *dws = r.dw + first;
       const WT *wheres = static_cast<const WT *>(r.where) + first;
+      if (whole) {
+        static_for<0, 8>([&](auto uu) {
+          constexpr int u = decltype(uu)::value;
+          fa[8 * h + u] = stream_f32_at<32 * u * 4>(dxs);
+          fb[8 * h + u] = stream_f32_at<32 * u * 4>(dws);
+          fw[8 * h + u] = stream_raw_where_at<WT, 32 * u>(wheres);
+        });
+        continue;
+      }
       static_for<0, 8>([&](auto uu) {
         constexpr int u = decltype(uu)::value;
         const bool valid = blk + h < block_last && (blk + h) * kRecordBlock + 32 * u + lane < B;
@@ -617,10 +628,8 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
       });
     }
   };
-  int64_t blk = block_first;
-  if (blk < block_last) fetch(blk, a, b, wh);
-  for (; blk < block_last; blk += kBlocksPerFetch) {
-    if (blk + kBlocksPerFetch < block_last) fetch(blk + kBlocksPerFetch, na, nb, nwh);
+  // the terms of one fetch join the bins
+  auto consume = [&](const float (&ta)[CHUNKS], const float (&tb)[CHUNKS], const uint32_t (&tw)[CHUNKS]) {
 #pragma unroll
     for (int q = 0; q < CHUNKS; q += 4) {
       // adds `term` of the lane's four records to the bins at `at`, in record order
@@ -641,7 +650,7 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
       uint32_t row_thr[4], row_w[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const uint32_t where = unpack_where<WT>(wh[q + u]);
+        const uint32_t where = unpack_where<WT>(tw[q + u]);
         row_thr[u] = min((where & 0xffffu) - 1u, (uint32_t)N - 1u);  // clamped
         row_w[u] = min(where >> 16, (uint32_t)L - 1u);
       }
@@ -652,8 +661,8 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
         for (int u = 0; u < 4; ++u) {
           at_first[u] = first_half + (thr_first ? row_thr[u] : row_w[u]) * kRowBytes;
           at_second[u] = second_half + (thr_first ? row_w[u] : row_thr[u]) * kRowBytes;
-          term_first[u] = thr_first ? -a[q + u] : b[q + u];
-          term_second[u] = thr_first ? b[q + u] : -a[q + u];
+          term_first[u] = thr_first ? -ta[q + u] : tb[q + u];
+          term_second[u] = thr_first ? tb[q + u] : -ta[q + u];
         }
         add_four(at_first, term_first, first_wanted);
         __syncwarp();
@@ -666,8 +675,8 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
         for (int u = 0; u < 4; ++u) {
           at_thr[u] = my_column + row_thr[u] * kRowBytes;
           at_w[u] = my_column + kHalfBytes + row_w[u] * kRowBytes;
-          term_thr[u] = -a[q + u];
-          term_w[u] = b[q + u];
+          term_thr[u] = -ta[q + u];
+          term_w[u] = tb[q + u];
         }
 #pragma unroll
         for (int turn = 0; turn < kTurns; ++turn) {
@@ -679,12 +688,18 @@ __global__ void __launch_bounds__(32) reduce_parameter_records_private_kernel(Ev
         }
       }
     }
-#pragma unroll
-    for (int u = 0; u < CHUNKS; ++u) {
-      a[u] = na[u];
-      b[u] = nb[u];
-      wh[u] = nwh[u];
-    }
+  };
+  // two register sets take turns: while one is consumed the next fetch lands in the other (no copies between them)
+  int64_t blk = block_first;
+  if (blk < block_last) fetch(blk, a, b, wh);
+  while (blk < block_last) {
+    if (blk + kBlocksPerFetch < block_last) fetch(blk + kBlocksPerFetch, na, nb, nwh);
+    consume(a, b, wh);
+    blk += kBlocksPerFetch;
+    if (blk >= block_last) break;
+    if (blk + kBlocksPerFetch < block_last) fetch(blk + kBlocksPerFetch, a, b, wh);
+    consume(na, nb, nwh);
+    blk += kBlocksPerFetch;
   }
   __syncwarp();
   for (int t = (int)lane; t < bins; t += 32) {
