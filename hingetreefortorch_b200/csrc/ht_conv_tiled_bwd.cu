@@ -302,10 +302,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv_backward_tiled_kernel(ConvBw
         }
         if (!bins_wanted) {
           // The image gradient alone (the parameter gradients came from the kernel further down).  A walk past the
-          // last output channel repeats that channel's record with a zero upstream gradient and adds a zero.
+          // last output channel (it repeats that channel's record) adds nothing.
           if (position_valid) {
+            const bool ragged = jl + 4 > count_j;  // the same for the whole CTA
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
+              if (ragged && jl + u >= count_j) continue;
               const float wg = __fmul_rn(lds_f32(rec[u] + 4u * wk[u].path + (lay.w - 4u * kL)), gval[u]);
               const float dx = signed_term(wk[u].nm, wg);
               const uint32_t off = offset_of_vertex<OrdT, PAIRS>(rec[u], wk[u].v, lay.ord);
